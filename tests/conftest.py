@@ -1,0 +1,24 @@
+"""Shared pytest configuration: the ``gpu`` marker and import paths."""
+
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+
+
+@pytest.fixture(scope="session")
+def golden() -> dict:
+    """Fixtures recorded from the reference's Python host layer."""
+
+    return json.loads((ROOT / "tests" / "golden" / "reference_golden.json").read_text())

@@ -1,0 +1,182 @@
+"""Regenerate ``reference_golden.json`` from the reference's own Python layer.
+
+Run where the reference checkout is available (it is not on the GPU box):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference's CUDA kernels and its DeepGEMM scorer cannot run without their
+GPU and third-party dependency, but its pure-Python host layer imports on a
+CPU.  This script calls that layer (sample schedule, guarded rank, sample
+positions, RNG stream seeds, the standard input recipe, the output-contract
+validator and the cutoff-tie oracle) and records inputs and outputs as small
+fixtures; the tests replay them against this package's own implementations.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import json
+import sys
+from pathlib import Path
+
+
+def _digest(tensor) -> str:
+    import torch
+
+    return hashlib.sha256(tensor.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def main(reference_root: str) -> None:
+    sys.path.insert(0, str(Path(reference_root) / "src"))
+    import torch
+    from fused_index_topk.api import PrefillCase
+    from fused_index_topk.correctness import (
+        CorrectnessError,
+        build_score_threshold_oracle,
+        compare_topk_indices,
+        validate_topk_indices,
+    )
+    from fused_index_topk.inputs import input_stream_seeds, make_prefill_inputs
+    from fused_index_topk.kernel.plugin import (
+        _SAMPLING_SEED_XOR,
+        _TARGET_CANDIDATES,
+        production_sample_elements,
+    )
+    from fused_index_topk.kernel.sampling import common_random_sample_ids, guarded_sample_rank
+
+    golden: dict = {"source": "EdgePro001/FusedIndexTopK v0.3.0 python host layer"}
+
+    # 1. sample schedule + guarded rank + sample positions
+    schedule = []
+    for context in (8192, 12288, 16384, 16512, 32768, 40000, 65536, 98304, 131072, 163840):
+        samples = production_sample_elements(context)
+        rank = guarded_sample_rank(
+            samples, context, target_candidates=_TARGET_CANDIDATES, guard_sigmas=2.0
+        )
+        rank_loose = guarded_sample_rank(samples, context, target_candidates=3072, guard_sigmas=0.5)
+        seed = (0 ^ _SAMPLING_SEED_XOR) & ((1 << 63) - 1)
+        ids = common_random_sample_ids(torch, context, samples, seed=seed, device="cpu")
+        schedule.append(
+            {
+                "context_tokens": context,
+                "sample_elements": samples,
+                "sample_rank": rank,
+                "sample_rank_target3072_guard0p5": rank_loose,
+                "sampling_seed": seed,
+                "sample_ids_sha256": _digest(ids),
+                "sample_ids_head": ids[:8].tolist(),
+                "sample_ids_tail": ids[-4:].tolist(),
+            }
+        )
+    golden["sampling"] = schedule
+
+    # 2. RNG stream seeds
+    golden["stream_seeds"] = {
+        f"{seed}:{fixture}": input_stream_seeds(seed, fixture)
+        for seed in (0, 1, 20260803)
+        for fixture in ("A", "B")
+    }
+
+    # 3. the standard input recipe, generated on the CPU
+    recipe = []
+    for rows, keys, seed, fixture in ((6, 96, 0, "A"), (8, 8192, 0, "A"), (8, 8192, 0, "B"), (64, 512, 7, "B")):
+        case = PrefillCase(f"golden-q{rows}-n{keys}", rows, keys, top_k=min(2048, keys), seed=seed)
+        made = make_prefill_inputs(case, device="cpu", fixture_id=fixture)
+        recipe.append(
+            {
+                "query_tokens": rows, "context_tokens": keys, "seed": seed, "fixture_id": fixture,
+                "sha256": {
+                    name: _digest(getattr(made, name))
+                    for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")
+                },
+                "kv_scales_head": made.kv_scales[:4].tolist(),
+                "weights_head": made.weights[0, :4].tolist(),
+            }
+        )
+    golden["input_recipe"] = recipe
+
+    # 4. cutoff-tie oracle and tie-aware comparison on small dense score matrices
+    tie_cases = []
+    generator = torch.Generator().manual_seed(1234)
+    for rows, keys, top_k, levels in ((4, 12, 3, 5), (6, 40, 8, 6), (5, 64, 16, 4), (8, 33, 5, 50)):
+        case = PrefillCase("tie", rows, keys, top_k=top_k, seed=0)
+        values = torch.randint(0, levels, (rows, keys), generator=generator).float()
+        position = torch.arange(keys)[None, :]
+        ends = torch.arange(keys - rows + 1, keys + 1)[:, None]
+        scores = torch.where(position < ends, values, torch.full_like(values, -float("inf")))
+        top_values, top_ids = torch.topk(scores, top_k, dim=-1, sorted=False)
+        baseline = torch.where(torch.isfinite(top_values), top_ids, torch.full_like(top_ids, -1))
+        baseline = baseline.to(torch.int32).unsqueeze(1).contiguous()
+        summary, tie_rows = build_score_threshold_oracle(scores, baseline, case)
+        # a candidate that swaps one tied id per tied row, and one that takes a low id
+        swapped = baseline.clone()
+        broken = baseline.clone()
+        for row, tie in tie_rows.items():
+            chosen = set(int(v) for v in baseline[row, 0].tolist())
+            spare = [b for b in tie["boundary_ids"] if b not in chosen]
+            used = [b for b in tie["boundary_ids"] if b in chosen]
+            if spare and used:
+                column = baseline[row, 0].tolist().index(used[0])
+                swapped[row, 0, column] = spare[0]
+        verdict_swapped = compare_topk_indices(swapped, baseline, case, cutoff_tie_rows=tie_rows)
+        # replace a strictly-above-cutoff id by an unselected one -> must be rejected
+        rejected = None
+        for row in range(rows):
+            end = keys - rows + row + 1
+            if end <= top_k:
+                continue
+            chosen = set(int(v) for v in baseline[row, 0].tolist() if v >= 0)
+            live = scores[row, :end]
+            cutoff = torch.topk(live, top_k).values[-1]
+            above = [i for i in chosen if live[i] > cutoff]
+            spare = [i for i in range(end) if i not in chosen]
+            if above and spare:
+                column = baseline[row, 0].tolist().index(above[0])
+                broken[row, 0, column] = spare[0]
+                try:
+                    compare_topk_indices(broken, baseline, case, cutoff_tie_rows=tie_rows)
+                    rejected = False
+                except CorrectnessError:
+                    rejected = True
+                break
+        tie_cases.append(
+            {
+                "rows": rows, "keys": keys, "top_k": top_k,
+                "scores": [[None if v == -float("inf") else v for v in r] for r in scores.tolist()],
+                "baseline": baseline.tolist(),
+                "summary": summary,
+                "tie_rows": {str(k): {kk: list(vv) if isinstance(vv, tuple) else vv for kk, vv in v.items()}
+                             for k, v in tie_rows.items()},
+                "swapped": swapped.tolist(),
+                "swapped_verdict": verdict_swapped,
+                "broken": broken.tolist(),
+                "broken_rejected": rejected,
+            }
+        )
+    golden["tie_oracle"] = tie_cases
+
+    # 5. output-contract validator messages
+    case = PrefillCase("small", 3, 3, top_k=4, seed=1)
+    good = torch.tensor([[[0, -1, -1, -1]], [[1, 0, -1, -1]], [[2, 0, 1, -1]]], dtype=torch.int32)
+    contract = {"good_summary": validate_topk_indices(good, case), "violations": []}
+    for label, data in (
+        ("duplicate", [[[0, -1, -1, -1]], [[1, 1, -1, -1]], [[2, 0, 1, -1]]]),
+        ("outside", [[[1, -1, -1, -1]], [[1, 0, -1, -1]], [[2, 0, 1, -1]]]),
+        ("count", [[[0, -1, -1, -1]], [[1, 0, -1, -1]], [[2, 0, -1, -1]]]),
+        ("negative", [[[0, -2, -1, -1]], [[1, 0, -1, -1]], [[2, 0, 1, -1]]]),
+    ):
+        try:
+            validate_topk_indices(torch.tensor(data, dtype=torch.int32), case)
+            message = None
+        except CorrectnessError as error:
+            message = str(error)
+        contract["violations"].append({"label": label, "data": data, "message": message})
+    golden["output_contract"] = contract
+
+    target = Path(__file__).resolve().parent / "reference_golden.json"
+    target.write_text(json.dumps(golden, indent=1, sort_keys=True) + "\n")
+    print(f"wrote {target} ({target.stat().st_size} bytes)")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
