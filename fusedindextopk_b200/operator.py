@@ -1,0 +1,305 @@
+"""The operator: sampled thresholds -> fused score + exact Top-K -> device-masked repair.
+
+``fused_index_topk(q, (kv, kv_scales), weights, k_start, k_end, top_k=2048)``
+returns the exact, unordered Top-K key ids of every query row as int32
+``[Q,K]`` (``-1`` padded) and keeps the argument layout of
+``deep_gemm.fp8_mqa_logits`` as the reference calls it
+(``src/fused_index_topk/variants/common.py:19-26``).  ``Workspace`` owns every
+scratch buffer, like ``FusedIndexTopK.prepare`` does in the reference
+(``src/fused_index_topk/kernel/plugin.py:202-257``); the stage functions mirror
+the reference's five stage closures (``kernel/plugin.py:259-380``) and only
+launch kernels on the current stream: no allocation, no host synchronisation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+from . import _lib, sampling
+from ._lib import FusedArgs, check, current_stream, load_library, ptr
+
+TOP_K = _lib.TOP_K
+
+
+def _require(condition: bool, message: str) -> None:
+    if not condition:
+        raise ValueError(message)
+
+
+def validate_operator_inputs(q: Any, kv: Any, kv_scales: Any, weights: Any, k_start: Any, k_end: Any) -> tuple[int, int]:
+    """Shape / dtype / layout / device contract of the six inputs; returns ``(Q, N)``.
+
+    Same checks as the reference's host binding
+    (``kernel/csrc/long_fused_bindings.cpp:119-153``).
+    """
+
+    import torch
+
+    _require(q.is_cuda, "q must be a CUDA tensor (there is no CPU path)")
+    _require(q.dim() == 3 and q.shape[1] == _lib.HEADS and q.shape[2] == _lib.HEAD_DIM,
+             "q must have shape [Q, 64, 128]")
+    _require(kv.dim() == 2 and kv.shape[1] == _lib.HEAD_DIM, "kv must have shape [N, 128]")
+    _require(q.dtype == torch.float8_e4m3fn and kv.dtype == torch.float8_e4m3fn, "q and kv must be float8_e4m3fn")
+    rows, keys = int(q.shape[0]), int(kv.shape[0])
+    _require(rows > 0 and keys > 0, "Q and N must be positive")
+    _require(keys <= _lib.MAX_KEYS, f"N must not exceed {_lib.MAX_KEYS}")
+    _require(kv_scales.dtype == torch.float32 and tuple(kv_scales.shape) == (keys,), "kv_scales must be float32 [N]")
+    _require(weights.dtype == torch.float32 and tuple(weights.shape) == (rows, _lib.HEADS),
+             "weights must be float32 [Q, 64]")
+    _require(k_start.dtype == torch.int32 and k_end.dtype == torch.int32, "k_start and k_end must be int32")
+    _require(tuple(k_start.shape) == (rows,) and tuple(k_end.shape) == (rows,), "k_start and k_end must have shape [Q]")
+    for name, tensor in (("q", q), ("kv", kv), ("kv_scales", kv_scales), ("weights", weights),
+                         ("k_start", k_start), ("k_end", k_end)):
+        _require(tensor.is_contiguous(), f"{name} must be contiguous")
+        _require(tensor.device == q.device, f"{name} must live on the same device as q")
+    return rows, keys
+
+
+@dataclass
+class SamplePlan:
+    """Host-side decisions of the threshold prepass for one context length."""
+
+    context_tokens: int
+    sample_elements: int
+    sample_rank: int
+    target_candidates: int
+    sample_ids: Any          # int32 [S] on the device, sorted
+    enabled: bool            # False: every row has few enough keys, thresholds are -inf
+
+
+def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigmas: float = 2.0) -> SamplePlan:
+    """Sample size, guarded rank and sample positions (``kernel/plugin.py:187-201``)."""
+
+    import torch
+
+    target = sampling.TARGET_CANDIDATES
+    if context_tokens <= target:
+        empty = torch.zeros(0, dtype=torch.int32, device=device)
+        return SamplePlan(context_tokens, 0, 0, target, empty, False)
+    elements = sampling.production_sample_elements(context_tokens)
+    rank = sampling.guarded_sample_rank(
+        elements, context_tokens, target_candidates=target, guard_sigmas=guard_sigmas
+    )
+    ids = sampling.common_random_sample_ids(
+        torch, context_tokens, elements, seed=sampling.sampling_seed(seed), device=device
+    )
+    return SamplePlan(context_tokens, elements, rank, target, ids, True)
+
+
+@dataclass
+class Workspace:
+    """All scratch buffers of one (Q, N) problem on one device."""
+
+    rows: int
+    keys: int
+    device: Any
+    plan: SamplePlan
+    block_begin: int = 0
+    block_stride: int = 1
+    num_blocks: int = 0
+    buffers: dict = field(default_factory=dict)
+
+    def __getattr__(self, name: str) -> Any:
+        buffers = self.__dict__.get("buffers", {})
+        if name in buffers:
+            return buffers[name]
+        raise AttributeError(name)
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported an expired bounded wait.  Synchronises; not for timed code."""
+
+        value = int(self.status.item())
+        if value != 0:
+            raise _lib.ItkError(f"device status word is {value:#x} (bit 0: a bounded wait expired)")
+
+
+def make_workspace(
+    rows: int,
+    keys: int,
+    device: Any,
+    *,
+    seed: int = 0,
+    guard_sigmas: float = 2.0,
+    block_begin: int = 0,
+    block_stride: int = 1,
+    with_pairs: bool = False,
+    repair: bool = True,
+) -> Workspace:
+    """Allocate every buffer once, outside any timed region."""
+
+    import torch
+
+    load_library()
+    sizes = _lib.workspace_sizes(rows, keys, 1)
+    plan = make_sample_plan(keys, seed=seed, device=device, guard_sigmas=guard_sigmas)
+    total_blocks = (rows + _lib.BLOCK_Q - 1) // _lib.BLOCK_Q
+    owned = len(range(block_begin, total_blocks, block_stride))
+    u8, i32, i64, f32 = torch.uint8, torch.int32, torch.int64, torch.float32
+
+    def empty(shape, dtype):
+        return torch.empty(shape, device=device, dtype=dtype)
+
+    samples = max(plan.sample_elements, 1)
+    buffers = {
+        "output_ids": empty((rows, TOP_K), i32),
+        "failure_flags": torch.zeros(rows, device=device, dtype=u8),
+        "thresholds": torch.full((rows,), -math.inf, device=device, dtype=f32),
+        "spill_pairs": empty((rows, _lib.SPILL_U64_PER_ROW), i64),
+        "sampled_kv": empty((samples, _lib.HEAD_DIM), u8),
+        "sampled_scales": empty((samples,), f32),
+        "status": torch.zeros(1, device=device, dtype=i32),
+    }
+    assert buffers["spill_pairs"].numel() * 8 == sizes.spill_bytes
+    if with_pairs:
+        buffers["output_pairs"] = empty((rows, TOP_K), i64)
+        buffers["output_counts"] = torch.zeros(rows, device=device, dtype=i32)
+    if repair:
+        chunks = sizes.repair_chunks
+        buffers.update(
+            repair_pairs=empty((rows, _lib.REPAIR_CHUNK), i64),
+            local_pairs=empty((rows, TOP_K), i64),
+            local_counts=torch.zeros(rows, device=device, dtype=i32),
+            accumulator_pairs=empty((rows, TOP_K), i64),
+            accumulator_counts=torch.zeros(rows, device=device, dtype=i32),
+            repair_error_flags=torch.zeros(rows, device=device, dtype=u8),
+            chunk_starts=empty((chunks, rows), i32),
+            chunk_ends=empty((chunks, rows), i32),
+        )
+    return Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
+
+
+# --------------------------------------------------------------------------- stages
+
+
+def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None) -> Any:
+    """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph."""
+
+    import torch
+
+    if not ws.plan.enabled:
+        ws.thresholds.fill_(-math.inf)
+        return ws.thresholds
+    library = load_library()
+    stream = current_stream(torch, ws.device)
+    plan = ws.plan
+    check(library.itk_gather_sampled_kv(
+        ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
+        ws.keys, plan.sample_elements, stream,
+    ))
+    check(library.itk_sample_thresholds(
+        ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
+        ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
+        plan.target_candidates, ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
+        ptr(ws.status), stream,
+    ))
+    return ws.thresholds
+
+
+def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, thresholds=None,
+                   diag_logits=None, trace=None, force_compute: bool = False, max_ctas: int = 0,
+                   key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False) -> Any:
+    """Stage ``fused_topk``: one launch of the persistent fused kernel."""
+
+    import torch
+
+    args = FusedArgs()
+    args.q, args.kv, args.kv_scales, args.weights = ptr(q), ptr(kv), ptr(kv_scales), ptr(weights)
+    args.k_start, args.k_end = ptr(k_start), ptr(k_end)
+    args.thresholds = ptr(ws.thresholds if thresholds is None else thresholds)
+    args.out_ids = ptr(ws.output_ids)
+    if want_pairs:
+        args.out_pairs = ptr(ws.output_pairs)
+        args.out_counts = ptr(ws.output_counts)
+    args.failure_flags = ptr(ws.failure_flags)
+    args.spill = ptr(ws.spill_pairs)
+    args.diag_logits = ptr(diag_logits)
+    args.diag_stride = 0 if diag_logits is None else int(diag_logits.stride(0))
+    args.trace = ptr(trace)
+    args.status = ptr(ws.status)
+    args.rows, args.keys = ws.rows, ws.keys
+    args.key_lo = key_lo
+    args.key_hi = ws.keys if key_hi is None else key_hi
+    args.shards = 1
+    args.block_begin, args.block_stride, args.num_blocks = ws.block_begin, ws.block_stride, ws.num_blocks
+    args.force_compute = 1 if force_compute else 0
+    args.max_ctas = max_ctas
+    check(load_library().itk_fused_topk(ctypes.byref(args), current_stream(torch, ws.device)))
+    return ws.output_ids
+
+
+def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
+               key_hi: int | None = None, want_pairs: bool = False) -> Any:
+    """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags."""
+
+    import torch
+
+    library = load_library()
+    stream = current_stream(torch, ws.device)
+    key_hi = ws.keys if key_hi is None else key_hi
+    check(library.itk_update_chunk_ranges(
+        ptr(k_start), ptr(k_end), ptr(ws.chunk_starts), ptr(ws.chunk_ends), ws.rows, ws.keys, stream
+    ))
+    first = True
+    for chunk_index, chunk_lo in enumerate(range(0, ws.keys, _lib.REPAIR_CHUNK)):
+        chunk_hi = min(ws.keys, chunk_lo + _lib.REPAIR_CHUNK)
+        if chunk_hi <= key_lo or chunk_lo >= key_hi:
+            continue
+        check(library.itk_repair_produce(
+            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
+            ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
+            ws.num_blocks, ptr(ws.status), stream,
+        ))
+        check(library.itk_chunk_local_topk(
+            ptr(ws.repair_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
+            ptr(ws.failure_flags), ptr(ws.local_pairs), ptr(ws.local_counts), ptr(ws.repair_error_flags),
+            ws.rows, 1 if first else 0, stream,
+        ))
+        check(library.itk_merge_topk_pairs(
+            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.local_pairs), ptr(ws.local_counts),
+            ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, 1 if first else 0, stream,
+        ))
+        first = False
+    check(library.itk_finalize_repair(
+        ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.output_ids),
+        ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None,
+        ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, stream,
+    ))
+    return ws.output_ids
+
+
+def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end) -> Any:
+    """Sampling + fused kernel + repair on the current stream; returns ``ws.output_ids``."""
+
+    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end)
+    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end)
+    if "repair_pairs" in ws.buffers:
+        run_repair(ws, q, kv, kv_scales, weights, k_start, k_end)
+    return ws.output_ids
+
+
+_WORKSPACES: dict[tuple, Workspace] = {}
+
+
+def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *, workspace: Workspace | None = None,
+                     seed: int = 0) -> Any:
+    """Exact unordered Top-K key ids per query row, int32 ``[Q, K]``, ``-1`` padded.
+
+    ``kv_pair`` is ``(kv, kv_scales)``.  Without ``workspace`` one is cached per
+    (Q, N, device, seed); the returned tensor is that workspace's output buffer
+    and is overwritten by the next call with the same key.
+    """
+
+    kv, kv_scales = kv_pair
+    _require(top_k == TOP_K, f"top_k must be {TOP_K}")
+    rows, keys = validate_operator_inputs(q, kv, kv_scales, weights, k_start, k_end)
+    if workspace is None:
+        key = (rows, keys, str(q.device), int(seed))
+        workspace = _WORKSPACES.get(key)
+        if workspace is None:
+            workspace = make_workspace(rows, keys, q.device, seed=seed)
+            _WORKSPACES[key] = workspace
+    _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
+    return run_operator(workspace, q, kv, kv_scales, weights, k_start, k_end)

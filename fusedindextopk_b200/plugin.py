@@ -1,0 +1,250 @@
+"""The operator as a ``VariantPlugin``: the drop-in boundary towards a harness.
+
+Mirrors ``FusedIndexTopK`` / ``create_variant`` of the reference
+(``src/fused_index_topk/kernel/plugin.py:67-490``): same plugin id, same option
+names and validation errors, ``supports`` / ``fingerprint_metadata`` /
+``prepare``, a prepared graph whose stages re-read ``artifacts["inputs"]`` on
+every run (so one prepared graph serves fixture A and fixture B) and whose
+terminal artifact ``"indices"`` is int32 ``[Q,1,K]``.  Differences that follow
+from the B200 design: the sampled GEMM and the threshold selection are one
+stage (one launch), a query block is four rows, and odd Q is supported.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import math
+from pathlib import Path
+from typing import Any, Mapping
+
+from . import _lib, operator, sampling
+from .api import (
+    API_VERSION,
+    PrefillCase,
+    PrefillInputs,
+    PreparedGraph,
+    RunMode,
+    StageNode,
+    StageSpec,
+    VariantDescriptor,
+)
+
+_ROOT = Path(__file__).resolve().parent
+_ALLOWED_OPTIONS = {"verbose_build", "sample_guard_sigmas", "debug_ctas", "diagnostic", "block_q"}
+
+
+def _source_fingerprint() -> dict[str, Any]:
+    digest = hashlib.sha256()
+    files = sorted((_ROOT / "csrc").glob("*.cu*")) + sorted(_ROOT.glob("*.py"))
+    for path in files:
+        digest.update(path.name.encode())
+        digest.update(path.read_bytes())
+    return {"sha256": digest.hexdigest(), "files": len(files)}
+
+
+class FusedIndexTopK:
+    """Same-kernel score production and exact Top-K for B200, with device-masked repair."""
+
+    descriptor = VariantDescriptor(
+        plugin_id="fused_index_topk",
+        display_name="FusedIndexTopK",
+        api_version=API_VERSION,
+        implementation_version="0.1.0",
+        mode="fused",
+        description=(
+            "Persistent tcgen05/TMEM score production with in-CTA exact Top-K, bounded "
+            "overflow spill and device-masked exact repair"
+        ),
+        implementation="b200-native-tcgen05+cuda-radix",
+        exact_topk=True,
+        source_revision="fusedindextopk-b200-0.1",
+        supported_arches=("sm100",),
+        tags=(
+            "prefill", "sm100", "deepseek-v3.2", "same-kernel-exact-topk",
+            "bounded-overflow-salvage", "device-exactness-guard", "no-host-sync", "no-dense-logits",
+        ),
+    )
+
+    def __init__(self, options: Mapping[str, Any] | None = None) -> None:
+        self.options = dict(options or {})
+        unknown = set(self.options) - _ALLOWED_OPTIONS
+        if unknown:
+            raise ValueError(f"unknown FusedIndexTopK options: {sorted(unknown)}")
+        guard = self.options.get("sample_guard_sigmas", 2.0)
+        if isinstance(guard, bool) or not isinstance(guard, (int, float)) or not math.isfinite(guard) or guard < 0:
+            raise ValueError("sample_guard_sigmas must be finite and non-negative")
+        self.sample_guard_sigmas = float(guard)
+        self.debug_ctas = self.options.get("debug_ctas", 0)
+        if type(self.debug_ctas) is not int or self.debug_ctas < 0:
+            raise ValueError("debug_ctas must be a nonnegative integer")
+        self.diagnostic = self.options.get("diagnostic", False)
+        if type(self.diagnostic) is not bool:
+            raise ValueError("diagnostic must be bool")
+        self.block_q = self.options.get("block_q", _lib.BLOCK_Q)
+        if type(self.block_q) is not int or self.block_q != _lib.BLOCK_Q:
+            raise ValueError(f"block_q must be {_lib.BLOCK_Q}")
+
+    def supports(self, case: PrefillCase) -> bool:
+        return (
+            case.batch_size == 1
+            and case.causal
+            and case.indexer_heads == _lib.HEADS
+            and case.head_dim == _lib.HEAD_DIM
+            and case.query_tokens > 0
+            and case.context_tokens >= case.query_tokens
+            and case.context_tokens >= case.top_k > 0
+            and 8192 <= case.context_tokens <= sampling.MAX_CONTEXT
+            and case.context_tokens % 128 == 0
+            and case.top_k == sampling.TOP_K
+        )
+
+    def fingerprint_metadata(self) -> Mapping[str, Any]:
+        return {
+            "algorithm": "same-kernel-exact-topk-with-bounded-overflow-salvage-b200",
+            "operator_sources": _source_fingerprint(),
+            "options": self.options,
+            "normal_candidate_gmem_bytes": 0,
+            "spill_capacity_per_segment": _lib.SPILL_U64_PER_ROW // 8,
+            "spill_workspace_bytes_per_row": _lib.SPILL_U64_PER_ROW * 8,
+            "spill_index_bits": 32,
+            "candidate_index_bits": 16,
+            "index_encoding": "segment-relative-lossless",
+            "candidate_segments": 8,
+            "max_context": sampling.MAX_CONTEXT,
+            "block_q": self.block_q,
+            "timed_repair": True,
+            "repair_host_sync": False,
+        }
+
+    def prepare(
+        self,
+        case: PrefillCase,
+        inputs: PrefillInputs,
+        *,
+        options: Mapping[str, Any],
+        mode: RunMode,
+    ) -> PreparedGraph:
+        if not self.supports(case):
+            raise ValueError(f"unsupported FusedIndexTopK case: {case}")
+        if options and dict(options) != self.options:
+            raise ValueError("variant options changed after FusedIndexTopK construction")
+        import torch
+
+        device = inputs.q.device
+        ws = operator.make_workspace(
+            case.query_tokens, case.context_tokens, device, seed=case.seed,
+            guard_sigmas=self.sample_guard_sigmas,
+        )
+        diag = None
+        if self.diagnostic:
+            diag = torch.full(
+                (case.query_tokens, case.context_tokens), -math.inf, device=device, dtype=torch.float32
+            )
+        max_ctas = self.debug_ctas
+
+        def tensors(artifacts: dict) -> tuple:
+            standard: PrefillInputs = artifacts["inputs"]
+            operator.validate_operator_inputs(
+                standard.q, standard.kv, standard.kv_scales, standard.weights, standard.k_start, standard.k_end
+            )
+            return (standard.q, standard.kv, standard.kv_scales, standard.weights, standard.k_start, standard.k_end)
+
+        def run_sample_threshold(context: Any, artifacts: dict) -> None:
+            del context
+            operator.run_sample_thresholds(ws, *tensors(artifacts))
+            artifacts["sampled_kv"] = ws.sampled_kv
+            artifacts["sampled_scales"] = ws.sampled_scales
+            artifacts["thresholds"] = ws.thresholds
+
+        def run_fused_topk(context: Any, artifacts: dict) -> None:
+            del context
+            operator.run_fused_topk(
+                ws, *tensors(artifacts), thresholds=artifacts["thresholds"], diag_logits=diag,
+                force_compute=diag is not None, max_ctas=max_ctas,
+            )
+            artifacts["fast_failure_flags"] = ws.failure_flags
+            artifacts["fast_indices"] = ws.output_ids.unsqueeze(1)
+            artifacts["spill_pairs"] = ws.spill_pairs
+            if diag is not None:
+                artifacts["diagnostic_logits"] = diag
+
+        def run_hierarchical_repair(context: Any, artifacts: dict) -> None:
+            del context
+            operator.run_repair(ws, *tensors(artifacts))
+            artifacts["failure_flags"] = ws.failure_flags
+            artifacts["repair_error_flags"] = ws.repair_error_flags
+            artifacts["indices"] = ws.output_ids.unsqueeze(1)
+
+        nodes = (
+            StageNode(
+                StageSpec(
+                    stage_id="sample_threshold",
+                    dependencies=(),
+                    consumes=("inputs",),
+                    produces=("sampled_kv", "sampled_scales", "thresholds"),
+                    semantic_ops=("indexer", "topk"),
+                    description="Gather the common random key sample, score it on the tensor cores and "
+                                "radix-select the guarded sample rank per row",
+                    kernel_regexes=("itk_gather_kernel", "itk_fused_kernel"),
+                ),
+                run_sample_threshold,
+            ),
+            StageNode(
+                StageSpec(
+                    stage_id="fused_topk",
+                    dependencies=("sample_threshold",),
+                    consumes=("inputs", "thresholds"),
+                    produces=("fast_failure_flags", "fast_indices"),
+                    semantic_ops=("indexer", "topk", "output"),
+                    description="UMMA score production and exact Top-K in CTA shared memory",
+                    kernel_regexes=("itk_fused_kernel",),
+                ),
+                run_fused_topk,
+            ),
+            StageNode(
+                StageSpec(
+                    stage_id="hierarchical_repair",
+                    dependencies=("fused_topk",),
+                    consumes=("inputs", "fast_failure_flags", "fast_indices"),
+                    produces=("failure_flags", "repair_error_flags", "indices"),
+                    semantic_ops=("indexer", "topk", "output"),
+                    description="Device-masked exact 16K-chunk rescans with online Top-2048 pair merge",
+                    kernel_regexes=(
+                        "itk_chunk_ranges_kernel", "itk_fused_kernel", "itk_pair_topk_kernel",
+                        "itk_finalize_repair_kernel",
+                    ),
+                ),
+                run_hierarchical_repair,
+            ),
+        )
+        sizes = _lib.workspace_sizes(case.query_tokens, case.context_tokens, 1)
+        return PreparedGraph(
+            descriptor=self.descriptor,
+            nodes=nodes,
+            initial_artifacts={"inputs": inputs},
+            terminal_artifact="indices",
+            metadata={
+                "algorithm": "same-kernel-bounded-overflow-salvage-b200",
+                "sample_elements": ws.plan.sample_elements,
+                "sample_rank_descending": ws.plan.sample_rank,
+                "sample_target_candidates": ws.plan.target_candidates,
+                "sample_guard_sigmas": self.sample_guard_sigmas,
+                "sampling_granularity": "individual-random-token",
+                "dense_logits_materialized": diag is not None,
+                "candidate_segments": 8,
+                "device_failure_flags": True,
+                "timed_failure_repair": True,
+                "repair_dispatch": "device-mask-no-host-sync",
+                "repair_chunk_elements": _lib.REPAIR_CHUNK,
+                "repair_chunks": sizes.repair_chunks,
+                "repair_merge": "online-exact-top2048-pairs",
+                "spill_workspace_bytes": sizes.spill_bytes,
+                "same_kernel_exact_topk": True,
+                "workspace": ws,
+                "resources": _lib.resource_report() if torch.cuda.is_available() else {},
+            },
+        )
+
+
+def create_variant(options: Mapping[str, Any] | None = None) -> FusedIndexTopK:
+    return FusedIndexTopK(options)

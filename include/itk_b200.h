@@ -1,0 +1,181 @@
+/*
+ * C ABI of the B200 fused score + exact Top-K operator (libitk_b200.so).
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, never allocates, never synchronises and never
+ * writes its inputs ("_out" convention: the caller owns every buffer).  The
+ * return value is 0 on success or a negative ITK_ERR_* code; itk_last_error()
+ * gives the message of the calling thread's last failure.  Conditions found on
+ * the device (a row the fast path could not prove complete, an inconsistent
+ * repair, an expired bounded wait) are reported in device memory: the per-row
+ * failure / repair-error flags and the status word.
+ *
+ * Each declaration names the reference interface it replaces (paths relative to
+ * the reference repository root).
+ *
+ * Tensor contract (src/fused_index_topk/kernel/csrc/long_fused_bindings.cpp:119-153):
+ *   q         [Q,64,128]  fp8 e4m3, contiguous, 16-byte aligned
+ *   kv        [N,128]     fp8 e4m3, contiguous, 16-byte aligned
+ *   kv_scales [N]         fp32
+ *   weights   [Q,64]      fp32, 16-byte aligned
+ *   k_start, k_end [Q]    int32, end-exclusive key range of each query row
+ *   scores are kv_scales[n] * sum_h weights[q,h] * relu(sum_d q[q,h,d]*kv[n,d])
+ */
+#ifndef ITK_B200_H
+#define ITK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* itk_stream_t;
+
+#define ITK_OK 0
+#define ITK_ERR_ARGUMENT (-1)
+#define ITK_ERR_CUDA (-2)
+#define ITK_ERR_UNSUPPORTED (-3)
+
+#define ITK_TOP_K 2048
+#define ITK_HEADS 64
+#define ITK_HEAD_DIM 128
+#define ITK_BLOCK_Q 4
+#define ITK_REPAIR_CHUNK 16384
+#define ITK_SPILL_U64_PER_ROW 5632      /* 8 segments x 704 entries */
+#define ITK_MAX_KEYS 524288             /* 16-bit segment-relative candidate ids */
+#define ITK_MAX_PAIR_SOURCES 8
+
+/* bits of the device status word */
+#define ITK_STATUS_WAIT_EXPIRED 1
+
+/* values of the per-row repair error flag */
+#define ITK_REPAIR_ERR_COUNT 1
+#define ITK_REPAIR_ERR_LOCAL_SELECT 2
+#define ITK_REPAIR_ERR_MERGE_SELECT 3
+
+/* Library identity and one-time per-device set-up (raises the dynamic shared-memory
+ * limit of the kernels).  itk_init is idempotent and is also called lazily. */
+const char* itk_version(void);
+const char* itk_last_error(void);
+int itk_init(int device);
+
+/* Registers, shared memory and launch shape of every kernel, as "name=value" lines.
+ * Replaces resource_report() (sampling_threshold.cu:294-309, long_context_repair.cu:629-651). */
+int itk_resource_report(char* buffer, size_t buffer_bytes);
+
+/* Bytes the caller must provide for each workspace of a Q x N problem split into
+ * `shards` key ranges.  Replaces the allocations of FusedIndexTopK.prepare
+ * (src/fused_index_topk/kernel/plugin.py:202-257). */
+typedef struct itk_workspace_sizes {
+    size_t spill_bytes;            /* uint64 [shards,Q,8,704] */
+    size_t repair_pairs_bytes;     /* uint64 [shards*Q,16384] */
+    size_t pairs_bytes;            /* uint64 [shards,Q,2048]: local / accumulator / output pairs, each */
+    size_t counts_bytes;           /* int32  [shards,Q] */
+    size_t flags_bytes;            /* uint8  [shards,Q] */
+    size_t thresholds_bytes;       /* float  [shards,Q] */
+    size_t chunk_ranges_bytes;     /* int32  [chunks,Q], each of start and end */
+    int repair_chunks;
+} itk_workspace_sizes;
+int itk_workspace_bytes(int rows, int keys, int shards, itk_workspace_sizes* sizes);
+
+/* sampled_kv[s,:] = kv[sample_ids[s],:], sampled_scales[s] = kv_scales[sample_ids[s]].
+ * Replaces gather_out (sampling_threshold.cu:185-234). */
+int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t* sample_ids, void* sampled_kv,
+                          float* sampled_scales, int keys, int samples, itk_stream_t stream);
+
+/* Threshold prepass in one launch: scores of every query row against the S gathered
+ * sample keys on the tensor cores, then per row the sample_rank-th largest score among
+ * samples whose key position lies in [k_start,k_end) and whose score is finite;
+ * -inf when k_end-k_start <= target_candidates or fewer than sample_rank samples are
+ * valid.  Replaces deep_gemm.fp8_mqa_logits on the sample (kernel/plugin.py:272-282)
+ * followed by threshold_out (sampling_threshold.cu:236-292).  diag_logits (optional,
+ * fp32 [Q,diag_stride]) receives the dense sampled scores. */
+int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,
+                          const int32_t* sample_ids, const int32_t* k_start, const int32_t* k_end,
+                          float* thresholds, int rows, int samples, int sample_rank, int target_candidates,
+                          float* diag_logits, long long diag_stride, int* status, itk_stream_t stream);
+
+/* Arguments of the fused kernel.  Replaces fp8_mqa_topk_out
+ * (kernel/csrc/long_fused_bindings.cpp:100-184). */
+typedef struct itk_fused_args {
+    const void* q;
+    const void* kv;
+    const float* kv_scales;
+    const float* weights;
+    const int32_t* k_start;
+    const int32_t* k_end;
+    const float* thresholds;    /* [shards,Q] */
+    int32_t* out_ids;           /* [Q,2048]; may be null when out_pairs is given */
+    uint64_t* out_pairs;        /* optional [shards,Q,2048]: (ordered score << 32) | key */
+    int32_t* out_counts;        /* optional [shards,Q], with out_pairs */
+    uint8_t* failure_flags;     /* [shards,Q]: 1 = row must be repaired */
+    uint64_t* spill;            /* [shards,Q,8,704] scratch */
+    float* diag_logits;         /* optional fp32 [Q,diag_stride] dense scores (-inf outside the range) */
+    long long diag_stride;
+    long long* trace;           /* optional int64 [CTAs,32] phase trace; selects the diagnostic build.
+                                 * Counterpart of the ITK_LONG_DIAGNOSTIC trace
+                                 * (kernel/csrc/include/fused_index_topk/long_cta_topk.cuh:8-29) */
+    int* status;                /* device status word (or-ed) */
+    int rows;                   /* Q */
+    int keys;                   /* N */
+    int key_lo;                 /* first key scored (multiple of 128) */
+    int key_hi;                 /* one past the last key scored */
+    int shards;                 /* key range is cut into this many equal shards (>= 1) */
+    int block_begin;            /* first owned block of 4 query rows */
+    int block_stride;           /* stride between owned blocks (number of ranks) */
+    int num_blocks;             /* owned blocks */
+    int force_compute;          /* 1: score rows even when all their keys are selected anyway */
+    int max_ctas;               /* 0 = one CTA per SM */
+} itk_fused_args;
+int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream);
+
+/* chunk_start/chunk_end [chunks,Q]: the row ranges rebased into each 16384-key chunk.
+ * Replaces update_ranges_out ( long_context_repair.cu:671-701; kernel :653-669). */
+int itk_update_chunk_ranges(const int32_t* k_start, const int32_t* k_end, int32_t* chunk_start,
+                            int32_t* chunk_end, int rows, int keys, itk_stream_t stream);
+
+/* For rows whose failure flag is set: recompute the scores of keys
+ * [chunk_lo, chunk_hi) (at most 16384) and write every pair to
+ * repair_pairs[row, key-chunk_lo] (0 where the key is outside the row's range).
+ * Replaces produce_repair_candidates_out (kernel/csrc/repair/repair_producer_bindings.cpp:19-30). */
+int itk_repair_produce(const void* q, const void* kv, const float* kv_scales, const float* weights,
+                       const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
+                       uint64_t* repair_pairs, int rows, int keys, int chunk_lo, int chunk_hi, int block_begin,
+                       int block_stride, int num_blocks, int* status, itk_stream_t stream);
+
+/* Exact Top-2048 pairs of one chunk for flagged rows.  chunk_start/chunk_end are the
+ * chunk-local ranges of itk_update_chunk_ranges (the number of live pairs must equal
+ * their difference, else repair error 1).  Replaces local_topk_pairs_out
+ * (long_context_repair.cu:467-527). */
+int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_start, const int32_t* chunk_end,
+                         const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
+                         uint8_t* repair_error_flags, int rows, int first_chunk, itk_stream_t stream);
+
+/* accumulator <- Top-2048(accumulator U local) for flagged rows.  Replaces
+ * merge_topk_pairs_out (long_context_repair.cu:529-576). */
+int itk_merge_topk_pairs(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* local_pairs,
+                         const int32_t* local_counts, const uint8_t* failure_flags, uint8_t* repair_error_flags,
+                         int rows, int first_chunk, itk_stream_t stream);
+
+/* Repaired rows: ids (and optionally pairs / counts) into the operator output, flag
+ * cleared.  Replaces finalize_repair_out (long_context_repair.cu:578-616). */
+int itk_finalize_repair(const uint64_t* accumulator_pairs, const int32_t* accumulator_counts, int32_t* out_ids,
+                        uint64_t* out_pairs, int32_t* out_counts, uint8_t* failure_flags,
+                        const uint8_t* repair_error_flags, int rows, itk_stream_t stream);
+
+/* Exact Top-2048 of the union of `sources` candidate lists per row, each
+ * [Q,2048] pairs with [Q] counts: the merge step after key-range sharding, across
+ * shards of one GPU or across the all-gathered per-GPU candidates.  A row is flagged
+ * in failure_flags (optional) when the union holds fewer than min(2048, valid) pairs.
+ * Has no counterpart kernel in the reference (which is single-GPU); it applies the
+ * selection rule of select_topk_pairs (long_context_repair.cu:139-235). */
+int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts,
+                              int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
+                              itk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ITK_B200_H */

@@ -1,0 +1,263 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs.
+
+Three levels, as the operator's contract defines them:
+(i)   diagnostic dense scores vs the float64-accumulated oracle: ``|err| <= 1e-3 * rowmax``;
+(ii)  the returned id sets are a bit-exact Top-K of the kernel's own fp32 scores under
+      the tie rule (no tolerance);
+(iii) vs the oracle's sets, differences only inside the tolerance window, counted.
+"""
+
+from __future__ import annotations
+
+import math
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+from oracle import oracle  # noqa: E402
+
+from fusedindextopk_b200 import _lib, operator  # noqa: E402
+from fusedindextopk_b200.api import PrefillCase, RunMode, execute_graph  # noqa: E402
+from fusedindextopk_b200.correctness import (  # noqa: E402
+    score_threshold_check,
+    tolerance_set_report,
+    validate_topk_indices,
+)
+from fusedindextopk_b200.inputs import inputs_to, make_prefill_inputs, make_workload_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+RELATIVE_TOLERANCE = 1e-3  # of the row maximum, for fp32 scores
+
+
+@pytest.fixture(scope="module")
+def device():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _tensors(inputs):
+    return (inputs.q, inputs.kv, inputs.kv_scales, inputs.weights, inputs.k_start, inputs.k_end)
+
+
+def _assert_close_to_oracle(got: torch.Tensor, want: torch.Tensor) -> float:
+    finite = torch.isfinite(want)
+    assert torch.equal(finite, torch.isfinite(got)), "mask pattern differs"
+    row_max = torch.where(finite, want, torch.zeros_like(want)).abs().amax(dim=1, keepdim=True)
+    error = torch.where(finite, (got - want).abs(), torch.zeros_like(want))
+    worst = float((error / row_max.clamp_min(1e-30)).max())
+    assert worst <= RELATIVE_TOLERANCE, f"score error {worst:.3e} of the row maximum"
+    return worst
+
+
+def _run_with_diagnostics(host, device, *, thresholds=None, repair=True):
+    rows, keys = host.case.query_tokens, host.case.context_tokens
+    gpu = inputs_to(host, device)
+    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed)
+    if thresholds is None:
+        operator.run_sample_thresholds(ws, *_tensors(gpu))
+    else:
+        ws.thresholds.fill_(thresholds)
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(ws, *_tensors(gpu), diag_logits=logits, force_compute=True)
+    fast_flags = ws.failure_flags.clone()
+    if repair:
+        operator.run_repair(ws, *_tensors(gpu))
+    torch.cuda.synchronize()
+    ws.check_status()
+    return ws, logits, fast_flags
+
+
+def test_library_loads_and_reports_resources(device):
+    report = _lib.resource_report()
+    assert int(report["fused_topk.registers_per_thread"]) <= 128
+    assert int(report["fused_topk.local_bytes_per_thread"]) <= 64
+    assert int(report["sm_count"]) >= 100
+
+
+@pytest.mark.parametrize("rows,keys", [(8, 8192), (5, 8192), (1, 9000)])
+def test_sampled_scores_and_thresholds(device, rows, keys):
+    host = make_workload_inputs("c0", query_tokens=rows, context_tokens=keys)
+    gpu = inputs_to(host, device)
+    ws = operator.make_workspace(rows, keys, device)
+    plan = ws.plan
+    diag = torch.full((rows, plan.sample_elements), math.nan, device=device)
+    operator.run_sample_thresholds(ws, *_tensors(gpu), diag_logits=diag)
+    torch.cuda.synchronize()
+    ws.check_status()
+    want = oracle.sampled_logits(host.q, host.kv, host.kv_scales, host.weights, plan.sample_ids.cpu())
+    _assert_close_to_oracle(diag.cpu(), want)
+    # the threshold is the exact guarded rank of the kernel's own sampled scores
+    expected = oracle.sampled_thresholds(
+        diag.cpu(), plan.sample_ids.cpu(), host.k_start, host.k_end, plan.sample_rank, plan.target_candidates
+    )
+    assert torch.equal(ws.thresholds.cpu(), expected)
+    # the production build (no dense output) gives the same thresholds
+    first = ws.thresholds.clone()
+    ws.thresholds.fill_(123.0)
+    operator.run_sample_thresholds(ws, *_tensors(gpu))
+    torch.cuda.synchronize()
+    assert torch.equal(ws.thresholds, first)
+
+
+@pytest.mark.parametrize(
+    "workload,rows,keys",
+    [("c0", 8, 8192), ("c1", 16, 16384), ("c0", 7, 9000), ("c0", 1, 8192), ("c1", 6, 3000), ("c0", 3, 100)],
+)
+def test_fused_scores_and_topk_against_oracle(device, workload, rows, keys):
+    host = make_workload_inputs(workload, query_tokens=rows, context_tokens=keys)
+    case = PrefillCase("parity", rows, keys, 2048, 0)
+    ws, logits, _ = _run_with_diagnostics(host, device)
+    want = oracle.dense_logits(host.q, host.kv, host.kv_scales, host.weights, host.k_start, host.k_end)
+    _assert_close_to_oracle(logits.cpu(), want)
+    assert int(ws.failure_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)          # (ii) bit-exact on own scores
+    report = tolerance_set_report(indices, want, case, relative_tolerance=RELATIVE_TOLERANCE)  # (iii)
+    assert report["status"] == "passed"
+
+
+@pytest.mark.parametrize("threshold", [-math.inf, math.inf])
+def test_forced_spill_and_forced_repair(device, threshold):
+    """-inf floods the candidate segments (spill, then overflow); +inf starves them (underflow)."""
+
+    host = make_workload_inputs("c1", query_tokens=12, context_tokens=16384)
+    case = PrefillCase("forced", 12, 16384, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=threshold)
+    assert int(fast_flags.sum()) == 12, "every row must have been flagged by the fast path"
+    assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+
+
+def test_spill_path_without_overflow(device):
+    """N = 8192 with threshold -inf fills every segment to exactly its smem + spill capacity."""
+
+    host = make_workload_inputs("c0", query_tokens=8, context_tokens=8192)
+    case = PrefillCase("spill", 8, 8192, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=-math.inf, repair=False)
+    assert int(fast_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+
+
+def test_tie_workload_is_exact_under_the_tie_rule(device):
+    host = make_workload_inputs("c4", query_tokens=32, context_tokens=32768)
+    case = PrefillCase("ties", 32, 32768, 2048, 0)
+    ws, logits, _ = _run_with_diagnostics(host, device)
+    assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    verdict = score_threshold_check(indices, logits.cpu(), case)
+    assert verdict["rows_with_cutoff_ties"] > 0, "the tie workload must actually tie at the cutoff"
+
+
+def test_zero_queries_tie_everywhere(device):
+    """All-zero queries make every score 0: any K valid ids are an exact answer."""
+
+    host = make_workload_inputs("c0", query_tokens=4, context_tokens=8192)
+    host.q = torch.zeros_like(host.q.view(torch.uint8)).view(torch.float8_e4m3fn)
+    case = PrefillCase("zero", 4, 8192, 2048, 0)
+    ws, logits, _ = _run_with_diagnostics(host, device)
+    assert int(ws.failure_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+
+
+def test_public_callable_and_ab_fixtures_share_one_workspace(device):
+    case = PrefillCase("ab", 24, 8192, 2048, seed=3)
+    results = {}
+    for fixture in ("A", "B", "A"):
+        host = make_prefill_inputs(case, device="cpu", fixture_id=fixture)
+        gpu = inputs_to(host, device)
+        from fusedindextopk_b200 import fused_index_topk
+
+        ids = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end, seed=case.seed)
+        torch.cuda.synchronize()
+        assert ids.shape == (24, 2048) and ids.dtype == torch.int32
+        want_ids, want_logits = oracle.fused_index_topk(
+            host.q, host.kv, host.kv_scales, host.weights, host.k_start, host.k_end
+        )
+        indices = ids.unsqueeze(1).contiguous().cpu()
+        validate_topk_indices(indices, case)
+        tolerance_set_report(indices, want_logits, case, relative_tolerance=RELATIVE_TOLERANCE)
+        results.setdefault(fixture, []).append(indices.clone())
+    assert torch.equal(results["A"][0].sort(dim=-1).values, results["A"][1].sort(dim=-1).values)
+    assert not torch.equal(results["A"][0].sort(dim=-1).values, results["B"][0].sort(dim=-1).values)
+
+
+def test_plugin_graph_matches_reference_output_contract(device):
+    from fusedindextopk_b200 import create_variant
+
+    case = PrefillCase("plugin", 16, 8192, 2048, seed=5)
+    plugin = create_variant({"diagnostic": True})
+    assert plugin.supports(case)
+    host = make_prefill_inputs(case, device="cpu")
+    graph = plugin.prepare(case, inputs_to(host, device), options={"diagnostic": True}, mode=RunMode.CORRECTNESS)
+    assert [node.spec.stage_id for node in graph.nodes] == ["sample_threshold", "fused_topk", "hierarchical_repair"]
+    indices = execute_graph(graph, case)
+    torch.cuda.synchronize()
+    assert tuple(indices.shape) == (16, 1, 2048) and indices.dtype == torch.int32
+    indices = indices.contiguous().cpu()
+    validate_topk_indices(indices, case)
+    want = oracle.dense_logits(host.q, host.kv, host.kv_scales, host.weights, host.k_start, host.k_end)
+    tolerance_set_report(indices, want, case, relative_tolerance=RELATIVE_TOLERANCE)
+    # fixture B through the same prepared graph
+    host_b = make_prefill_inputs(case, device="cpu", fixture_id="B")
+    indices_b = execute_graph(graph, case, inputs=inputs_to(host_b, device)).contiguous().cpu()
+    torch.cuda.synchronize()
+    want_b = oracle.dense_logits(host_b.q, host_b.kv, host_b.kv_scales, host_b.weights, host_b.k_start, host_b.k_end)
+    tolerance_set_report(indices_b, want_b, case, relative_tolerance=RELATIVE_TOLERANCE)
+
+
+def test_invalid_arguments_raise(device):
+    host = make_workload_inputs("c0", query_tokens=4, context_tokens=8192)
+    gpu = inputs_to(host, device)
+    from fusedindextopk_b200 import fused_index_topk
+
+    with pytest.raises(ValueError, match="top_k"):
+        fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end, top_k=1024)
+    with pytest.raises(ValueError, match="CUDA"):
+        fused_index_topk(host.q, (host.kv, host.kv_scales), host.weights, host.k_start, host.k_end)
+    with pytest.raises(ValueError, match="int32"):
+        fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start.long(), gpu.k_end)
+    ws = operator.make_workspace(4, 8192, device)
+    args = _lib.FusedArgs()
+    with pytest.raises(_lib.ItkError, match="must not be null"):
+        _lib.check(_lib.load_library().itk_fused_topk(args, None))
+    assert ws.status.item() == 0
+
+
+@pytest.mark.parametrize(
+    "workload,rows,keys",
+    [("c1", 4096, 16384), ("c2", 256, 65536), ("c3", 64, 163840), ("c3s", 64, 131072), ("c4", 512, 32768)],
+)
+def test_full_size_properties(device, workload, rows, keys):
+    """Benchmark-sized cases: the result is a bit-exact Top-K of the kernel's own dense
+    scores (tie rule), satisfies the output contract and leaves no row flagged."""
+
+    host = make_workload_inputs(workload, query_tokens=rows, context_tokens=keys)
+    case = PrefillCase("full", rows, keys, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device)
+    assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits, case)
+    # the production build (no dense output) returns the same sets where scores are distinct
+    gpu = inputs_to(host, device)
+    first = indices.clone()
+    operator.run_operator(ws, *_tensors(gpu))
+    torch.cuda.synchronize()
+    ws.check_status()
+    again = ws.output_ids.unsqueeze(1).contiguous()
+    validate_topk_indices(again, case)
+    score_threshold_check(again, logits, case)
+    if workload != "c4":
+        assert torch.equal(first.sort(dim=-1).values, again.sort(dim=-1).values)
