@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the fused score + exact Top-K operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1] [--impl ours|reference]
+
+One step = one operator call (threshold sampling + fused kernel + device-masked
+repair) over one batch of seeded synthetic inputs of the named workload.  The
+default workload is c1 (Q=4096, N=16384, K=2048, 16 sink keys), the shape the
+headline metric is quoted on.  With N > 1 ranks (launched by torch.distributed.run)
+the query rows of the same problem are sharded over the ranks in blocks of four
+rows dealt round-robin, keys replicated, no collective on the data path; a step
+then costs the slowest rank's time ("strong" scaling).  For the short-Q workload
+c3s the key range is sharded instead, and the step includes the NCCL all-gather of
+the per-rank Top-2048 candidates and the merge.
+
+Rank 0 prints ONE JSON line.  `value` is microseconds per call with inputs resident
+in HBM (CUDA events, summed over the K timed steps, max over ranks); `e2e` is the
+same call through the public API from pinned host buffers with the host->device
+copies of all inputs and the device->host copy of the ids inside the timed region;
+`roofline` is the fused kernel alone against the dense-FP8 tensor-core peak;
+`cpu_baseline` is the CPU restatement of the reference path (dense fp32 scores +
+torch.topk) on a bounded row sample.  `--impl reference` times only that CPU path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fused_score_topk_us_per_call"
+UNIT = "us/call"
+L2_FLUSH_BYTES = 512 * 1024 * 1024
+NOMINAL_FP8_TFLOPS = 4500.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch, from the ncu
+# capture summarised under profiles/ (bytes per launch at the named size), or None.
+NCU_TRAFFIC_BYTES = {}
+
+
+def algorithmic_flops(rows_list, heads=64, dim=128) -> float:
+    """2*H*d per causally valid (query, key) pair; rows_list = valid keys per row."""
+
+    return 2.0 * heads * dim * float(sum(rows_list))
+
+
+def fp8_peak_tflops() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        measured = json.loads(path.read_text())
+        return 2.0 * float(measured["bf16_tflops"]), "2 x measured cuBLAS bf16 burst (MEASURED_PEAKS.json), of measured"
+    return 2.0 * 1590.0, "2 x fallback bf16 1590 TFLOP/s, of fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index = index
+        self.lines: list[str] = []
+        self.process = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.process is not None and self.process.stdout is not None
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [item.strip() for item in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[4:8]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def cpu_reference_time(host, sample_rows: int, threads: int) -> dict:
+    """Time the CPU restatement (dense fp32 scores + torch.topk) on evenly spaced rows."""
+
+    import torch
+
+    from oracle import oracle
+
+    torch.set_num_threads(threads)
+    rows = host.case.query_tokens
+    picked = torch.linspace(0, rows - 1, steps=min(sample_rows, rows)).round().long().unique()
+    q = host.q[picked]
+    weights = host.weights[picked]
+    k_start, k_end = host.k_start[picked], host.k_end[picked]
+    begin = time.perf_counter()
+    logits = oracle.dense_logits(q, host.kv, host.kv_scales, weights, k_start, k_end,
+                                 accumulate=torch.float32, row_chunk=8)
+    oracle.reference_topk_indices(logits, k_end)
+    elapsed = time.perf_counter() - begin
+    per_row = elapsed / picked.numel()
+    return {
+        "value": per_row * rows * 1e6, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": f"{picked.numel()} evenly spaced query rows of {rows}, {elapsed:.2f} s of CPU work, "
+                  f"extrapolated per row x Q (torch dense fp32 scores + torch.topk, the reference's exact path)",
+        "seconds": elapsed,
+    }
+
+
+def shard_rows(host, rank: int, world: int):
+    """Inputs of the query blocks (4 rows each) owned by `rank`: blocks rank, rank+world, ..."""
+
+    import torch
+    from dataclasses import replace
+
+    if world == 1:
+        return host, torch.arange(host.case.query_tokens)
+    rows = host.case.query_tokens
+    blocks = torch.arange((rows + 3) // 4)
+    mine = blocks[rank::world]
+    row_ids = (mine[:, None] * 4 + torch.arange(4)[None, :]).flatten()
+    row_ids = row_ids[row_ids < rows]
+    case = replace(host.case, query_tokens=int(row_ids.numel()))
+    local = replace(
+        host, case=case, q=host.q[row_ids].contiguous(), weights=host.weights[row_ids].contiguous(),
+        k_start=host.k_start[row_ids].contiguous(), k_end=host.k_end[row_ids].contiguous(),
+    )
+    return local, row_ids
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="c1")
+    parser.add_argument("--rows", type=int, default=None, help="scale the workload down to this many query rows")
+    parser.add_argument("--keys", type=int, default=None, help="scale the workload down to this many keys")
+    parser.add_argument("--cpu-sample-rows", type=int, default=2048)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-e2e", action="store_true")
+    args = parser.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+
+    import torch
+
+    from fusedindextopk_b200.inputs import WORKLOADS, inputs_to, make_workload_inputs
+
+    workload = WORKLOADS[args.workload]
+    config = {
+        "workload": f"{args.workload}: Q={args.rows or workload.query_tokens} N={args.keys or workload.context_tokens} "
+                    f"K=2048 H=64 d=128 fp8 e4m3, {workload.description}",
+        "query_tokens": args.rows or workload.query_tokens,
+        "context_tokens": args.keys or workload.context_tokens,
+        "top_k": 2048,
+        "partitioning": "single GPU" if world == 1 else f"query blocks of 4 rows round-robin over {world} ranks, keys replicated",
+        "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written before every timed step (L2 flush)",
+        "includes": "threshold sampling + fused kernel + device-masked repair",
+    }
+    threads = os.cpu_count() or 1
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        host = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys)
+        rows_per_step = max(8, min(args.cpu_sample_rows, host.case.query_tokens) // 2)
+        for _ in range(min(args.warmup, 1)):
+            cpu_reference_time(host, 8, threads)
+        values = [cpu_reference_time(host, rows_per_step, threads) for _ in range(args.steps)]
+        value = statistics.mean(item["value"] for item in values)
+        line = {
+            "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"each step: {values[0]['sample']}"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "queries_per_s": host.case.query_tokens / (value * 1e-6),
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line))
+        return
+
+    # ------------------------------------------------------------------ our arm (GPU)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    from fusedindextopk_b200 import operator
+
+    host_full = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys)
+    host, row_ids = shard_rows(host_full, rank, world)
+    rows, keys = host.case.query_tokens, host.case.context_tokens
+    gpu = inputs_to(host, device)
+    tensors = (gpu.q, gpu.kv, gpu.kv_scales, gpu.weights, gpu.k_start, gpu.k_end)
+    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    chunks = (keys + 16383) // 16384
+    launches_per_step = (2 if ws.plan.enabled else 0) + 1 + 1 + 3 * chunks + 1
+
+    def barrier() -> None:
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_steps(count: int):
+        total_ms, fused_ms = 0.0, 0.0
+        events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(count)]
+        for ev in events:
+            flush.fill_(1)
+            ev[0].record()
+            operator.run_sample_thresholds(ws, *tensors)
+            ev[1].record()
+            operator.run_fused_topk(ws, *tensors)
+            ev[2].record()
+            operator.run_repair(ws, *tensors)
+            ev[3].record()
+        torch.cuda.synchronize()
+        for ev in events:
+            total_ms += ev[0].elapsed_time(ev[3])
+            fused_ms += ev[1].elapsed_time(ev[2])
+        return total_ms, fused_ms
+
+    barrier()
+    timed_steps(max(args.warmup, 3))
+    ws.check_status()
+    flagged_fast = None
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms, fused_ms = timed_steps(args.steps)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ws.check_status()
+    unrepaired = int(ws.failure_flags.sum().item())
+
+    # ------------------------------------------------------------------ end to end from pinned host memory
+    e2e_ms = 0.0
+    h2d_bytes = d2h_bytes = 0
+    if not args.no_e2e:
+        from fusedindextopk_b200 import fused_index_topk
+
+        pinned = {name: getattr(host, name).pin_memory() for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")}
+        staged = {name: torch.empty_like(getattr(gpu, name)) for name in pinned}
+        out_host = torch.empty((rows, 2048), dtype=torch.int32).pin_memory()
+        h2d_bytes = sum(t.numel() * t.element_size() for t in pinned.values())
+        d2h_bytes = out_host.numel() * out_host.element_size()
+
+        def e2e_step():
+            for name, source in pinned.items():
+                staged[name].copy_(source, non_blocking=True)
+            ids = fused_index_topk(staged["q"], (staged["kv"], staged["kv_scales"]), staged["weights"],
+                                   staged["k_start"], staged["k_end"], workspace=ws)
+            out_host.copy_(ids, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        for _ in range(args.steps):
+            flush.fill_(1)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            e2e_step()
+            end.record()
+            end.synchronize()
+            e2e_ms += begin.elapsed_time(end)
+        barrier()
+
+    if distributed:
+        stats = torch.tensor([total_ms, fused_ms, e2e_ms, float(unrepaired)], device=device, dtype=torch.float64)
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        total_ms, fused_ms, e2e_ms, unrepaired = (float(stats[0]), float(stats[1]), float(stats[2]), int(stats[3]))
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    us_per_call = total_ms * 1e3 / args.steps
+    fused_us = fused_ms * 1e3 / args.steps
+    total_rows = host_full.case.query_tokens
+    flops_total = algorithmic_flops(host_full.k_end.tolist())          # k_start == 0
+    flops_rank = algorithmic_flops(host.k_end.tolist())                # the slowest rank's launch
+    peak, peak_source = fp8_peak_tflops()
+    achieved = flops_rank / (fused_us * 1e-6) / 1e12
+    line = {
+        "metric": METRIC, "value": us_per_call, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": us_per_call / 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic",
+        "config": config,
+        "queries_per_s": total_rows / (us_per_call * 1e-6),
+        "algorithmic_tflops": flops_total / (us_per_call * 1e-6) / 1e12,
+        "fraction_of_fp8_peak_end_to_end": flops_total / (us_per_call * 1e-6) / 1e12 / (peak * args.gpus),
+        "fused_kernel_us": fused_us,
+        "unrepaired_rows": unrepaired,
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_BYTES.get((args.workload, total_rows, keys)),
+            "kernel": "itk_fused_kernel<kModeTopK>", "peak_source": peak_source,
+            "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
+            "flops_per_launch": flops_rank,
+        },
+        "clocks": clocks,
+    }
+    if not args.no_e2e:
+        e2e_us = e2e_ms * 1e3 / args.steps
+        line["e2e"] = {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes}
+    if not args.no_cpu_baseline and args.gpus == 1:
+        baseline = cpu_reference_time(host_full, args.cpu_sample_rows, threads)
+        baseline.pop("seconds", None)
+        line["cpu_baseline"] = baseline
+    print(json.dumps(line))
+    if distributed:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -12,7 +12,10 @@ from ctypes import POINTER, c_char_p, c_int, c_int32, c_longlong, c_size_t, c_ui
 from pathlib import Path
 from typing import Any
 
-LIBRARY_PATH = Path(__file__).resolve().parent / "libitk_b200.so"
+import os
+
+# ITK_B200_LIBRARY points the loader at another build of the same library (timing studies).
+LIBRARY_PATH = Path(os.environ.get("ITK_B200_LIBRARY") or Path(__file__).resolve().parent / "libitk_b200.so")
 
 TOP_K = 2048
 HEADS = 64
@@ -20,7 +23,7 @@ HEAD_DIM = 128
 BLOCK_Q = 4
 REPAIR_CHUNK = 16384
 SPILL_U64_PER_ROW = 5632
-MAX_KEYS = 524288
+MAX_KEYS = 262144
 MAX_PAIR_SOURCES = 8
 STATUS_WAIT_EXPIRED = 1
 
@@ -50,7 +53,7 @@ class FusedArgs(ctypes.Structure):
         ("k_start", c_void_p), ("k_end", c_void_p), ("thresholds", c_void_p),
         ("out_ids", c_void_p), ("out_pairs", c_void_p), ("out_counts", c_void_p),
         ("failure_flags", c_void_p), ("spill", c_void_p), ("diag_logits", c_void_p),
-        ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p),
+        ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p), ("debug_skip", c_int),
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
         ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
         ("force_compute", c_int), ("max_ctas", c_int),

@@ -304,6 +304,7 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.diag_logits = a.diag_logits;
     params.diag_stride = a.diag_stride;
     params.trace = a.trace;
+    params.debug_skip = a.debug_skip;
     params.status = a.status;
     params.rows = a.rows;
     params.keys = a.keys;

@@ -38,6 +38,13 @@
 
 #include "itk_ptx.cuh"
 
+// Build-time experiment switch for timing studies (0 in every shipped build):
+//   1 = epilogue only drains TMEM and hands the buffer back, 2 = drain + head reduction, no filtering,
+//   3 = like 1 without even reading TMEM, 4 = like 1 and the key tiles are not fetched (stale shared memory).
+#ifndef ITK_EXPERIMENT
+#define ITK_EXPERIMENT 0
+#endif
+
 namespace itk {
 
 constexpr int kHeads = 64;
@@ -50,16 +57,20 @@ constexpr int kAccBuffers = 2;
 constexpr int kTmemColumns = kAccBuffers * kUmmaN;  // 512 = all of TMEM
 constexpr int kTopK = 2048;
 
-constexpr int kSegments = 8;                   // one per epilogue warp: segment = (key >> 5) & 7
-constexpr int kSegCap = 320;                   // shared-memory candidates per (row, segment)
+constexpr int kSegments = 4;                   // one per TMEM lane quarter: segment = (key >> 5) & 3
+constexpr int kSegCap = 640;                   // shared-memory candidates per (row, segment)
 constexpr int kRowCap = kSegments * kSegCap;   // 2560
-constexpr int kSpillSegCap = 704;              // global spill entries per (row, segment)
+constexpr int kSpillSegCap = 1408;             // global spill entries per (row, segment)
 constexpr int kSpillRow = kSegments * kSpillSegCap;  // 5632 u64 per row
 constexpr int kRepairChunk = 16384;
 
 constexpr int kThreads = 512;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kEpilogueThreads = 256;
+constexpr int kEpilogueWarps = kEpilogueThreads / 32;
+constexpr int kEpilogueRegisters = 192;        // per-thread budget of the two epilogue warpgroups
+constexpr int kOtherRegisters = 64;            // ... and of the producer / issuer / consumer warpgroups
+static_assert(256 * kEpilogueRegisters + 256 * kOtherRegisters <= 65536, "register pool of one SM");
 constexpr int kConsumerThreads = 192;
 constexpr int kConsumerWarps = kConsumerThreads / 32;
 
@@ -99,6 +110,7 @@ struct FusedParams {
     float* diag_logits;         // [rows, diag_stride] dense scores, diagnostic builds only
     long long diag_stride;
     long long* trace;           // [grid, kTraceFields] per-CTA cycle counters, diagnostic builds only
+    int debug_skip;             // diagnostic builds only: 1 no selection, 2 no compaction, 4 no head reduction
     int* status;                // device status word, bits are or-ed in
     int rows;                   // Q
     int keys;                   // N (or S in kModeSample)
@@ -146,16 +158,16 @@ static_assert(kFusedSmemBytes <= 232448, "fused kernel exceeds the 227 KB shared
 static_assert(kSegCap % 32 == 0 && kSpillSegCap % 32 == 0, "segment capacities are warp multiples");
 
 // mbar_wait that adds the cycles it took to `cycles` in diagnostic builds.
-template <bool DIAG>
+template <bool DIAG, bool HOT = false>
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                            long long& cycles) {
     if (DIAG) {
         const long long begin = clock64();
-        const bool ok = mbar_wait(bar, parity, abort_flag);
+        const bool ok = mbar_wait<HOT>(bar, parity, abort_flag);
         cycles += clock64() - begin;
         return ok;
     }
-    return mbar_wait(bar, parity, abort_flag);
+    return mbar_wait<HOT>(bar, parity, abort_flag);
 }
 
 // ------------------------------------------------------------------ work units
@@ -231,12 +243,12 @@ __device__ __forceinline__ void consumer_sync() {
 
 // Key index of shared-memory candidate `packed` stored in segment `segment`.
 __device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
-    return static_cast<int>(((packed >> 5) << 8) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
+    return static_cast<int>(((packed >> 5) << 7) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
 }
 
 __device__ __forceinline__ uint16_t encode_key(int key) {
     const uint32_t k = static_cast<uint32_t>(key);
-    return static_cast<uint16_t>(((k >> 8) << 5) | (k & 31u));
+    return static_cast<uint16_t>(((k >> 7) << 5) | (k & 31u));
 }
 
 // Warp-aggregated slot reservation: every lane calls, active lanes get distinct slots.
@@ -250,6 +262,15 @@ __device__ __forceinline__ int warp_reserve(int* counter, bool active, int lane)
     return active ? base + __popc(mask & ((1u << lane) - 1u)) : -1;
 }
 
+// Adds one count per active lane to hist[bin]; lanes of a warp that hit the same bin
+// are combined into one shared-memory atomic.  Every lane of the warp must call.
+__device__ __forceinline__ void warp_hist_add(int* hist, bool active, uint32_t bin, int lane) {
+    const unsigned live = __ballot_sync(0xffffffffu, active);
+    if (!active) return;
+    const unsigned peers = __match_any_sync(live, bin);
+    if (lane == __ffs(static_cast<int>(peers)) - 1) atomicAdd(&hist[bin], __popc(peers));
+}
+
 // The view the consumer has of one row's candidates: counted shared-memory
 // segments plus the row's spill region in global memory.
 struct RowCandidates {
@@ -259,33 +280,143 @@ struct RowCandidates {
     const uint64_t* spill;    // [kSegments][kSpillSegCap]
 };
 
-// Four rounds of 8-bit radix selection over the ordered score bits of one row.
+// Spilled candidates live in global memory (L2); every consumer thread keeps up to
+// kSpillRegs of them in registers so that the selection rounds do not pay the L2
+// latency again.  Entry e of the row's spill (segments concatenated) belongs to
+// thread e % 192, register e / 192; entries beyond 192 * kSpillRegs stay in global memory.
+constexpr int kSpillRegs = 8;
+constexpr int kSpillCached = kSpillRegs * kConsumerThreads;
+
+struct SpillView {
+    int first[kSegments + 1];         // prefix sums of the per-segment spill counts
+    uint32_t score[kSpillRegs];
+    uint32_t key[kSpillRegs];
+};
+
+__device__ __forceinline__ uint64_t spill_entry(const RowCandidates& c, const SpillView& v, int e) {
+    int segment = 0;
+    int begin = 0;
+#pragma unroll
+    for (int i = 1; i < kSegments; ++i) {
+        if (e >= v.first[i]) {
+            segment = i;
+            begin = v.first[i];
+        }
+    }
+    return c.spill[segment * kSpillSegCap + (e - begin)];
+}
+
+__device__ __forceinline__ void load_spill(const RowCandidates& c, SpillView& v, int ctid) {
+    v.first[0] = 0;
+#pragma unroll
+    for (int s = 0; s < kSegments; ++s) {
+        const int spilled = c.spill == nullptr ? 0 : min(max(c.counts[s] - kSegCap, 0), kSpillSegCap);
+        v.first[s + 1] = v.first[s] + spilled;
+    }
+    const int total = v.first[kSegments];
+#pragma unroll
+    for (int k = 0; k < kSpillRegs; ++k) {
+        const int e = ctid + k * kConsumerThreads;
+        uint64_t pair = 0ull;
+        if (e < total) pair = spill_entry(c, v, e);
+        v.score[k] = static_cast<uint32_t>(pair >> 32);
+        v.key[k] = static_cast<uint32_t>(pair);
+    }
+}
+
+// Calls visit(live, score) for every candidate of the row, warp-uniformly (all 32 lanes of
+// every consumer warp make every call; `live` tells whether the lane holds a candidate).
+template <typename Visit>
+__device__ __forceinline__ void for_each_score(const RowCandidates& c, const SpillView& v, int ctid, Visit&& visit) {
+    const int lane = ctid & 31;
+    const int cwarp = ctid >> 5;
+#pragma unroll 1
+    for (int s = 0; s < kSegments; ++s) {
+        const int in_smem = min(c.counts[s], kSegCap);
+        for (int base = cwarp * 32; base < in_smem; base += kConsumerThreads) {
+            const int i = base + lane;
+            const bool live = i < in_smem;
+            visit(live, live ? c.scores[s * kSegCap + i] : 0u);
+        }
+    }
+    const int total = v.first[kSegments];
+#pragma unroll
+    for (int k = 0; k < kSpillRegs; ++k) {
+        if (k * kConsumerThreads < total) visit(ctid + k * kConsumerThreads < total, v.score[k]);
+    }
+    for (int base = kSpillCached + cwarp * 32; base < total; base += kConsumerThreads) {
+        const int e = base + lane;
+        const bool live = e < total;
+        visit(live, live ? static_cast<uint32_t>(spill_entry(c, v, e) >> 32) : 0u);
+    }
+}
+
+// Same enumeration, also handing out the key of each candidate.
+template <typename Visit>
+__device__ __forceinline__ void for_each_pair(const RowCandidates& c, const SpillView& v, int ctid, Visit&& visit) {
+    const int lane = ctid & 31;
+    const int cwarp = ctid >> 5;
+#pragma unroll 1
+    for (int s = 0; s < kSegments; ++s) {
+        const int in_smem = min(c.counts[s], kSegCap);
+        for (int base = cwarp * 32; base < in_smem; base += kConsumerThreads) {
+            const int i = base + lane;
+            const bool live = i < in_smem;
+            visit(live, live ? c.scores[s * kSegCap + i] : 0u, live ? decode_key(c.ids[s * kSegCap + i], s) : 0);
+        }
+    }
+    const int total = v.first[kSegments];
+#pragma unroll
+    for (int k = 0; k < kSpillRegs; ++k) {
+        if (k * kConsumerThreads < total)
+            visit(ctid + k * kConsumerThreads < total, v.score[k], static_cast<int>(v.key[k]));
+    }
+    for (int base = kSpillCached + cwarp * 32; base < total; base += kConsumerThreads) {
+        const int e = base + lane;
+        const bool live = e < total;
+        const uint64_t pair = live ? spill_entry(c, v, e) : 0ull;
+        visit(live, static_cast<uint32_t>(pair >> 32), static_cast<int>(static_cast<uint32_t>(pair)));
+    }
+}
+
+// Radix selection over the ordered score bits of one row, 8 bits per round.
 // On return `prefix` is the rank-th largest score and `rank` the number of
 // candidates equal to it that belong to the top `rank_in`.  Needs
-// rank_in <= number of candidates.  Called by all consumer threads.
-__device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidates& c, int ctid, int rank_in,
-                                             uint32_t& prefix, int& rank) {
-    prefix = 0;
+// rank_in <= number of candidates.  Called by all consumer threads.  Leading
+// bytes that all candidates share are found first and skipped.
+__device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidates& c, const SpillView& v, int ctid,
+                                             int rank_in, uint32_t& prefix, int& rank) {
+    const int lane = ctid & 31;
+    // bits in which any two candidates differ
+    if (ctid == 0) {
+        sh.sel_bin = 0;                                   // reused as the OR of (score ^ reference)
+        sh.sel_greater = static_cast<int>(c.scores[0]);   // reference: any candidate, or 0 if the segment is empty
+        int s = 0;
+        while (s < kSegments && c.counts[s] == 0) ++s;
+        if (s < kSegments) sh.sel_greater = static_cast<int>(c.scores[s * kSegCap]);
+    }
+    consumer_sync();
+    const uint32_t reference = static_cast<uint32_t>(sh.sel_greater);
+    uint32_t differing = 0;
+    for_each_score(c, v, ctid, [&](bool live, uint32_t score) { differing |= live ? (score ^ reference) : 0u; });
+    differing = __reduce_or_sync(0xffffffffu, differing);
+    if (lane == 0 && differing != 0u) atomicOr(reinterpret_cast<unsigned*>(&sh.sel_bin), differing);
+    consumer_sync();
+    differing = static_cast<uint32_t>(sh.sel_bin);
+    consumer_sync();
+    const int shared_bytes = differing == 0u ? 4 : __clz(differing) >> 3;   // leading bytes common to all
+
+    uint32_t mask = shared_bytes == 0 ? 0u : 0xffffffffu << (32 - 8 * shared_bytes);
+    if (shared_bytes == 4) mask = 0xffffffffu;
+    prefix = reference & mask;
     rank = rank_in;
-    uint32_t mask = 0;
 #pragma unroll 1
-    for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int shift = 24 - 8 * shared_bytes; shift >= 0; shift -= 8) {
         for (int bin = ctid; bin < 256; bin += kConsumerThreads) sh.hist[bin] = 0;
         consumer_sync();
-#pragma unroll 1
-        for (int s = 0; s < kSegments; ++s) {
-            const int count = c.counts[s];
-            const int in_smem = min(count, kSegCap);
-            for (int i = ctid; i < in_smem; i += kConsumerThreads) {
-                const uint32_t score = c.scores[s * kSegCap + i];
-                if ((score & mask) == prefix) atomicAdd(&sh.hist[(score >> shift) & 255u], 1);
-            }
-            const int spilled = min(count, kSegCap + kSpillSegCap) - kSegCap;
-            for (int i = ctid; i < spilled; i += kConsumerThreads) {
-                const uint32_t score = static_cast<uint32_t>(c.spill[s * kSpillSegCap + i] >> 32);
-                if ((score & mask) == prefix) atomicAdd(&sh.hist[(score >> shift) & 255u], 1);
-            }
-        }
+        for_each_score(c, v, ctid, [&](bool live, uint32_t score) {
+            warp_hist_add(sh.hist, live && (score & mask) == prefix, (score >> shift) & 255u, lane);
+        });
         consumer_sync();
         if (ctid < 32) {
             // lane l owns bins 8l .. 8l+7; `above` = candidates in bins owned by higher lanes
@@ -322,59 +453,30 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
 
 // Writes the selected candidates of one row: everything above `cutoff`, then
 // `equal_needed` of the candidates equal to it (any of them).  With
-// take_all = true every candidate is written.  Returns nothing; the number of
-// entries written is greater_total + equal_needed (or the candidate total).
-__device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, int ctid, uint32_t cutoff,
-                                         int equal_needed, int greater_total, bool take_all, int32_t* out_ids,
-                                         uint64_t* out_pairs) {
+// take_all = true every candidate is written.
+__device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, const SpillView& v, int ctid,
+                                         uint32_t cutoff, int equal_needed, int greater_total, bool take_all,
+                                         int32_t* out_ids, uint64_t* out_pairs) {
     const int lane = ctid & 31;
-    const int cwarp = ctid >> 5;
-#pragma unroll 1
-    for (int s = 0; s < kSegments; ++s) {
-        const int count = c.counts[s];
-        const int in_smem = min(count, kSegCap);
-        for (int base = cwarp * 32; base < in_smem; base += kConsumerThreads) {
-            const int i = base + lane;
-            const bool live = i < in_smem;
-            const uint32_t score = live ? c.scores[s * kSegCap + i] : 0u;
-            const bool greater = live && (take_all || score > cutoff);
-            const bool equal = live && !take_all && score == cutoff;
-            const int g = warp_reserve(&sh.sel_gcount, greater, lane);
-            const int e = warp_reserve(&sh.sel_ecount, equal, lane);
-            int position = -1;
-            if (greater) position = g;
-            else if (equal && e < equal_needed) position = greater_total + e;
-            if (position >= 0 && position < kTopK) {
-                const int key = decode_key(c.ids[s * kSegCap + i], s);
-                if (out_ids != nullptr) out_ids[position] = key;
-                if (out_pairs != nullptr)
-                    out_pairs[position] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
-            }
+    for_each_pair(c, v, ctid, [&](bool live, uint32_t score, int key) {
+        const bool greater = live && (take_all || score > cutoff);
+        const bool equal = live && !take_all && score == cutoff;
+        const int g = warp_reserve(&sh.sel_gcount, greater, lane);
+        const int e = warp_reserve(&sh.sel_ecount, equal, lane);
+        int position = -1;
+        if (greater) position = g;
+        else if (equal && e < equal_needed) position = greater_total + e;
+        if (position >= 0 && position < kTopK) {
+            if (out_ids != nullptr) out_ids[position] = key;
+            if (out_pairs != nullptr)
+                out_pairs[position] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
         }
-        const int spilled = min(count, kSegCap + kSpillSegCap) - kSegCap;
-        for (int base = cwarp * 32; base < spilled; base += kConsumerThreads) {
-            const int i = base + lane;
-            const bool live = i < spilled;
-            const uint64_t pair = live ? c.spill[s * kSpillSegCap + i] : 0ull;
-            const uint32_t score = static_cast<uint32_t>(pair >> 32);
-            const bool greater = live && (take_all || score > cutoff);
-            const bool equal = live && !take_all && score == cutoff;
-            const int g = warp_reserve(&sh.sel_gcount, greater, lane);
-            const int e = warp_reserve(&sh.sel_ecount, equal, lane);
-            int position = -1;
-            if (greater) position = g;
-            else if (equal && e < equal_needed) position = greater_total + e;
-            if (position >= 0 && position < kTopK) {
-                if (out_ids != nullptr) out_ids[position] = static_cast<int32_t>(static_cast<uint32_t>(pair));
-                if (out_pairs != nullptr) out_pairs[position] = pair;
-            }
-        }
-    }
+    });
 }
 
 // Exact Top-2048 of one row from its candidates (kModeTopK consumer).
 __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                 int slot, bool has_tiles, int ctid) {
+                                                 int slot, bool has_tiles, int ctid, long long* phase = nullptr) {
     const int row = u.row0 + r;
     const long long row_slot = static_cast<long long>(u.shard) * p.rows + row;
     const int start = max(__ldg(p.k_start + row), u.key_lo);
@@ -436,9 +538,22 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
         consumer_sync();
         return;
     }
+    SpillView view;
+    long long stamp = phase != nullptr ? clock64() : 0;
+    load_spill(c, view, ctid);
+    if (phase != nullptr) {
+        // the cached spill entries are only complete once their loads have returned
+        uint32_t touch = 0;
+#pragma unroll
+        for (int k = 0; k < kSpillRegs; ++k) touch |= view.score[k];
+        if (touch == 0x80000001u) phase[3] += 1;
+        const long long now = clock64();
+        phase[0] += now - stamp;
+        stamp = now;
+    }
     if (total <= kTopK) {
         // only reachable when valid <= 2048 (threshold forced to -inf): take everything
-        emit_row(sh, c, ctid, 0u, 0, 0, true, out_ids, out_pairs);
+        emit_row(sh, c, view, ctid, 0u, 0, 0, true, out_ids, out_pairs);
         for (int i = total + ctid; i < kTopK; i += kConsumerThreads) {
             if (out_ids != nullptr) out_ids[i] = -1;
             if (out_pairs != nullptr) out_pairs[i] = 0ull;
@@ -446,14 +561,20 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
     } else {
         uint32_t cutoff;
         int equal_needed;
-        radix_select(sh, c, ctid, kTopK, cutoff, equal_needed);
-        emit_row(sh, c, ctid, cutoff, equal_needed, kTopK - equal_needed, false, out_ids, out_pairs);
+        radix_select(sh, c, view, ctid, kTopK, cutoff, equal_needed);
+        if (phase != nullptr) {
+            const long long now = clock64();
+            phase[1] += now - stamp;
+            stamp = now;
+        }
+        emit_row(sh, c, view, ctid, cutoff, equal_needed, kTopK - equal_needed, false, out_ids, out_pairs);
     }
     if (ctid == 0) {
         p.failure_flags[row_slot] = 0;
         if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
     }
     consumer_sync();
+    if (phase != nullptr) phase[2] += clock64() - stamp;
 }
 
 // Threshold of one row = rank-th largest valid sampled score (kModeSample consumer).
@@ -490,14 +611,42 @@ __device__ __forceinline__ void consume_sample_row(FusedShared& sh, const FusedP
         consumer_sync();
         return;
     }
+    SpillView view;
+    load_spill(c, view, ctid);
     uint32_t cutoff;
     int unused;
-    radix_select(sh, c, ctid, p.sample_rank, cutoff, unused);
+    radix_select(sh, c, view, ctid, p.sample_rank, cutoff, unused);
     if (ctid == 0) p.thresholds_out[row] = ordered_to_float(cutoff);
     consumer_sync();
 }
 
 // ------------------------------------------------------------------ the kernel
+
+__device__ __forceinline__ uint64_t pack_pair(float lo, float hi) {
+    uint64_t packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(lo), "f"(hi));
+    return packed;
+}
+
+__device__ __forceinline__ void unpack_pair(uint64_t packed, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(packed));
+}
+
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Lane 0 waits on the barrier, the warp then reconverges: one poller per warp.
+template <bool DIAG, bool HOT = false>
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane,
+                                          long long& cycles) {
+    int ok = 1;
+    if (lane == 0) ok = timed_wait<DIAG, HOT>(bar, parity, abort_flag, cycles) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
 
 template <int MODE, bool DIAG>
 __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_constant__ FusedParams p) {
@@ -520,11 +669,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         mbar_init(&sh.q_empty, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.w_full[i], 1);
-            mbar_init(&sh.w_empty[i], kEpilogueThreads);
+            mbar_init(&sh.w_empty[i], kEpilogueWarps);
             mbar_init(&sh.acc_full[i], 1);
-            mbar_init(&sh.acc_empty[i], kEpilogueThreads / 2);
-            mbar_init(&sh.cand_ready[i], kEpilogueThreads);
-            mbar_init(&sh.cand_free[i], kConsumerThreads);
+            mbar_init(&sh.acc_empty[i], kEpilogueWarps);
+            mbar_init(&sh.cand_ready[i], kEpilogueWarps);
+            mbar_init(&sh.cand_free[i], 1);
         }
         sh.abort = 0;
         fence_mbar_init();
@@ -540,6 +689,10 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = sh.tmem_base;
 
+    const bool is_epilogue = warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + kEpilogueWarps;
+    if (!is_epilogue) {
+    // Register budget per warpgroup: producer / issuer / consumer warpgroups give registers back ...
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegisters));
     if (warp == 0) {
         // ============================================================ TMA producer
         if (lane == 0) {
@@ -556,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 mbar_arrive_expect_tx(&sh.q_full, kQBytes);
                 tma_load_2d(smem_q, &p.map_q, &sh.q_full, 0, u.block * kUmmaN);
                 const int ws = q_iter & 1;
-                ok = mbar_wait(&sh.w_empty[ws], ((q_iter >> 1) & 1) ^ 1, abort_flag);
+                ok = timed_wait<DIAG>(&sh.w_empty[ws], ((q_iter >> 1) & 1) ^ 1, abort_flag, wait_q);
                 if (!ok) break;
                 const uint32_t w_bytes = static_cast<uint32_t>(u.nrows) * kHeads * sizeof(float);
                 mbar_arrive_expect_tx(&sh.w_full[ws], w_bytes);
@@ -566,8 +719,12 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     const int stage = kv_iter % kKvStages;
                     ok = timed_wait<DIAG>(&sh.kv_empty[stage], ((kv_iter / kKvStages) & 1) ^ 1, abort_flag, wait_kv);
                     if (!ok) break;
+#if ITK_EXPERIMENT == 4
+                    mbar_arrive(&sh.kv_full[stage]);
+#else
                     mbar_arrive_expect_tx(&sh.kv_full[stage], kKvBytes);
                     tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0, t * kTileKeys);
+#endif
                 }
                 ++q_iter;
             }
@@ -591,7 +748,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(kTileKeys, kUmmaN);
             const uint64_t desc_q = umma_desc_sw128_kmajor(smem_u32(smem_q));
             int kv_iter = 0, q_iter = 0;
-            int acc_iter[kAccBuffers] = {0, 0};
             bool ok = true;
             long long wait_acc = 0, wait_kv = 0, wait_q = 0;
             const long long role_begin = DIAG ? clock64() : 0;
@@ -602,11 +758,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 ok = timed_wait<DIAG>(&sh.q_full, q_iter & 1, abort_flag, wait_q);
                 if (!ok) break;
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
-                    const int buffer = t & 1;
+                    const int buffer = kv_iter & 1;
                     const int stage = kv_iter % kKvStages;
-                    ok = timed_wait<DIAG>(&sh.acc_empty[buffer], (acc_iter[buffer] & 1) ^ 1, abort_flag, wait_acc);
+                    ok = timed_wait<DIAG, true>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
                     if (!ok) break;
-                    ok = timed_wait<DIAG>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
+                    ok = timed_wait<DIAG, true>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
                     if (!ok) break;
                     tcgen05_fence_after_sync();
                     const uint64_t desc_kv = umma_desc_sw128_kmajor(smem_u32(smem_kv + stage * kKvBytes));
@@ -618,7 +774,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     }
                     umma_commit(&sh.kv_empty[stage]);
                     umma_commit(&sh.acc_full[buffer]);
-                    ++acc_iter[buffer];
                 }
                 if (!ok) break;
                 umma_commit(&sh.q_empty);
@@ -637,17 +792,84 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) atomicOr(p.status, kStatusWaitExpired);
         }
-    } else if (warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + kEpilogueThreads / 32) {
+    } else {
+        // ============================================================ Top-K / threshold consumers
+        if (MODE != kModeRepair) {
+            const int cwarp = warp < kEpilogueWarp0 ? warp - 2 : warp - 12 + 2;   // warps 2,3,12..15 -> 0..5
+            const int ctid = cwarp * 32 + lane;
+            int unit_iter = 0;
+            bool ok = true;
+            long long wait_ready = 0, select_cycles = 0;
+            long long phase[4] = {0, 0, 0, 0};
+            const long long role_begin = DIAG ? clock64() : 0;
+            if (DIAG && p.trace != nullptr && ctid == 0)
+                p.trace[static_cast<long long>(blockIdx.x) * kTraceFields + kTraceNsBegin] = global_timer_ns();
+            for (int iter = 0; ok; ++iter) {
+                Unit u;
+                if (!load_unit<MODE>(p, iter, u)) break;
+                const bool has_tiles = u.tile_end > u.tile_begin;
+                const int slot = unit_iter & 1;
+                if (has_tiles) {
+                    // one thread polls; the others sleep in the named barrier until it is through
+                    if (ctid == 0) {
+                        const bool got = timed_wait<DIAG>(&sh.cand_ready[slot], (unit_iter >> 1) & 1, abort_flag, wait_ready);
+                        sh.sel_failed = got ? 0 : -1;
+                    }
+                    consumer_sync();
+                    ok = sh.sel_failed != -1;
+                    consumer_sync();
+                    if (!ok) break;
+                }
+                const long long select_begin = DIAG ? clock64() : 0;
+                for (int r = 0; r < u.nrows; ++r) {
+                    if (DIAG && (p.debug_skip & 1)) continue;
+                    if (MODE == kModeTopK) consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
+                    else consume_sample_row(sh, p, u, r, slot, has_tiles, ctid);
+                }
+                if (DIAG) select_cycles += clock64() - select_begin;
+                if (has_tiles) {
+                    consumer_sync();
+                    if (ctid == 0) mbar_arrive(&sh.cand_free[slot]);
+                    ++unit_iter;
+                }
+            }
+            if (DIAG && p.trace != nullptr && ctid == 0) {
+                long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
+                trace[kTraceConTotal] = clock64() - role_begin;
+                trace[kTraceConWaitReady] = wait_ready;
+                trace[kTraceConSelect] = select_cycles;
+                trace[kTraceConUnits] = unit_iter;
+                trace[27] = phase[0];   // spill caching
+                trace[28] = phase[1];   // radix rounds
+                trace[29] = phase[2];   // emit
+                trace[kTraceNsEnd] = global_timer_ns();
+            }
+            if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
+        }
+    }
+    } else {
+        // ... and the two epilogue warpgroups (warps 4-11) take most of the register file.
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegisters));
         // ============================================================ epilogue
-        const int ew = warp - kEpilogueWarp0;   // 0..7 = candidate segment
-        const int wg = ew >> 2;                 // TMEM buffer / tile parity served by this warpgroup
-        const int quarter = ew & 3;             // TMEM lane quarter this warp may read (= warp % 4)
-        const int lane_key = quarter * 32 + lane;
+        // Every tile is shared by both warpgroups: warpgroup g owns query rows 2g and 2g+1
+        // (accumulator columns [128g, 128g+128)); a warp reads the 32 TMEM lanes (= keys) of
+        // its quarter, which is also its candidate segment.  Accumulators come out of TMEM in
+        // the 16x256b fragment layout: thread t of a warp holds, for lanes l = t/4 and l+8 of
+        // a 16-lane half, the column pairs 8n + 2(t%4) + {0,1}, n = 0..7, of one query row.
+        // So a thread only ever needs 16 of the 64 head weights of each of its two rows, kept
+        // in registers for the whole unit: no shared-memory traffic in the hot loop.  The
+        // four threads of a quad then combine their partial head sums with two shuffles.
+        const int ew = warp - kEpilogueWarp0;
+        const int wg = ew >> 2;
+        const int quarter = ew & 3;             // = warp % 4, the TMEM lane quarter this warp may read
+        const int quad = lane & 3;              // column-pair selector inside the fragment
+        const int own_i = quad & 1;             // which of the warpgroup's two rows this thread finishes
+        const int own_lane = (lane >> 2) + 8 * (quad >> 1);   // lane inside a 16-lane half it finishes
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(wg * kUmmaN);
+                                   static_cast<uint32_t>(wg * 2 * kHeads);
         const float minus_inf = __int_as_float(0xff800000);
         int unit_iter = 0;  // units with tiles
-        int acc_iter = 0;   // tiles of this warpgroup's parity
+        int acc_iter = 0;   // tiles
         bool ok = true;
         long long wait_acc = 0, wait_free = 0, wait_w = 0;
         const long long role_begin = DIAG ? clock64() : 0;
@@ -658,144 +880,213 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             const int slot = unit_iter & 1;
             const uint32_t use_parity = (unit_iter >> 1) & 1;
             if (MODE != kModeRepair) {
-                ok = timed_wait<DIAG>(&sh.cand_free[slot], use_parity ^ 1, abort_flag, wait_free);
+                ok = warp_wait<DIAG>(&sh.cand_free[slot], use_parity ^ 1, abort_flag, lane, wait_free);
                 if (!ok) break;
             }
-            ok = timed_wait<DIAG>(&sh.w_full[slot], use_parity, abort_flag, wait_w);
+            ok = warp_wait<DIAG>(&sh.w_full[slot], use_parity, abort_flag, lane, wait_w);
             if (!ok) break;
 
-            int row_lo[kBlockQ], row_hi[kBlockQ], count[kBlockQ];
-            float threshold[kBlockQ];
-            bool row_on[kBlockQ];
-#pragma unroll
-            for (int r = 0; r < kBlockQ; ++r) {
-                count[r] = 0;
-                row_on[r] = r < u.nrows;
-                row_lo[r] = 0;
-                row_hi[r] = 0;
-                threshold[r] = minus_inf;
-                if (row_on[r]) {
-                    const int row = u.row0 + r;
-                    const long long row_slot = static_cast<long long>(u.shard) * p.rows + row;
-                    const int start = __ldg(p.k_start + row);
-                    const int end = __ldg(p.k_end + row);
-                    if (MODE == kModeSample) {
-                        row_lo[r] = start;
-                        row_hi[r] = end;
-                        row_on[r] = end - start > p.target_candidates;
+            // the row this thread finishes: range, threshold, whether it is wanted at all
+            const int own_r = wg * 2 + own_i;
+            int row_lo = 0, row_hi = 0;
+            float threshold = minus_inf;
+            bool row_on = own_r < u.nrows;
+            long long own_slot = 0;
+            if (row_on) {
+                const int row = u.row0 + own_r;
+                own_slot = static_cast<long long>(u.shard) * p.rows + row;
+                const int start = __ldg(p.k_start + row);
+                const int end = __ldg(p.k_end + row);
+                if (MODE == kModeSample) {
+                    row_lo = start;
+                    row_hi = end;
+                    row_on = end - start > p.target_candidates;
+                } else {
+                    row_lo = max(start, u.key_lo);
+                    row_hi = min(min(end, p.keys), u.key_hi);
+                    if (MODE == kModeTopK) {
+                        const int valid = row_hi - row_lo;
+                        if (valid > kTopK) threshold = __ldg(p.thresholds + own_slot);
+                        row_on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
                     } else {
-                        row_lo[r] = max(start, u.key_lo);
-                        row_hi[r] = min(min(end, p.keys), u.key_hi);
-                        if (MODE == kModeTopK) {
-                            const int valid = row_hi[r] - row_lo[r];
-                            if (valid > kTopK) threshold[r] = __ldg(p.thresholds + row_slot);
-                            row_on[r] = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
-                        } else {
-                            row_on[r] = p.failure_flags[row_slot] != 0;
-                        }
+                        row_on = p.failure_flags[own_slot] != 0;
                     }
                 }
             }
+            int count0 = 0, count1 = 0;   // candidates of row 2g / 2g+1 in this warp's segment (warp-uniform)
 
-            for (int t = u.tile_begin; t < u.tile_end; ++t) {
-                if ((t & 1) != wg) continue;
-                const int key = t * kTileKeys + lane_key;   // key (or sample position) of this thread
+            // head weights of this thread's column pairs, both rows
+            uint64_t w0[8], w1[8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                w0[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][(wg * 2 + 0) * kHeads + 8 * n + 2 * quad]);
+                w1[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][(wg * 2 + 1) * kHeads + 8 * n + 2 * quad]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh.w_empty[slot]);   // weights are in registers now
+
+            // scale and range key of the two keys this thread finishes in tile t (one per 16-lane half)
+            const auto per_key = [&](int t, float (&scale)[2], int (&range_key)[2]) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
+                    const bool key_ok = key < p.keys;
+                    scale[h] = key_ok ? __ldg(p.kv_scales + key) : 0.0f;
+                    range_key[h] = key;
+                    if (MODE == kModeSample) range_key[h] = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
+                }
+            };
+            // partial head sums of one fragment load: lanes l and l+8, this thread's 16 heads.
+            // ReLU is applied in place on the fragment registers, which are consecutive pairs
+            // already, so the packed multiply-add can read them without any move.
+            const auto relu_fma = [](uint32_t& x0, uint32_t& x1, uint64_t w, uint64_t& acc) {
+                asm("{\n\t"
+                    ".reg .b64 t;\n\t"
+                    "max.f32 %0, %0, 0f00000000;\n\t"
+                    "max.f32 %1, %1, 0f00000000;\n\t"
+                    "mov.b64 t, {%0, %1};\n\t"
+                    "fma.rn.f32x2 %2, t, %3, %2;\n\t"
+                    "}"
+                    : "+f"(*reinterpret_cast<float*>(&x0)), "+f"(*reinterpret_cast<float*>(&x1)), "+l"(acc)
+                    : "l"(w));
+            };
+            const auto partial = [&](uint32_t (&r)[32], const uint64_t (&w)[8], float& lane_a, float& lane_b) {
+                uint64_t a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll
+                for (int n = 0; n < 8; n += 2) {
+                    relu_fma(r[4 * n + 0], r[4 * n + 1], w[n], a0);
+                    relu_fma(r[4 * n + 2], r[4 * n + 3], w[n], b0);
+                    relu_fma(r[4 * n + 4], r[4 * n + 5], w[n + 1], a1);
+                    relu_fma(r[4 * n + 6], r[4 * n + 7], w[n + 1], b1);
+                }
+                float x0, x1, x2, x3;
+                unpack_pair(a0, x0, x1);
+                unpack_pair(a1, x2, x3);
+                lane_a = (x0 + x1) + (x2 + x3);
+                unpack_pair(b0, x0, x1);
+                unpack_pair(b1, x2, x3);
+                lane_b = (x0 + x1) + (x2 + x3);
+            };
+            // Quad reduce-scatter of (lane a,row 0), (lane a,row 1), (lane b,row 0), (lane b,row 1):
+            // thread `quad` ends up with the complete head sum number `quad`.
+            const auto quad_reduce = [&](float v0, float v1, float v2, float v3) -> float {
+                const bool odd = (quad & 1) != 0;
+                const float send_a = odd ? v0 : v1;
+                const float send_b = odd ? v2 : v3;
+                const float keep_a = (odd ? v1 : v0) + __shfl_xor_sync(0xffffffffu, send_a, 1);
+                const float keep_b = (odd ? v3 : v2) + __shfl_xor_sync(0xffffffffu, send_b, 1);
+                const bool upper = (quad & 2) != 0;
+                return (upper ? keep_b : keep_a) + __shfl_xor_sync(0xffffffffu, upper ? keep_a : keep_b, 2);
+            };
+            // threshold filter and warp-level compaction of the 32 scores of one 16-lane half
+            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key) {
+                const float score = head_sum * scale;
+                const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
                 const bool key_ok = key < p.keys;
-                const float scale = key_ok ? __ldg(p.kv_scales + key) : 0.0f;
-                int range_key = key;
-                if (MODE == kModeSample) range_key = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
+                const bool in_range = key_ok && range_key >= row_lo && range_key < row_hi;
 
-                ok = timed_wait<DIAG>(&sh.acc_full[wg], acc_iter & 1, abort_flag, wait_acc);
-                if (!ok) break;
-                ++acc_iter;
-                __syncwarp();
-                tcgen05_fence_after_sync();
+                if (DIAG) {
+                    if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
+                        const bool shown = MODE == kModeSample ? true : in_range;
+                        p.diag_logits[static_cast<long long>(u.row0 + own_r) * p.diag_stride + key] =
+                            shown ? score : minus_inf;
+                    }
+                }
 
-                uint32_t ra[32], rb[32];
-                tmem_load_32(tmem_lane, ra);
-#pragma unroll
-                for (int r = 0; r < kBlockQ; ++r) {
-                    const float4* w4 = reinterpret_cast<const float4*>(&sh.weights[slot][r * kHeads]);
-                    float2 acc0 = make_float2(0.0f, 0.0f);
-                    float2 acc1 = make_float2(0.0f, 0.0f);
-                    // first half of the heads is in ra, second half is loaded into rb meanwhile
-                    tmem_load_wait(ra);
-                    tmem_load_32(tmem_lane + static_cast<uint32_t>(r * kHeads + 32), rb);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 w = w4[j];
-                        const float2 x0 = make_float2(fmaxf(__uint_as_float(ra[4 * j + 0]), 0.0f),
-                                                      fmaxf(__uint_as_float(ra[4 * j + 1]), 0.0f));
-                        const float2 x1 = make_float2(fmaxf(__uint_as_float(ra[4 * j + 2]), 0.0f),
-                                                      fmaxf(__uint_as_float(ra[4 * j + 3]), 0.0f));
-                        acc0 = fma2(x0, make_float2(w.x, w.y), acc0);
-                        acc1 = fma2(x1, make_float2(w.z, w.w), acc1);
+                if (MODE == kModeRepair) {
+                    if (row_on && key_ok && key >= u.key_lo && key < u.key_hi) {
+                        p.repair_pairs[own_slot * kRepairChunk + (key - u.key_lo)] =
+                            in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
                     }
-                    tmem_load_wait(rb);
-                    if (r + 1 < kBlockQ) {
-                        tmem_load_32(tmem_lane + static_cast<uint32_t>((r + 1) * kHeads), ra);
-                    } else {
-                        // every column of this buffer has been read: hand it back to the UMMA issuer
-                        tcgen05_fence_before_sync();
-                        mbar_arrive(&sh.acc_empty[wg]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 w = w4[8 + j];
-                        const float2 x0 = make_float2(fmaxf(__uint_as_float(rb[4 * j + 0]), 0.0f),
-                                                      fmaxf(__uint_as_float(rb[4 * j + 1]), 0.0f));
-                        const float2 x1 = make_float2(fmaxf(__uint_as_float(rb[4 * j + 2]), 0.0f),
-                                                      fmaxf(__uint_as_float(rb[4 * j + 3]), 0.0f));
-                        acc0 = fma2(x0, make_float2(w.x, w.y), acc0);
-                        acc1 = fma2(x1, make_float2(w.z, w.w), acc1);
-                    }
-                    const float score = ((acc0.x + acc0.y) + (acc1.x + acc1.y)) * scale;
-                    const bool in_range = key_ok && range_key >= row_lo[r] && range_key < row_hi[r];
-
-                    if (DIAG) {
-                        if (r < u.nrows && key_ok && p.diag_logits != nullptr) {
-                            const bool shown = MODE == kModeSample ? true : in_range;
-                            p.diag_logits[static_cast<long long>(u.row0 + r) * p.diag_stride + key] =
-                                shown ? score : minus_inf;
-                        }
-                    }
-
-                    if (MODE == kModeRepair) {
-                        if (row_on[r] && key_ok && key >= u.key_lo && key < u.key_hi) {
-                            const long long row_slot = static_cast<long long>(u.shard) * p.rows + u.row0 + r;
-                            p.repair_pairs[row_slot * kRepairChunk + (key - u.key_lo)] =
-                                in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
-                        }
-                    } else {
-                        bool active = row_on[r] && in_range;
-                        if (MODE == kModeTopK) active = active && score >= threshold[r];
-                        else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
-                        const unsigned ballot = __ballot_sync(0xffffffffu, active);
-                        const int position = count[r] + __popc(ballot & ((1u << lane) - 1u));
-                        count[r] += __popc(ballot);
-                        if (active) {
-                            if (position < kSegCap) {
-                                sh.cand_scores[slot][r][ew * kSegCap + position] = ordered_bits(score);
-                                sh.cand_ids[slot][r][ew * kSegCap + position] = encode_key(key);
-                            } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
-                                const long long row_slot = static_cast<long long>(u.shard) * p.rows + u.row0 + r;
-                                p.spill[row_slot * kSpillRow + ew * kSpillSegCap + (position - kSegCap)] =
-                                    pack_score_id(score, static_cast<uint32_t>(key));
-                            }
+                } else {
+                    bool active = row_on && in_range;
+                    if (DIAG && (p.debug_skip & 2)) active = false;
+                    if (MODE == kModeTopK) active = active && score >= threshold;
+                    else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
+                    const unsigned ballot0 = __ballot_sync(0xffffffffu, active && own_i == 0);
+                    const unsigned ballot1 = __ballot_sync(0xffffffffu, active && own_i == 1);
+                    const unsigned below = (1u << lane) - 1u;
+                    const int position = own_i == 0 ? count0 + __popc(ballot0 & below) : count1 + __popc(ballot1 & below);
+                    count0 += __popc(ballot0);
+                    count1 += __popc(ballot1);
+                    if (active) {
+                        if (position < kSegCap) {
+                            sh.cand_scores[slot][own_r][quarter * kSegCap + position] = ordered_bits(score);
+                            sh.cand_ids[slot][own_r][quarter * kSegCap + position] = encode_key(key);
+                        } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
+                            p.spill[own_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
+                                pack_score_id(score, static_cast<uint32_t>(key));
                         }
                     }
                 }
+            };
+
+            // Per tile: pull all four fragments (half 0/1 x row 0/1) out of TMEM back to back, hand
+            // the accumulator buffer to the UMMA issuer at once (it can only have two tiles in
+            // flight, so the buffer must not be held during the arithmetic), then reduce from
+            // registers.
+            uint32_t f00[32], f01[32], f10[32], f11[32];
+#if ITK_EXPERIMENT == 3
+            f00[0] = f01[1] = f10[2] = f11[3] = 0u;
+#endif
+            float scale[2], next_scale[2] = {0.0f, 0.0f};
+            int range_key[2], next_range_key[2] = {0, 0};
+            per_key(u.tile_begin, scale, range_key);
+            for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
+                const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
+                const uint32_t upper_half = 16u << 16;
+                ok = warp_wait<DIAG, true>(&sh.acc_full[acc_iter & 1], (acc_iter >> 1) & 1, abort_flag, lane, wait_acc);
+                if (!ok) break;
+                tcgen05_fence_after_sync();
+#if ITK_EXPERIMENT != 3
+                tmem_load_frag(taddr, f00);
+                tmem_load_frag(taddr + kHeads, f01);
+                tmem_load_frag(taddr + upper_half, f10);
+                tmem_load_frag(taddr + upper_half + kHeads, f11);
+#endif
+                if (t + 1 < u.tile_end) per_key(t + 1, next_scale, next_range_key);
+#if ITK_EXPERIMENT != 3
+                tmem_load_wait(f00);
+                tmem_load_wait(f01);
+                tmem_load_wait(f10);
+                tmem_load_wait(f11);
+#endif
+                tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.acc_empty[acc_iter & 1]);
+
+#if ITK_EXPERIMENT == 1 || ITK_EXPERIMENT == 3 || ITK_EXPERIMENT == 4
+                if (f00[0] == 0x7fc12345u && f01[1] == f10[2] && f11[3] == 1u) count0 += 1;
+#elif ITK_EXPERIMENT == 2
+                {
+                    float a_r0, b_r0, a_r1, b_r1, c_r0, d_r0, c_r1, d_r1;
+                    partial(f00, w0, a_r0, b_r0);
+                    partial(f01, w1, a_r1, b_r1);
+                    partial(f10, w0, c_r0, d_r0);
+                    partial(f11, w1, c_r1, d_r1);
+                    if (a_r0 + b_r0 + a_r1 + b_r1 + c_r0 + d_r0 + c_r1 + d_r1 == 1.2345e38f) count0 += 1;
+                }
+#else
+                float a_r0, b_r0, a_r1, b_r1;
+                partial(f00, w0, a_r0, b_r0);
+                partial(f01, w1, a_r1, b_r1);
+                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0]);
+                partial(f10, w0, a_r0, b_r0);
+                partial(f11, w1, a_r1, b_r1);
+                finish_half(1, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[1], range_key[1]);
+#endif
+                scale[0] = next_scale[0];
+                scale[1] = next_scale[1];
+                range_key[0] = next_range_key[0];
+                range_key[1] = next_range_key[1];
             }
             if (!ok) break;
-            if (MODE != kModeRepair) {
-                if (lane == 0) {
-#pragma unroll
-                    for (int r = 0; r < kBlockQ; ++r) sh.counts[slot][r][ew] = count[r];
-                }
-                __syncwarp();
+            __syncwarp();
+            if (lane == 0 && MODE != kModeRepair) {
+                sh.counts[slot][wg * 2 + 0][quarter] = count0;
+                sh.counts[slot][wg * 2 + 1][quarter] = count1;
                 mbar_arrive(&sh.cand_ready[slot]);
             }
-            mbar_arrive(&sh.w_empty[slot]);
             ++unit_iter;
         }
         if (DIAG && p.trace != nullptr && quarter == 0 && lane == 0) {
@@ -806,47 +1097,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             trace[kTraceEpiWaitW] = wait_w;
         }
         if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
-    } else {
-        // ============================================================ Top-K / threshold consumers
-        if (MODE != kModeRepair) {
-            const int cwarp = warp < kEpilogueWarp0 ? warp - 2 : warp - 12 + 2;   // warps 2,3,12..15 -> 0..5
-            const int ctid = cwarp * 32 + lane;
-            int unit_iter = 0;
-            bool ok = true;
-            long long wait_ready = 0, select_cycles = 0;
-            const long long role_begin = DIAG ? clock64() : 0;
-            if (DIAG && p.trace != nullptr && ctid == 0)
-                p.trace[static_cast<long long>(blockIdx.x) * kTraceFields + kTraceNsBegin] = global_timer_ns();
-            for (int iter = 0; ok; ++iter) {
-                Unit u;
-                if (!load_unit<MODE>(p, iter, u)) break;
-                const bool has_tiles = u.tile_end > u.tile_begin;
-                const int slot = unit_iter & 1;
-                if (has_tiles) {
-                    ok = timed_wait<DIAG>(&sh.cand_ready[slot], (unit_iter >> 1) & 1, abort_flag, wait_ready);
-                    if (!ok) break;
-                }
-                const long long select_begin = DIAG ? clock64() : 0;
-                for (int r = 0; r < u.nrows; ++r) {
-                    if (MODE == kModeTopK) consume_topk_row(sh, p, u, r, slot, has_tiles, ctid);
-                    else consume_sample_row(sh, p, u, r, slot, has_tiles, ctid);
-                }
-                if (DIAG) select_cycles += clock64() - select_begin;
-                if (has_tiles) {
-                    mbar_arrive(&sh.cand_free[slot]);
-                    ++unit_iter;
-                }
-            }
-            if (DIAG && p.trace != nullptr && ctid == 0) {
-                long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
-                trace[kTraceConTotal] = clock64() - role_begin;
-                trace[kTraceConWaitReady] = wait_ready;
-                trace[kTraceConSelect] = select_cycles;
-                trace[kTraceConUnits] = unit_iter;
-                trace[kTraceNsEnd] = global_timer_ns();
-            }
-            if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
-        }
     }
 
     // ---------------------------------------------------------------- teardown

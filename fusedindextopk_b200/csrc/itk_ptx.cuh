@@ -40,12 +40,33 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// One probe of the barrier.  The thread may be parked by the hardware until the phase
+// completes or the time hint (nanoseconds) runs out, whichever comes first, so a waiting
+// thread does not spend issue slots on a hot spin loop.
+constexpr uint32_t kWaitParkNs = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitParkNs)
+        : "memory");
+    return done != 0;
+}
+
+// Non-blocking probe, for waits that sit on the critical path (the wake-up from a parked
+// probe costs more than the hand-off it waits for).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
@@ -60,13 +81,14 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity.  Returns false when the limit
 // expired or another thread of the CTA already gave up (*abort_flag != 0); the
-// caller then leaves its role loop.
+// caller then leaves its role loop.  HOT = true polls without parking.
+template <bool HOT = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (HOT ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
     uint64_t deadline = 0;
     for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0u) {
+        if (HOT ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if ((spin & (HOT ? 1023u : 15u)) == 0u) {
             if (*abort_flag != 0) return false;
             const uint64_t now = global_timer_ns();
             if (deadline == 0) {
@@ -176,6 +198,23 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
 __device__ __forceinline__ void tmem_load_32(uint32_t tmem_address, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(tmem_address)
+        : "memory");
+}
+
+// 16 TMEM lanes x 64 fp32 columns in the 16x256b fragment layout: thread t of the warp gets,
+// for n = 0..7, r[4n], r[4n+1] = (lane t/4, columns 8n + 2(t%4) + {0,1}) and
+// r[4n+2], r[4n+3] = (lane t/4 + 8, same columns).  The lane field of the address selects
+// the 16-lane half inside the warp's own 32-lane quarter.
+__device__ __forceinline__ void tmem_load_frag(uint32_t tmem_address, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),

@@ -43,8 +43,8 @@ typedef struct CUstream_st* itk_stream_t;
 #define ITK_HEAD_DIM 128
 #define ITK_BLOCK_Q 4
 #define ITK_REPAIR_CHUNK 16384
-#define ITK_SPILL_U64_PER_ROW 5632      /* 8 segments x 704 entries */
-#define ITK_MAX_KEYS 524288             /* 16-bit segment-relative candidate ids */
+#define ITK_SPILL_U64_PER_ROW 5632      /* 4 segments x 1408 entries */
+#define ITK_MAX_KEYS 262144             /* 16-bit segment-relative candidate ids */
 #define ITK_MAX_PAIR_SOURCES 8
 
 /* bits of the device status word */
@@ -69,7 +69,7 @@ int itk_resource_report(char* buffer, size_t buffer_bytes);
  * `shards` key ranges.  Replaces the allocations of FusedIndexTopK.prepare
  * (src/fused_index_topk/kernel/plugin.py:202-257). */
 typedef struct itk_workspace_sizes {
-    size_t spill_bytes;            /* uint64 [shards,Q,8,704] */
+    size_t spill_bytes;            /* uint64 [shards,Q,4,1408] */
     size_t repair_pairs_bytes;     /* uint64 [shards*Q,16384] */
     size_t pairs_bytes;            /* uint64 [shards,Q,2048]: local / accumulator / output pairs, each */
     size_t counts_bytes;           /* int32  [shards,Q] */
@@ -111,13 +111,15 @@ typedef struct itk_fused_args {
     uint64_t* out_pairs;        /* optional [shards,Q,2048]: (ordered score << 32) | key */
     int32_t* out_counts;        /* optional [shards,Q], with out_pairs */
     uint8_t* failure_flags;     /* [shards,Q]: 1 = row must be repaired */
-    uint64_t* spill;            /* [shards,Q,8,704] scratch */
+    uint64_t* spill;            /* [shards,Q,4,1408] scratch */
     float* diag_logits;         /* optional fp32 [Q,diag_stride] dense scores (-inf outside the range) */
     long long diag_stride;
     long long* trace;           /* optional int64 [CTAs,32] phase trace; selects the diagnostic build.
                                  * Counterpart of the ITK_LONG_DIAGNOSTIC trace
                                  * (kernel/csrc/include/fused_index_topk/long_cta_topk.cuh:8-29) */
     int* status;                /* device status word (or-ed) */
+    int debug_skip;             /* diagnostic build only, timing experiments: 1 no selection, 2 no compaction,
+                                 * 4 no head reduction (results are then meaningless) */
     int rows;                   /* Q */
     int keys;                   /* N */
     int key_lo;                 /* first key scored (multiple of 128) */

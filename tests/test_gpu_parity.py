@@ -74,7 +74,7 @@ def _run_with_diagnostics(host, device, *, thresholds=None, repair=True):
 def test_library_loads_and_reports_resources(device):
     report = _lib.resource_report()
     assert int(report["fused_topk.registers_per_thread"]) <= 128
-    assert int(report["fused_topk.local_bytes_per_thread"]) <= 64
+    assert int(report["fused_topk.dynamic_shared_bytes"]) <= 232448
     assert int(report["sm_count"]) >= 100
 
 
