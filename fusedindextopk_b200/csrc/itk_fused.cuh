@@ -131,7 +131,11 @@ struct __align__(16) FusedShared {
     uint32_t cand_scores[2][kBlockQ][kRowCap];
     uint16_t cand_ids[2][kBlockQ][kRowCap];
     int counts[2][kBlockQ][kSegments];
-    int hist[256];
+    int hist[kConsumerWarps][256];   // one digit histogram per consumer warp
+    int warp_greater[kConsumerWarps];
+    int warp_equal[kConsumerWarps];
+    uint32_t sel_ref;
+    uint32_t sel_or;
     int sel_bin;
     int sel_greater;
     int sel_failed;
@@ -141,12 +145,11 @@ struct __align__(16) FusedShared {
     uint32_t tmem_base;
     int abort;
     uint64_t kv_full[kKvStages];
-    uint64_t kv_empty[kKvStages];
+    uint64_t tile_done[kKvStages];   // one arrival per finished tile: frees the key stage and publishes the accumulator
     uint64_t q_full;
     uint64_t q_empty;
     uint64_t w_full[2];
     uint64_t w_empty[2];
-    uint64_t acc_full[kAccBuffers];
     uint64_t acc_empty[kAccBuffers];
     uint64_t cand_ready[2];
     uint64_t cand_free[2];
@@ -262,170 +265,158 @@ __device__ __forceinline__ int warp_reserve(int* counter, bool active, int lane)
     return active ? base + __popc(mask & ((1u << lane) - 1u)) : -1;
 }
 
-// Adds one count per active lane to hist[bin]; lanes of a warp that hit the same bin
-// are combined into one shared-memory atomic.  Every lane of the warp must call.
-__device__ __forceinline__ void warp_hist_add(int* hist, bool active, uint32_t bin, int lane) {
-    const unsigned live = __ballot_sync(0xffffffffu, active);
-    if (!active) return;
-    const unsigned peers = __match_any_sync(live, bin);
-    if (lane == __ffs(static_cast<int>(peers)) - 1) atomicAdd(&hist[bin], __popc(peers));
-}
-
 // The view the consumer has of one row's candidates: counted shared-memory
 // segments plus the row's spill region in global memory.
 struct RowCandidates {
     const uint32_t* scores;   // [kRowCap]
     const uint16_t* ids;      // [kRowCap]
     const int* counts;        // [kSegments], may exceed the capacities
-    const uint64_t* spill;    // [kSegments][kSpillSegCap]
+    const uint64_t* spill;    // [kSegments][kSpillSegCap], null when the mode has no spill
 };
 
-// Spilled candidates live in global memory (L2); every consumer thread keeps up to
-// kSpillRegs of them in registers so that the selection rounds do not pay the L2
-// latency again.  Entry e of the row's spill (segments concatenated) belongs to
-// thread e % 192, register e / 192; entries beyond 192 * kSpillRegs stay in global memory.
+// Every consumer thread keeps "its" candidates of the row in registers for the whole
+// selection, so the radix rounds touch neither shared nor global memory for them:
+//   * shared-memory candidate i of a segment belongs to thread i % 192, slot i / 192
+//     (at most kSegCap / 192 rounded up = 4 slots per segment, 16 in all);
+//   * spill entry e (the segments' spill regions concatenated) belongs to thread e % 192,
+//     slot e / 192, for the first 192 * kSpillRegs entries; later ones stay in global memory
+//     and are re-read in every pass (only when a threshold is far too low).
+constexpr int kSmemSlots = (kSegCap + kConsumerThreads - 1) / kConsumerThreads;   // 4
+constexpr int kOwnSmem = kSegments * kSmemSlots;                                   // 16
 constexpr int kSpillRegs = 8;
 constexpr int kSpillCached = kSpillRegs * kConsumerThreads;
 
-struct SpillView {
-    int first[kSegments + 1];         // prefix sums of the per-segment spill counts
-    uint32_t score[kSpillRegs];
-    uint32_t key[kSpillRegs];
+struct OwnCandidates {
+    uint32_t smem_score[kOwnSmem];
+    uint32_t spill_score[kSpillRegs];
+    uint32_t spill_key[kSpillRegs];
+    uint32_t smem_live;               // bit j: smem_score[j] holds a candidate
+    uint32_t spill_live;              // bit k: spill_score[k] holds a candidate
+    int spill_first[kSegments + 1];   // prefix sums of the per-segment spill counts
 };
 
-__device__ __forceinline__ uint64_t spill_entry(const RowCandidates& c, const SpillView& v, int e) {
+__device__ __forceinline__ uint64_t spill_entry(const RowCandidates& c, const OwnCandidates& own, int e) {
     int segment = 0;
     int begin = 0;
 #pragma unroll
     for (int i = 1; i < kSegments; ++i) {
-        if (e >= v.first[i]) {
+        if (e >= own.spill_first[i]) {
             segment = i;
-            begin = v.first[i];
+            begin = own.spill_first[i];
         }
     }
     return c.spill[segment * kSpillSegCap + (e - begin)];
 }
 
-__device__ __forceinline__ void load_spill(const RowCandidates& c, SpillView& v, int ctid) {
-    v.first[0] = 0;
+__device__ __forceinline__ void load_own(const RowCandidates& c, OwnCandidates& own, int ctid) {
+    own.smem_live = 0u;
+    own.spill_live = 0u;
+    own.spill_first[0] = 0;
 #pragma unroll
     for (int s = 0; s < kSegments; ++s) {
-        const int spilled = c.spill == nullptr ? 0 : min(max(c.counts[s] - kSegCap, 0), kSpillSegCap);
-        v.first[s + 1] = v.first[s] + spilled;
+        const int count = c.counts[s];
+        const int in_smem = min(count, kSegCap);
+        const int spilled = c.spill == nullptr ? 0 : min(max(count - kSegCap, 0), kSpillSegCap);
+        own.spill_first[s + 1] = own.spill_first[s] + spilled;
+#pragma unroll
+        for (int k = 0; k < kSmemSlots; ++k) {
+            const int i = ctid + k * kConsumerThreads;
+            const bool live = i < in_smem;
+            own.smem_score[s * kSmemSlots + k] = live ? c.scores[s * kSegCap + i] : 0u;
+            own.smem_live |= live ? 1u << (s * kSmemSlots + k) : 0u;
+        }
     }
-    const int total = v.first[kSegments];
+    const int total = own.spill_first[kSegments];
 #pragma unroll
     for (int k = 0; k < kSpillRegs; ++k) {
         const int e = ctid + k * kConsumerThreads;
         uint64_t pair = 0ull;
-        if (e < total) pair = spill_entry(c, v, e);
-        v.score[k] = static_cast<uint32_t>(pair >> 32);
-        v.key[k] = static_cast<uint32_t>(pair);
+        if (e < total) {
+            pair = spill_entry(c, own, e);
+            own.spill_live |= 1u << k;
+        }
+        own.spill_score[k] = static_cast<uint32_t>(pair >> 32);
+        own.spill_key[k] = static_cast<uint32_t>(pair);
     }
 }
 
-// Calls visit(live, score) for every candidate of the row, warp-uniformly (all 32 lanes of
-// every consumer warp make every call; `live` tells whether the lane holds a candidate).
+// visit(score) for every candidate this thread owns in registers.
 template <typename Visit>
-__device__ __forceinline__ void for_each_score(const RowCandidates& c, const SpillView& v, int ctid, Visit&& visit) {
+__device__ __forceinline__ void for_own_scores(const OwnCandidates& own, Visit&& visit) {
+#pragma unroll
+    for (int j = 0; j < kOwnSmem; ++j)
+        if (own.smem_live >> j & 1u) visit(own.smem_score[j]);
+#pragma unroll
+    for (int k = 0; k < kSpillRegs; ++k)
+        if (own.spill_live >> k & 1u) visit(own.spill_score[k]);
+}
+
+// visit(pair) for the spill entries beyond the register cache, split over the threads.
+template <typename Visit>
+__device__ __forceinline__ void for_excess_spill(const RowCandidates& c, const OwnCandidates& own, int ctid,
+                                                 Visit&& visit) {
+    const int total = own.spill_first[kSegments];
+    for (int e = kSpillCached + ctid; e < total; e += kConsumerThreads) visit(spill_entry(c, own, e));
+}
+
+// Radix selection over the ordered score bits of one row, up to 8 bits per round.
+// On return `cutoff` is the rank-th largest score and `equal_needed` the number of
+// candidates equal to it that belong to the top `rank_in`.  Needs rank_in <= number of
+// candidates.  Called by all consumer threads.  The leading bits that all candidates
+// share are found first and skipped; every warp counts into its own histogram, so
+// the only contention on the shared-memory atomics is inside a warp.
+__device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own,
+                                             int ctid, int rank_in, uint32_t& cutoff, int& equal_needed) {
     const int lane = ctid & 31;
     const int cwarp = ctid >> 5;
-#pragma unroll 1
-    for (int s = 0; s < kSegments; ++s) {
-        const int in_smem = min(c.counts[s], kSegCap);
-        for (int base = cwarp * 32; base < in_smem; base += kConsumerThreads) {
-            const int i = base + lane;
-            const bool live = i < in_smem;
-            visit(live, live ? c.scores[s * kSegCap + i] : 0u);
-        }
-    }
-    const int total = v.first[kSegments];
-#pragma unroll
-    for (int k = 0; k < kSpillRegs; ++k) {
-        if (k * kConsumerThreads < total) visit(ctid + k * kConsumerThreads < total, v.score[k]);
-    }
-    for (int base = kSpillCached + cwarp * 32; base < total; base += kConsumerThreads) {
-        const int e = base + lane;
-        const bool live = e < total;
-        visit(live, live ? static_cast<uint32_t>(spill_entry(c, v, e) >> 32) : 0u);
-    }
-}
-
-// Same enumeration, also handing out the key of each candidate.
-template <typename Visit>
-__device__ __forceinline__ void for_each_pair(const RowCandidates& c, const SpillView& v, int ctid, Visit&& visit) {
-    const int lane = ctid & 31;
-    const int cwarp = ctid >> 5;
-#pragma unroll 1
-    for (int s = 0; s < kSegments; ++s) {
-        const int in_smem = min(c.counts[s], kSegCap);
-        for (int base = cwarp * 32; base < in_smem; base += kConsumerThreads) {
-            const int i = base + lane;
-            const bool live = i < in_smem;
-            visit(live, live ? c.scores[s * kSegCap + i] : 0u, live ? decode_key(c.ids[s * kSegCap + i], s) : 0);
-        }
-    }
-    const int total = v.first[kSegments];
-#pragma unroll
-    for (int k = 0; k < kSpillRegs; ++k) {
-        if (k * kConsumerThreads < total)
-            visit(ctid + k * kConsumerThreads < total, v.score[k], static_cast<int>(v.key[k]));
-    }
-    for (int base = kSpillCached + cwarp * 32; base < total; base += kConsumerThreads) {
-        const int e = base + lane;
-        const bool live = e < total;
-        const uint64_t pair = live ? spill_entry(c, v, e) : 0ull;
-        visit(live, static_cast<uint32_t>(pair >> 32), static_cast<int>(static_cast<uint32_t>(pair)));
-    }
-}
-
-// Radix selection over the ordered score bits of one row, 8 bits per round.
-// On return `prefix` is the rank-th largest score and `rank` the number of
-// candidates equal to it that belong to the top `rank_in`.  Needs
-// rank_in <= number of candidates.  Called by all consumer threads.  Leading
-// bytes that all candidates share are found first and skipped.
-__device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidates& c, const SpillView& v, int ctid,
-                                             int rank_in, uint32_t& prefix, int& rank) {
-    const int lane = ctid & 31;
-    // bits in which any two candidates differ
+    int* my_hist = sh.hist[cwarp];
     if (ctid == 0) {
-        sh.sel_bin = 0;                                   // reused as the OR of (score ^ reference)
-        sh.sel_greater = static_cast<int>(c.scores[0]);   // reference: any candidate, or 0 if the segment is empty
         int s = 0;
-        while (s < kSegments && c.counts[s] == 0) ++s;
-        if (s < kSegments) sh.sel_greater = static_cast<int>(c.scores[s * kSegCap]);
+        while (s < kSegments - 1 && c.counts[s] == 0) ++s;
+        sh.sel_ref = c.scores[s * kSegCap];   // any candidate of the row
+        sh.sel_or = 0u;
     }
     consumer_sync();
-    const uint32_t reference = static_cast<uint32_t>(sh.sel_greater);
-    uint32_t differing = 0;
-    for_each_score(c, v, ctid, [&](bool live, uint32_t score) { differing |= live ? (score ^ reference) : 0u; });
+    const uint32_t reference = sh.sel_ref;
+    uint32_t differing = 0u;
+    for_own_scores(own, [&](uint32_t score) { differing |= score ^ reference; });
+    for_excess_spill(c, own, ctid, [&](uint64_t pair) { differing |= static_cast<uint32_t>(pair >> 32) ^ reference; });
     differing = __reduce_or_sync(0xffffffffu, differing);
-    if (lane == 0 && differing != 0u) atomicOr(reinterpret_cast<unsigned*>(&sh.sel_bin), differing);
+    if (lane == 0 && differing != 0u) atomicOr(&sh.sel_or, differing);
     consumer_sync();
-    differing = static_cast<uint32_t>(sh.sel_bin);
-    consumer_sync();
-    const int shared_bytes = differing == 0u ? 4 : __clz(differing) >> 3;   // leading bytes common to all
+    differing = sh.sel_or;
 
-    uint32_t mask = shared_bytes == 0 ? 0u : 0xffffffffu << (32 - 8 * shared_bytes);
-    if (shared_bytes == 4) mask = 0xffffffffu;
-    prefix = reference & mask;
-    rank = rank_in;
+    int bits = differing == 0u ? 0 : 32 - __clz(differing);   // low bits in which candidates may differ
+    uint32_t mask = bits == 32 ? 0u : 0xffffffffu << bits;
+    uint32_t prefix = reference & mask;
+    int rank = rank_in;
 #pragma unroll 1
-    for (int shift = 24 - 8 * shared_bytes; shift >= 0; shift -= 8) {
-        for (int bin = ctid; bin < 256; bin += kConsumerThreads) sh.hist[bin] = 0;
-        consumer_sync();
-        for_each_score(c, v, ctid, [&](bool live, uint32_t score) {
-            warp_hist_add(sh.hist, live && (score & mask) == prefix, (score >> shift) & 255u, lane);
+    while (bits > 0) {
+        const int width = min(8, bits);
+        const int shift = bits - width;
+        const uint32_t digit_mask = (1u << width) - 1u;
+        for (int bin = lane; bin < 256; bin += 32) my_hist[bin] = 0;
+        __syncwarp();
+        for_own_scores(own, [&](uint32_t score) {
+            if ((score & mask) == prefix) atomicAdd(&my_hist[(score >> shift) & digit_mask], 1);
+        });
+        for_excess_spill(c, own, ctid, [&](uint64_t pair) {
+            const uint32_t score = static_cast<uint32_t>(pair >> 32);
+            if ((score & mask) == prefix) atomicAdd(&my_hist[(score >> shift) & digit_mask], 1);
         });
         consumer_sync();
         if (ctid < 32) {
-            // lane l owns bins 8l .. 8l+7; `above` = candidates in bins owned by higher lanes
+            // lane l owns bins 8l .. 8l+7 (summed over the warps' histograms); `above` =
+            // candidates in bins owned by higher lanes
             int bins[8];
             int mine = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                bins[j] = sh.hist[ctid * 8 + j];
-                mine += bins[j];
+                int sum = 0;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) sum += sh.hist[w][ctid * 8 + j];
+                bins[j] = sum;
+                mine += sum;
             }
             int suffix = mine;
 #pragma unroll
@@ -447,31 +438,85 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
         consumer_sync();
         prefix |= static_cast<uint32_t>(sh.sel_bin) << shift;
         rank -= sh.sel_greater;
-        mask |= 0xffu << shift;
+        mask |= digit_mask << shift;
+        bits = shift;
     }
+    cutoff = prefix;
+    equal_needed = rank;
 }
 
 // Writes the selected candidates of one row: everything above `cutoff`, then
-// `equal_needed` of the candidates equal to it (any of them).  With
-// take_all = true every candidate is written.
-__device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, const SpillView& v, int ctid,
+// `equal_needed` of the candidates equal to it (any of them); with take_all every
+// candidate.  Two passes without atomics: per-warp totals first, then each warp writes
+// behind the totals of the warps before it, lanes ordered by ballot.
+__device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own, int ctid,
                                          uint32_t cutoff, int equal_needed, int greater_total, bool take_all,
                                          int32_t* out_ids, uint64_t* out_pairs) {
     const int lane = ctid & 31;
-    for_each_pair(c, v, ctid, [&](bool live, uint32_t score, int key) {
-        const bool greater = live && (take_all || score > cutoff);
-        const bool equal = live && !take_all && score == cutoff;
-        const int g = warp_reserve(&sh.sel_gcount, greater, lane);
-        const int e = warp_reserve(&sh.sel_ecount, equal, lane);
+    const int cwarp = ctid >> 5;
+    const int total_spill = own.spill_first[kSegments];
+    int greater = 0, equal = 0;
+    const auto tally = [&](uint32_t score) {
+        greater += (take_all || score > cutoff) ? 1 : 0;
+        equal += (!take_all && score == cutoff) ? 1 : 0;
+    };
+    for_own_scores(own, tally);
+    for_excess_spill(c, own, ctid, [&](uint64_t pair) { tally(static_cast<uint32_t>(pair >> 32)); });
+    greater = __reduce_add_sync(0xffffffffu, greater);
+    equal = __reduce_add_sync(0xffffffffu, equal);
+    if (lane == 0) {
+        sh.warp_greater[cwarp] = greater;
+        sh.warp_equal[cwarp] = equal;
+    }
+    consumer_sync();
+    int next_greater = 0, next_equal = 0;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+        next_greater += w < cwarp ? sh.warp_greater[w] : 0;
+        next_equal += w < cwarp ? sh.warp_equal[w] : 0;
+    }
+    const unsigned below = (1u << lane) - 1u;
+    const auto place = [&](bool live, uint32_t score) -> int {
+        const bool is_greater = live && (take_all || score > cutoff);
+        const bool is_equal = live && !take_all && score == cutoff;
+        const unsigned ballot_g = __ballot_sync(0xffffffffu, is_greater);
+        const unsigned ballot_e = __ballot_sync(0xffffffffu, is_equal);
         int position = -1;
-        if (greater) position = g;
-        else if (equal && e < equal_needed) position = greater_total + e;
-        if (position >= 0 && position < kTopK) {
-            if (out_ids != nullptr) out_ids[position] = key;
-            if (out_pairs != nullptr)
-                out_pairs[position] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
+        if (is_greater) {
+            position = next_greater + __popc(ballot_g & below);
+        } else if (is_equal) {
+            const int e = next_equal + __popc(ballot_e & below);
+            if (e < equal_needed) position = greater_total + e;
         }
-    });
+        next_greater += __popc(ballot_g);
+        next_equal += __popc(ballot_e);
+        return position < kTopK ? position : -1;
+    };
+    const auto write = [&](int position, uint32_t score, int key) {
+        if (out_ids != nullptr) out_ids[position] = key;
+        if (out_pairs != nullptr) out_pairs[position] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
+    };
+#pragma unroll
+    for (int j = 0; j < kOwnSmem; ++j) {
+        const int s = j / kSmemSlots;
+        const int i = ctid + (j % kSmemSlots) * kConsumerThreads;
+        const int position = place((own.smem_live >> j & 1u) != 0u, own.smem_score[j]);
+        if (position >= 0) write(position, own.smem_score[j], decode_key(c.ids[s * kSegCap + i], s));
+    }
+#pragma unroll
+    for (int k = 0; k < kSpillRegs; ++k) {
+        if (k * kConsumerThreads < total_spill) {
+            const int position = place((own.spill_live >> k & 1u) != 0u, own.spill_score[k]);
+            if (position >= 0) write(position, own.spill_score[k], static_cast<int>(own.spill_key[k]));
+        }
+    }
+    for (int base = kSpillCached + cwarp * 32; base < total_spill; base += kConsumerThreads) {
+        const int e = base + lane;
+        const bool live = e < total_spill;
+        const uint64_t pair = live ? spill_entry(c, own, e) : 0ull;
+        const int position = place(live, static_cast<uint32_t>(pair >> 32));
+        if (position >= 0) write(position, static_cast<uint32_t>(pair >> 32), static_cast<int>(static_cast<uint32_t>(pair)));
+    }
 }
 
 // Exact Top-2048 of one row from its candidates (kModeTopK consumer).
@@ -538,14 +583,14 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
         consumer_sync();
         return;
     }
-    SpillView view;
+    OwnCandidates view;
     long long stamp = phase != nullptr ? clock64() : 0;
-    load_spill(c, view, ctid);
+    load_own(c, view, ctid);
     if (phase != nullptr) {
-        // the cached spill entries are only complete once their loads have returned
+        // the cached entries are only complete once their loads have returned
         uint32_t touch = 0;
 #pragma unroll
-        for (int k = 0; k < kSpillRegs; ++k) touch |= view.score[k];
+        for (int k = 0; k < kSpillRegs; ++k) touch |= view.spill_score[k];
         if (touch == 0x80000001u) phase[3] += 1;
         const long long now = clock64();
         phase[0] += now - stamp;
@@ -611,8 +656,8 @@ __device__ __forceinline__ void consume_sample_row(FusedShared& sh, const FusedP
         consumer_sync();
         return;
     }
-    SpillView view;
-    load_spill(c, view, ctid);
+    OwnCandidates view;
+    load_own(c, view, ctid);
     uint32_t cutoff;
     int unused;
     radix_select(sh, c, view, ctid, p.sample_rank, cutoff, unused);
@@ -651,7 +696,9 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 template <int MODE, bool DIAG>
 __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_constant__ FusedParams p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Align by pointer arithmetic on the shared array (not through an integer cast) so that the
+    // compiler keeps the shared address space: LDS/STS/ATOMS instead of generic accesses.
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* smem_q = smem;
     uint8_t* smem_kv = smem + kQBytes;
     FusedShared& sh = *reinterpret_cast<FusedShared*>(smem + kSmemTileBytes);
@@ -663,14 +710,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     if (threadIdx.x == 0) {
         for (int i = 0; i < kKvStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
-            mbar_init(&sh.kv_empty[i], 1);
+            mbar_init(&sh.tile_done[i], 1);
         }
         mbar_init(&sh.q_full, 1);
         mbar_init(&sh.q_empty, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.w_full[i], 1);
             mbar_init(&sh.w_empty[i], kEpilogueWarps);
-            mbar_init(&sh.acc_full[i], 1);
             mbar_init(&sh.acc_empty[i], kEpilogueWarps);
             mbar_init(&sh.cand_ready[i], kEpilogueWarps);
             mbar_init(&sh.cand_free[i], 1);
@@ -717,7 +763,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                           &sh.w_full[ws]);
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
                     const int stage = kv_iter % kKvStages;
-                    ok = timed_wait<DIAG>(&sh.kv_empty[stage], ((kv_iter / kKvStages) & 1) ^ 1, abort_flag, wait_kv);
+                    ok = timed_wait<DIAG>(&sh.tile_done[stage], ((kv_iter / kKvStages) & 1) ^ 1, abort_flag, wait_kv);
                     if (!ok) break;
 #if ITK_EXPERIMENT == 4
                     mbar_arrive(&sh.kv_full[stage]);
@@ -757,23 +803,38 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 if (u.tile_end == u.tile_begin) continue;
                 ok = timed_wait<DIAG>(&sh.q_full, q_iter & 1, abort_flag, wait_q);
                 if (!ok) break;
+                // The tensor pipe accepts only a couple of UMMAs ahead of the one it executes, so
+                // every cycle this thread spends between two batches of issues is a bubble.  The
+                // barriers of tile t+1 are therefore probed while the UMMAs of tile t execute
+                // (a probe takes less time than one UMMA); the blocking waits at the top are
+                // normally satisfied already.
+                bool acc_ready = false, kv_ready = false;
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
                     const int buffer = kv_iter & 1;
                     const int stage = kv_iter % kKvStages;
-                    ok = timed_wait<DIAG, true>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
-                    if (!ok) break;
-                    ok = timed_wait<DIAG, true>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
-                    if (!ok) break;
+                    if (!acc_ready) {
+                        ok = timed_wait<DIAG, true>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
+                        if (!ok) break;
+                    }
+                    if (!kv_ready) {
+                        ok = timed_wait<DIAG, true>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
+                        if (!ok) break;
+                    }
                     tcgen05_fence_after_sync();
                     const uint64_t desc_kv = umma_desc_sw128_kmajor(smem_u32(smem_kv + stage * kKvBytes));
                     const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buffer * kUmmaN);
-#pragma unroll
-                    for (int k = 0; k < kHeadDim / 32; ++k) {
-                        // advance both operands by 32 bytes (= 2 descriptor address units) per K step
-                        umma_f8(tmem_d, desc_kv + 2 * k, desc_q + 2 * k, idesc, k > 0 ? 1u : 0u);
-                    }
-                    umma_commit(&sh.kv_empty[stage]);
-                    umma_commit(&sh.acc_full[buffer]);
+                    const int next = kv_iter + 1;
+                    const bool more = t + 1 < u.tile_end;
+                    // advance both operands by 32 bytes (= 2 descriptor address units) per K step
+                    umma_f8(tmem_d, desc_kv, desc_q, idesc, 0u);
+                    acc_ready = more && mbar_test_wait(&sh.acc_empty[next & 1], ((next >> 1) & 1) ^ 1);
+                    umma_f8(tmem_d, desc_kv + 2, desc_q + 2, idesc, 1u);
+                    kv_ready = more && mbar_test_wait(&sh.kv_full[next % kKvStages], (next / kKvStages) & 1);
+                    umma_f8(tmem_d, desc_kv + 4, desc_q + 4, idesc, 1u);
+                    if (more && !acc_ready) acc_ready = mbar_test_wait(&sh.acc_empty[next & 1], ((next >> 1) & 1) ^ 1);
+                    umma_f8(tmem_d, desc_kv + 6, desc_q + 6, idesc, 1u);
+                    // a single commit per tile frees the key stage and publishes the accumulator
+                    umma_commit(&sh.tile_done[stage]);
                 }
                 if (!ok) break;
                 umma_commit(&sh.q_empty);
@@ -871,7 +932,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
-        long long wait_acc = 0, wait_free = 0, wait_w = 0;
+        long long wait_acc = 0, wait_free = 0, wait_w = 0, cyc_drain = 0, cyc_release = 0;
         const long long role_begin = DIAG ? clock64() : 0;
         for (int iter = 0; ok; ++iter) {
             Unit u;
@@ -1035,9 +1096,12 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
                 const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
                 const uint32_t upper_half = 16u << 16;
-                ok = warp_wait<DIAG, true>(&sh.acc_full[acc_iter & 1], (acc_iter >> 1) & 1, abort_flag, lane, wait_acc);
+                ok = warp_wait<DIAG, true>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, lane, wait_acc);
                 if (!ok) break;
+                const long long stamp_a = DIAG ? clock64() : 0;
+#if ITK_EXPERIMENT != 5
                 tcgen05_fence_after_sync();
+#endif
 #if ITK_EXPERIMENT != 3
                 tmem_load_frag(taddr, f00);
                 tmem_load_frag(taddr + kHeads, f01);
@@ -1051,11 +1115,19 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 tmem_load_wait(f10);
                 tmem_load_wait(f11);
 #endif
+                const long long stamp_b = DIAG ? clock64() : 0;
+#if ITK_EXPERIMENT != 5
                 tcgen05_fence_before_sync();
+#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh.acc_empty[acc_iter & 1]);
+                const long long stamp_c = DIAG ? clock64() : 0;
+                if (DIAG) {
+                    cyc_drain += stamp_b - stamp_a;
+                    cyc_release += stamp_c - stamp_b;
+                }
 
-#if ITK_EXPERIMENT == 1 || ITK_EXPERIMENT == 3 || ITK_EXPERIMENT == 4
+#if ITK_EXPERIMENT == 1 || ITK_EXPERIMENT == 3 || ITK_EXPERIMENT == 4 || ITK_EXPERIMENT == 5
                 if (f00[0] == 0x7fc12345u && f01[1] == f10[2] && f11[3] == 1u) count0 += 1;
 #elif ITK_EXPERIMENT == 2
                 {
@@ -1095,6 +1167,10 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             trace[kTraceEpiWaitAcc] = wait_acc;
             trace[kTraceEpiWaitFree] = wait_free;
             trace[kTraceEpiWaitW] = wait_w;
+            if (wg == 0) {
+                trace[5] = cyc_drain;     // TMEM fragment loads until landed
+                trace[6] = cyc_release;   // fence + warp sync + arrive
+            }
         }
         if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
     }
