@@ -77,7 +77,7 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
         except OSError:
@@ -91,7 +91,15 @@ class ClockSampler:
         for line in self.process.stdout:
             self.lines.append(line.strip())
 
-    def stop(self) -> dict:
+    def wait_first_sample(self, seconds: float = 3.0) -> None:
+        deadline = time.time() + seconds
+        while self.process is not None and not self.lines and time.time() < deadline:
+            time.sleep(0.01)
+
+    def mark(self) -> int:
+        return len(self.lines)
+
+    def stop(self, begin: int = 0, end: int | None = None) -> dict:
         if self.process is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.process.terminate()
@@ -101,7 +109,17 @@ class ClockSampler:
             self.process.kill()
         clocks, maxima, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = "timed steps"
+        chosen = self.lines[begin:end]
+        if len(chosen) < 3:
+            # the timed steps were shorter than a few sampling periods: use every sample taken
+            # while the GPU was under the same load (timed steps and the end-to-end loop)
+            chosen = self.lines[begin:]
+            window = "timed steps + end-to-end loop"
+        if len(chosen) < 3:
+            chosen = self.lines
+            window = "whole run under load (warm-up included)"
+        for line in chosen:
             parts = [item.strip() for item in line.split(",")]
             if len(parts) < 8:
                 continue
@@ -117,6 +135,7 @@ class ClockSampler:
             "sm_mhz": statistics.median(clocks) if clocks else None,
             "sm_max_mhz": max(maxima) if maxima else None,
             "samples": len(clocks),
+            "window": window,
             "reasons": sorted(reasons),
         }
 
@@ -148,27 +167,6 @@ def cpu_reference_time(host, sample_rows: int, threads: int) -> dict:
     }
 
 
-def shard_rows(host, rank: int, world: int):
-    """Inputs of the query blocks (4 rows each) owned by `rank`: blocks rank, rank+world, ..."""
-
-    import torch
-    from dataclasses import replace
-
-    if world == 1:
-        return host, torch.arange(host.case.query_tokens)
-    rows = host.case.query_tokens
-    blocks = torch.arange((rows + 3) // 4)
-    mine = blocks[rank::world]
-    row_ids = (mine[:, None] * 4 + torch.arange(4)[None, :]).flatten()
-    row_ids = row_ids[row_ids < rows]
-    case = replace(host.case, query_tokens=int(row_ids.numel()))
-    local = replace(
-        host, case=case, q=host.q[row_ids].contiguous(), weights=host.weights[row_ids].contiguous(),
-        k_start=host.k_start[row_ids].contiguous(), k_end=host.k_end[row_ids].contiguous(),
-    )
-    return local, row_ids
-
-
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -191,6 +189,7 @@ def main() -> None:
 
     import torch
 
+    from fusedindextopk_b200.distributed import shard_rows
     from fusedindextopk_b200.inputs import WORKLOADS, inputs_to, make_workload_inputs
 
     workload = WORKLOADS[args.workload]
@@ -242,15 +241,26 @@ def main() -> None:
 
     from fusedindextopk_b200 import operator
 
+    from fusedindextopk_b200 import distributed as shards
+
     host_full = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys)
-    host, row_ids = shard_rows(host_full, rank, world)
+    key_mode = args.workload == "c3s" and world > 1
+    key_offset = 0
+    if key_mode:
+        # short-Q long-context: shard the key range, all-gather the per-rank Top-2048 pairs, merge
+        host, key_offset = shards.shard_keys(host_full, rank, world)
+        config["partitioning"] = (f"key range cut into {world} slices of whole 128-key tiles, per-rank exact "
+                                  "Top-2048 pairs all-gathered over NCCL and merged on every rank")
+    else:
+        host, _ = shard_rows(host_full, rank, world)
     rows, keys = host.case.query_tokens, host.case.context_tokens
     gpu = inputs_to(host, device)
     tensors = (gpu.q, gpu.kv, gpu.kv_scales, gpu.weights, gpu.k_start, gpu.k_end)
-    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed)
+    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed, with_pairs=key_mode)
+    merged_ids = torch.empty((rows, 2048), dtype=torch.int32, device=device) if key_mode else None
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     chunks = (keys + 16383) // 16384
-    launches_per_step = (2 if ws.plan.enabled else 0) + 1 + 1 + 3 * chunks + 1
+    launches_per_step = (2 if ws.plan.enabled else 0) + 1 + 1 + 3 * chunks + 1 + (1 if key_mode else 0)
 
     def barrier() -> None:
         if distributed:
@@ -265,9 +275,13 @@ def main() -> None:
             ev[0].record()
             operator.run_sample_thresholds(ws, *tensors)
             ev[1].record()
-            operator.run_fused_topk(ws, *tensors)
+            operator.run_fused_topk(ws, *tensors, want_pairs=key_mode)
             ev[2].record()
-            operator.run_repair(ws, *tensors)
+            operator.run_repair(ws, *tensors, want_pairs=key_mode)
+            if key_mode:
+                gathered_pairs = shards.dist_all_gather(ws.output_pairs + key_offset)
+                gathered_counts = shards.dist_all_gather(ws.output_counts)
+                shards.gpu_merge(gathered_pairs, gathered_counts, merged_ids)
             ev[3].record()
         torch.cuda.synchronize()
         for ev in events:
@@ -275,23 +289,26 @@ def main() -> None:
             fused_ms += ev[1].elapsed_time(ev[2])
         return total_ms, fused_ms
 
-    barrier()
-    timed_steps(max(args.warmup, 3))
-    ws.check_status()
-    flagged_fast = None
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_first_sample()
+    barrier()
+    timed_steps(max(args.warmup, 3))
+    ws.check_status()
+    barrier()
+    mark_begin = sampler.mark()
     total_ms, fused_ms = timed_steps(args.steps)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    mark_end = sampler.mark()
     ws.check_status()
     unrepaired = int(ws.failure_flags.sum().item())
 
     # ------------------------------------------------------------------ end to end from pinned host memory
     e2e_ms = 0.0
     h2d_bytes = d2h_bytes = 0
+    if key_mode:
+        args.no_e2e = True
     if not args.no_e2e:
         from fusedindextopk_b200 import fused_index_topk
 
@@ -321,6 +338,7 @@ def main() -> None:
             e2e_ms += begin.elapsed_time(end)
         barrier()
 
+    clocks = sampler.stop(mark_begin, mark_end) if rank == 0 else None
     if distributed:
         stats = torch.tensor([total_ms, fused_ms, e2e_ms, float(unrepaired)], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
@@ -333,8 +351,8 @@ def main() -> None:
     us_per_call = total_ms * 1e3 / args.steps
     fused_us = fused_ms * 1e3 / args.steps
     total_rows = host_full.case.query_tokens
-    flops_total = algorithmic_flops(host_full.k_end.tolist())          # k_start == 0
-    flops_rank = algorithmic_flops(host.k_end.tolist())                # the slowest rank's launch
+    flops_total = algorithmic_flops((host_full.k_end - host_full.k_start).tolist())
+    flops_rank = algorithmic_flops((host.k_end - host.k_start).tolist())   # this rank's fused launch
     peak, peak_source = fp8_peak_tflops()
     achieved = flops_rank / (fused_us * 1e-6) / 1e12
     line = {
