@@ -25,13 +25,14 @@ REPAIR_CHUNK = 16384
 SPILL_U64_PER_ROW = 5632
 MAX_KEYS = 262144
 MAX_PAIR_SOURCES = 8
+STATIC_MAX_ROWS = 256
 STATUS_WAIT_EXPIRED = 1
 
 EXPORTED_SYMBOLS = (
     "itk_version", "itk_last_error", "itk_init", "itk_resource_report", "itk_workspace_bytes",
     "itk_gather_sampled_kv", "itk_sample_thresholds", "itk_fused_topk", "itk_update_chunk_ranges",
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
-    "itk_merge_candidate_lists",
+    "itk_merge_candidate_lists", "itk_fused_topk_static",
 )
 
 
@@ -85,6 +86,7 @@ def load_library() -> ctypes.CDLL:
         [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p]
     )
     library.itk_fused_topk.argtypes = [POINTER(FusedArgs), c_void_p]
+    library.itk_fused_topk_static.argtypes = [POINTER(FusedArgs), c_void_p]
     library.itk_update_chunk_ranges.argtypes = [c_void_p] * 4 + [c_int, c_int, c_void_p]
     library.itk_repair_produce.argtypes = [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_void_p]
     library.itk_chunk_local_topk.argtypes = [c_void_p] * 7 + [c_int, c_int, c_void_p]

@@ -469,3 +469,46 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- no-allocation variant
+
+namespace {
+
+constexpr int kStaticMaxRows = ITK_STATIC_MAX_ROWS;
+
+// Spill scratch of the no-allocation entry point: part of the library image, one copy per
+// device context.  In host code this name is only a handle; the kernel must be given the
+// device address that cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) unsigned long long g_static_spill[static_cast<size_t>(kStaticMaxRows) * itk::kSpillRow];
+
+std::mutex g_static_mutex;
+uint64_t* g_static_spill_address[kMaxDevices] = {};
+
+}  // namespace
+
+extern "C" int itk_fused_topk_static(const itk_fused_args* args, itk_stream_t stream) {
+    ITK_REQUIRE(args != nullptr, "args must not be null");
+    ITK_REQUIRE(args->spill == nullptr, "the no-allocation variant owns its spill; pass spill = null");
+    ITK_REQUIRE(args->rows > 0 && args->rows <= kStaticMaxRows,
+                "the no-allocation variant handles at most %d query rows per call (got %d); split the call by rows",
+                kStaticMaxRows, args->rows);
+    ITK_REQUIRE(args->shards == 1, "the no-allocation variant does not offer key-range shards");
+    int device = 0;
+    ITK_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(ITK_ERR_UNSUPPORTED, "device index %d out of range", device);
+    uint64_t* spill = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (g_static_spill_address[device] == nullptr) {
+            // once per device, with that device current: resolve the symbol to a device address
+            void* address = nullptr;
+            ITK_CUDA(cudaGetSymbolAddress(&address, g_static_spill));
+            if (address == nullptr) return fail(ITK_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+            g_static_spill_address[device] = static_cast<uint64_t*>(address);
+        }
+        spill = g_static_spill_address[device];
+    }
+    itk_fused_args with_spill = *args;
+    with_spill.spill = spill;
+    return itk_fused_topk(&with_spill, stream);
+}

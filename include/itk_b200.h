@@ -177,6 +177,33 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
+/* The fused kernel for callers that must not allocate device memory.
+ *
+ * Some hosts of this operator cannot call cudaMalloc at the point where they run it:
+ * an inference engine that has handed the whole device to its own pool allocator and
+ * forbids foreign allocations, a plugin loaded into a process whose memory budget is
+ * fixed at start-up, or code running inside a region where allocation would
+ * synchronise the device.  itk_fused_topk needs one scratch buffer from its caller
+ * (the bounded overflow spill, 45056 bytes per query row); this variant takes the
+ * spill from an array that is part of the library image instead, so the caller passes
+ * only inputs, thresholds and outputs.  It has no counterpart in the reference, whose
+ * host bindings always receive the spill workspace from the Python plugin.
+ *
+ * Limits and rules:
+ *  - at most ITK_STATIC_MAX_ROWS query rows per call (larger problems are rejected with
+ *    ITK_ERR_ARGUMENT; split them by rows); args->spill must be null;
+ *    key-range shards (shards > 1) are not offered here;
+ *  - the array (ITK_STATIC_MAX_ROWS * 45056 bytes = 11 MiB) lives in every device
+ *    context that loads the library, until the process exits;
+ *  - the first call on a device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *  - every call on a device shares the one array: two calls that overlap on the GPU
+ *    (different streams, or graphs replayed concurrently) race on it and must be
+ *    serialised by the caller.  Nothing in it needs to start at zero: a row's spill is
+ *    only read up to the counts the same launch wrote. */
+#define ITK_STATIC_MAX_ROWS 256
+int itk_fused_topk_static(const itk_fused_args* args, itk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
