@@ -83,7 +83,7 @@ def load_library() -> ctypes.CDLL:
     library.itk_workspace_bytes.argtypes = [c_int, c_int, c_int, POINTER(WorkspaceSizes)]
     library.itk_gather_sampled_kv.argtypes = [c_void_p] * 5 + [c_int, c_int, c_void_p]
     library.itk_sample_thresholds.argtypes = (
-        [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p]
+        [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]
     )
     library.itk_fused_topk.argtypes = [POINTER(FusedArgs), c_void_p]
     library.itk_fused_topk_static.argtypes = [POINTER(FusedArgs), c_void_p]

@@ -225,7 +225,8 @@ int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t*
 int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,
                           const int32_t* sample_ids, const int32_t* k_start, const int32_t* k_end,
                           float* thresholds, int rows, int samples, int sample_rank, int target_candidates,
-                          float* diag_logits, long long diag_stride, int* status, itk_stream_t stream) {
+                          float* diag_logits, long long diag_stride, long long* trace, int* status,
+                          itk_stream_t stream) {
     ITK_REQUIRE(q && sampled_kv && sampled_scales && weights && sample_ids && k_start && k_end && thresholds && status,
                 "sample threshold pointers must not be null");
     ITK_REQUIRE(rows > 0 && samples > 0, "need rows > 0 and samples > 0");
@@ -249,6 +250,7 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
     params.sample_ids = sample_ids;
     params.diag_logits = diag_logits;
     params.diag_stride = diag_stride;
+    params.trace = trace;
     params.status = status;
     params.rows = rows;
     params.keys = samples;
@@ -262,7 +264,8 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
     params.sample_rank = sample_rank;
     params.target_candidates = target_candidates;
     params.top_k_min_valid = kTopK;
-    return launch_fused<kModeSample>(params, diag_logits != nullptr, fused_grid(device, params.num_blocks, 0), stream);
+    return launch_fused<kModeSample>(params, diag_logits != nullptr || trace != nullptr,
+                                     fused_grid(device, params.num_blocks, 0), stream);
 }
 
 int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {

@@ -623,46 +623,90 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
 }
 
 // Threshold of one row = rank-th largest valid sampled score (kModeSample consumer).
-__device__ __forceinline__ void consume_sample_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                   int slot, bool has_tiles, int ctid) {
+// One warp per row, no block-level synchronisation: the warp walks the row's candidates in
+// shared memory once per score bit (most significant differing bit first), counts the
+// candidates that agree with the prefix found so far and have the bit set, and keeps or
+// clears the bit so that exactly rank-1 candidates stay above the prefix.
+__device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
+                                                     int slot, bool has_tiles, int lane) {
     const int row = u.row0 + r;
     const int start = __ldg(p.k_start + row);
     const int end = __ldg(p.k_end + row);
     const float minus_inf = __int_as_float(0xff800000);
-    if (!has_tiles || end - start <= p.target_candidates) {
-        if (ctid == 0) p.thresholds_out[row] = minus_inf;
-        return;
-    }
-    RowCandidates c;
-    c.scores = sh.cand_scores[slot][r];
-    c.ids = sh.cand_ids[slot][r];
-    c.counts = sh.counts[slot][r];
-    c.spill = nullptr;
-    if (ctid == 0) {
+    float result = minus_inf;
+    if (has_tiles && end - start > p.target_candidates) {
+        const uint32_t* scores = sh.cand_scores[slot][r];
+        const int* counts = sh.counts[slot][r];
         int total = 0;
-        int overflow = 0;
-        for (int s = 0; s < kSegments; ++s) {
-            total += c.counts[s];
-            overflow |= c.counts[s] > kSegCap;
+        bool overflow = false;
+        uint32_t reference = 0u;
+#pragma unroll
+        for (int s = kSegments - 1; s >= 0; --s) {
+            total += counts[s];
+            overflow = overflow || counts[s] > kSegCap;
+            if (counts[s] > 0) reference = scores[s * kSegCap];
         }
-        sh.sel_total = total;
-        sh.sel_failed = overflow;
+        if (!overflow && total >= p.sample_rank) {
+            // candidate g of the row (segments concatenated) belongs to lane g % 32; the first
+            // kCached of a lane's candidates live in registers, the rest is re-read from shared
+            // memory four at a time (a single warp is latency-bound, so loads must overlap)
+            constexpr int kCached = 16;
+            const int first1 = counts[0], first2 = first1 + counts[1], first3 = first2 + counts[2];
+            const auto fetch = [&](int g) -> uint32_t {
+                int segment = 0, begin = 0;
+                if (g >= first1) { segment = 1; begin = first1; }
+                if (g >= first2) { segment = 2; begin = first2; }
+                if (g >= first3) { segment = 3; begin = first3; }
+                return scores[segment * kSegCap + (g - begin)];
+            };
+            uint32_t own[kCached];
+            uint32_t live = 0u;
+#pragma unroll
+            for (int m = 0; m < kCached; ++m) {
+                const int g = lane + 32 * m;
+                own[m] = g < total ? fetch(g) : 0u;
+                live |= g < total ? 1u << m : 0u;
+            }
+            const auto for_rest = [&](auto&& visit) {
+#pragma unroll 1
+                for (int g = lane + 32 * kCached; g < total; g += 128) {
+                    uint32_t x[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) x[k] = g + 32 * k < total ? fetch(g + 32 * k) : 0u;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) visit(g + 32 * k < total, x[k]);
+                }
+            };
+            uint32_t differing = 0u;
+#pragma unroll
+            for (int m = 0; m < kCached; ++m) differing |= (live >> m & 1u) ? own[m] ^ reference : 0u;
+            for_rest([&](bool valid, uint32_t score) { differing |= valid ? score ^ reference : 0u; });
+            differing = __reduce_or_sync(0xffffffffu, differing);
+            const int bits = differing == 0u ? 0 : 32 - __clz(differing);
+            uint32_t mask = bits == 32 ? 0u : 0xffffffffu << bits;
+            uint32_t prefix = reference & mask;
+            int rank = p.sample_rank;
+#pragma unroll 1
+            for (int bit = bits - 1; bit >= 0; --bit) {
+                const uint32_t probe = 1u << bit;
+                const uint32_t want = prefix | probe;       // agrees with the prefix and has the bit set
+                const uint32_t care = mask | probe;
+                int above = 0;
+#pragma unroll
+                for (int m = 0; m < kCached; ++m)
+                    above += static_cast<int>(live >> m & 1u) & static_cast<int>((own[m] & care) == want);
+                for_rest([&](bool valid, uint32_t score) {
+                    above += static_cast<int>(valid) & static_cast<int>((score & care) == want);
+                });
+                above = __reduce_add_sync(0xffffffffu, above);
+                if (above >= rank) prefix |= probe;   // the rank-th largest has this bit set
+                else rank -= above;                   // it lies among the candidates with the bit clear
+                mask |= probe;
+            }
+            result = ordered_to_float(prefix);
+        }
     }
-    consumer_sync();
-    const int total = sh.sel_total;
-    const bool overflow = sh.sel_failed != 0;
-    if (overflow || total < p.sample_rank) {
-        if (ctid == 0) p.thresholds_out[row] = minus_inf;
-        consumer_sync();
-        return;
-    }
-    OwnCandidates view;
-    load_own(c, view, ctid);
-    uint32_t cutoff;
-    int unused;
-    radix_select(sh, c, view, ctid, p.sample_rank, cutoff, unused);
-    if (ctid == 0) p.thresholds_out[row] = ordered_to_float(cutoff);
-    consumer_sync();
+    if (lane == 0) p.thresholds_out[row] = result;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -882,10 +926,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     if (!ok) break;
                 }
                 const long long select_begin = DIAG ? clock64() : 0;
-                for (int r = 0; r < u.nrows; ++r) {
-                    if (DIAG && (p.debug_skip & 1)) continue;
-                    if (MODE == kModeTopK) consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
-                    else consume_sample_row(sh, p, u, r, slot, has_tiles, ctid);
+                if (MODE == kModeTopK) {
+                    for (int r = 0; r < u.nrows; ++r) {
+                        if (DIAG && (p.debug_skip & 1)) continue;
+                        consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
+                    }
+                } else if (cwarp < u.nrows) {
+                    sample_threshold_row(sh, p, u, cwarp, slot, has_tiles, lane);   // one warp per row
                 }
                 if (DIAG) select_cycles += clock64() - select_begin;
                 if (has_tiles) {

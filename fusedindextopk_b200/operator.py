@@ -174,7 +174,8 @@ def make_workspace(
 # --------------------------------------------------------------------------- stages
 
 
-def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None) -> Any:
+def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None,
+                          trace=None) -> Any:
     """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph."""
 
     import torch
@@ -193,7 +194,7 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
         ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
         ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
         plan.target_candidates, ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
-        ptr(ws.status), stream,
+        ptr(trace), ptr(ws.status), stream,
     ))
     return ws.thresholds
 

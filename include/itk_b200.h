@@ -91,11 +91,13 @@ int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t*
  * -inf when k_end-k_start <= target_candidates or fewer than sample_rank samples are
  * valid.  Replaces deep_gemm.fp8_mqa_logits on the sample (kernel/plugin.py:272-282)
  * followed by threshold_out (sampling_threshold.cu:236-292).  diag_logits (optional,
- * fp32 [Q,diag_stride]) receives the dense sampled scores. */
+ * fp32 [Q,diag_stride]) receives the dense sampled scores; trace (optional, int64 [CTAs,32])
+ * the per-CTA phase trace.  Either selects the diagnostic build. */
 int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,
                           const int32_t* sample_ids, const int32_t* k_start, const int32_t* k_end,
                           float* thresholds, int rows, int samples, int sample_rank, int target_candidates,
-                          float* diag_logits, long long diag_stride, int* status, itk_stream_t stream);
+                          float* diag_logits, long long diag_stride, long long* trace, int* status,
+                          itk_stream_t stream);
 
 /* Arguments of the fused kernel.  Replaces fp8_mqa_topk_out
  * (kernel/csrc/long_fused_bindings.cpp:100-184). */
