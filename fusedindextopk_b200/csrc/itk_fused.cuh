@@ -40,7 +40,7 @@
 
 // Build-time experiment switch for timing studies (0 in every shipped build):
 //   1 = epilogue only drains TMEM and hands the buffer back, 2 = drain + head reduction, no filtering,
-//   3 = like 1 without even reading TMEM, 4 = like 1 and the key tiles are not fetched (stale shared memory).
+//   6 = everything but the Top-K selection of the consumer warps.
 #ifndef ITK_EXPERIMENT
 #define ITK_EXPERIMENT 0
 #endif
@@ -68,8 +68,8 @@ constexpr int kThreads = 512;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kEpilogueThreads = 256;
 constexpr int kEpilogueWarps = kEpilogueThreads / 32;
-constexpr int kEpilogueRegisters = 192;        // per-thread budget of the two epilogue warpgroups
-constexpr int kOtherRegisters = 64;            // ... and of the producer / issuer / consumer warpgroups
+constexpr int kEpilogueRegisters = 144;        // per-thread budget of the two epilogue warpgroups
+constexpr int kOtherRegisters = 112;            // ... and of the producer / issuer / consumer warpgroups
 static_assert(256 * kEpilogueRegisters + 256 * kOtherRegisters <= 65536, "register pool of one SM");
 constexpr int kConsumerThreads = 192;
 constexpr int kConsumerWarps = kConsumerThreads / 32;
@@ -929,6 +929,9 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 if (MODE == kModeTopK) {
                     for (int r = 0; r < u.nrows; ++r) {
                         if (DIAG && (p.debug_skip & 1)) continue;
+#if ITK_EXPERIMENT == 6
+                        continue;
+#endif
                         consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
                     }
                 } else if (cwarp < u.nrows) {
@@ -979,7 +982,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
-        long long wait_acc = 0, wait_free = 0, wait_w = 0, cyc_drain = 0, cyc_release = 0;
+        long long wait_acc = 0, wait_free = 0, wait_w = 0;
         const long long role_begin = DIAG ? clock64() : 0;
         for (int iter = 0; ok; ++iter) {
             Unit u;
@@ -1086,113 +1089,117 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const bool upper = (quad & 2) != 0;
                 return (upper ? keep_b : keep_a) + __shfl_xor_sync(0xffffffffu, upper ? keep_a : keep_b, 2);
             };
-            // threshold filter and warp-level compaction of the 32 scores of one 16-lane half
-            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key) {
+            // threshold filter and warp-level compaction of the 32 scores of one 16-lane half.
+            // Even lanes finish row 2g, odd lanes row 2g+1, so one ballot serves both rows.
+            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key, bool interior) {
                 const float score = head_sum * scale;
                 const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
-                const bool key_ok = key < p.keys;
-                const bool in_range = key_ok && range_key >= row_lo && range_key < row_hi;
-
-                if (DIAG) {
-                    if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
-                        const bool shown = MODE == kModeSample ? true : in_range;
-                        p.diag_logits[static_cast<long long>(u.row0 + own_r) * p.diag_stride + key] =
-                            shown ? score : minus_inf;
-                    }
-                }
-
-                if (MODE == kModeRepair) {
-                    if (row_on && key_ok && key >= u.key_lo && key < u.key_hi) {
-                        p.repair_pairs[own_slot * kRepairChunk + (key - u.key_lo)] =
-                            in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
-                    }
+                bool active;
+                if (MODE == kModeTopK && !DIAG && interior) {
+                    // the whole tile lies inside the row's key range: only the threshold decides
+                    active = row_on && score >= threshold;
                 } else {
-                    bool active = row_on && in_range;
+                    const bool key_ok = key < p.keys;
+                    const bool in_range = key_ok && range_key >= row_lo && range_key < row_hi;
+                    if (DIAG) {
+                        if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
+                            const bool shown = MODE == kModeSample ? true : in_range;
+                            p.diag_logits[static_cast<long long>(u.row0 + own_r) * p.diag_stride + key] =
+                                shown ? score : minus_inf;
+                        }
+                    }
+                    if (MODE == kModeRepair) {
+                        if (row_on && key_ok && key >= u.key_lo && key < u.key_hi) {
+                            p.repair_pairs[own_slot * kRepairChunk + (key - u.key_lo)] =
+                                in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
+                        }
+                        return;
+                    }
+                    active = row_on && in_range;
                     if (DIAG && (p.debug_skip & 2)) active = false;
                     if (MODE == kModeTopK) active = active && score >= threshold;
                     else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
-                    const unsigned ballot0 = __ballot_sync(0xffffffffu, active && own_i == 0);
-                    const unsigned ballot1 = __ballot_sync(0xffffffffu, active && own_i == 1);
-                    const unsigned below = (1u << lane) - 1u;
-                    const int position = own_i == 0 ? count0 + __popc(ballot0 & below) : count1 + __popc(ballot1 & below);
-                    count0 += __popc(ballot0);
-                    count1 += __popc(ballot1);
-                    if (active) {
-                        if (position < kSegCap) {
-                            sh.cand_scores[slot][own_r][quarter * kSegCap + position] = ordered_bits(score);
-                            sh.cand_ids[slot][own_r][quarter * kSegCap + position] = encode_key(key);
-                        } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
-                            p.spill[own_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
-                                pack_score_id(score, static_cast<uint32_t>(key));
-                        }
+                }
+                const unsigned ballot = __ballot_sync(0xffffffffu, active);
+                const unsigned even = ballot & 0x55555555u;
+                const unsigned odd = ballot & 0xaaaaaaaau;
+                const unsigned below = (1u << lane) - 1u;
+                const int position = own_i == 0 ? count0 + __popc(even & below) : count1 + __popc(odd & below);
+                count0 += __popc(even);
+                count1 += __popc(odd);
+                if (active) {
+                    if (position < kSegCap) {
+                        sh.cand_scores[slot][own_r][quarter * kSegCap + position] = ordered_bits(score);
+                        sh.cand_ids[slot][own_r][quarter * kSegCap + position] = encode_key(key);
+                    } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
+                        p.spill[own_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
+                            pack_score_id(score, static_cast<uint32_t>(key));
                     }
                 }
             };
 
-            // Per tile: pull all four fragments (half 0/1 x row 0/1) out of TMEM back to back, hand
-            // the accumulator buffer to the UMMA issuer at once (it can only have two tiles in
-            // flight, so the buffer must not be held during the arithmetic), then reduce from
-            // registers.
-            uint32_t f00[32], f01[32], f10[32], f11[32];
-#if ITK_EXPERIMENT == 3
-            f00[0] = f01[1] = f10[2] = f11[3] = 0u;
-#endif
+            // Software pipeline over the four fragment loads of a tile, (half 0,row 0), (half 0,row 1),
+            // (half 1,row 0), (half 1,row 1): while one fragment is reduced on the CUDA cores the
+            // next is on its way out of TMEM (TMEM read bandwidth, about 350 cycles per tile, hides
+            // under the arithmetic).  The accumulator buffer goes back to the UMMA issuer as soon
+            // as the fourth fragment has landed; the first fragment of the next tile is requested
+            // before the last filter step so that its latency is covered too.
+            uint32_t fx[32], fy[32];
             float scale[2], next_scale[2] = {0.0f, 0.0f};
             int range_key[2], next_range_key[2] = {0, 0};
             per_key(u.tile_begin, scale, range_key);
+            ok = warp_wait<DIAG, true>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, lane, wait_acc);
+            if (!ok) break;
+            tcgen05_fence_after_sync();
+            tmem_load_frag(tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN), fx);
             for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
                 const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
                 const uint32_t upper_half = 16u << 16;
-                ok = warp_wait<DIAG, true>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, lane, wait_acc);
-                if (!ok) break;
-                const long long stamp_a = DIAG ? clock64() : 0;
-#if ITK_EXPERIMENT != 5
-                tcgen05_fence_after_sync();
+                const bool more = t + 1 < u.tile_end;
+                const bool interior = t * kTileKeys >= row_lo && (t + 1) * kTileKeys <= row_hi;
+                if (more) per_key(t + 1, next_scale, next_range_key);
+                float a_r0, b_r0, a_r1, b_r1, c_r0, d_r0, c_r1, d_r1;
+
+                tmem_load_wait(fx);                                   // (half 0, row 0)
+                tmem_load_frag(taddr + kHeads, fy);
+#if ITK_EXPERIMENT != 1
+                partial(fx, w0, a_r0, b_r0);
 #endif
-#if ITK_EXPERIMENT != 3
-                tmem_load_frag(taddr, f00);
-                tmem_load_frag(taddr + kHeads, f01);
-                tmem_load_frag(taddr + upper_half, f10);
-                tmem_load_frag(taddr + upper_half + kHeads, f11);
+                tmem_load_wait(fy);                                   // (half 0, row 1)
+                tmem_load_frag(taddr + upper_half, fx);
+#if ITK_EXPERIMENT != 1
+                partial(fy, w1, a_r1, b_r1);
 #endif
-                if (t + 1 < u.tile_end) per_key(t + 1, next_scale, next_range_key);
-#if ITK_EXPERIMENT != 3
-                tmem_load_wait(f00);
-                tmem_load_wait(f01);
-                tmem_load_wait(f10);
-                tmem_load_wait(f11);
+                tmem_load_wait(fx);                                   // (half 1, row 0)
+                tmem_load_frag(taddr + upper_half + kHeads, fy);
+#if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
+                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0], interior);
+#elif ITK_EXPERIMENT == 2
+                if (a_r0 + a_r1 + b_r0 + b_r1 == 1.2345e38f) count0 += 1;
 #endif
-                const long long stamp_b = DIAG ? clock64() : 0;
-#if ITK_EXPERIMENT != 5
+#if ITK_EXPERIMENT != 1
+                partial(fx, w0, c_r0, d_r0);
+#endif
+                tmem_load_wait(fy);                                   // (half 1, row 1): buffer fully read
                 tcgen05_fence_before_sync();
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh.acc_empty[acc_iter & 1]);
-                const long long stamp_c = DIAG ? clock64() : 0;
-                if (DIAG) {
-                    cyc_drain += stamp_b - stamp_a;
-                    cyc_release += stamp_c - stamp_b;
-                }
-
-#if ITK_EXPERIMENT == 1 || ITK_EXPERIMENT == 3 || ITK_EXPERIMENT == 4 || ITK_EXPERIMENT == 5
-                if (f00[0] == 0x7fc12345u && f01[1] == f10[2] && f11[3] == 1u) count0 += 1;
-#elif ITK_EXPERIMENT == 2
-                {
-                    float a_r0, b_r0, a_r1, b_r1, c_r0, d_r0, c_r1, d_r1;
-                    partial(f00, w0, a_r0, b_r0);
-                    partial(f01, w1, a_r1, b_r1);
-                    partial(f10, w0, c_r0, d_r0);
-                    partial(f11, w1, c_r1, d_r1);
-                    if (a_r0 + b_r0 + a_r1 + b_r1 + c_r0 + d_r0 + c_r1 + d_r1 == 1.2345e38f) count0 += 1;
-                }
+#if ITK_EXPERIMENT != 1
+                partial(fy, w1, c_r1, d_r1);
 #else
-                float a_r0, b_r0, a_r1, b_r1;
-                partial(f00, w0, a_r0, b_r0);
-                partial(f01, w1, a_r1, b_r1);
-                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0]);
-                partial(f10, w0, a_r0, b_r0);
-                partial(f11, w1, a_r1, b_r1);
-                finish_half(1, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[1], range_key[1]);
+                if (fx[0] == 0x7fc12345u && fy[1] == 7u) count0 += 1;
+#endif
+                if (more) {
+                    const int next = acc_iter + 1;
+                    ok = warp_wait<DIAG, true>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, lane, wait_acc);
+                    if (!ok) break;
+                    tcgen05_fence_after_sync();
+                    tmem_load_frag(tmem_lane + static_cast<uint32_t>((next & 1) * kUmmaN), fx);
+                }
+#if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
+                finish_half(1, t, quad_reduce(c_r0, c_r1, d_r0, d_r1), scale[1], range_key[1], interior);
+#elif ITK_EXPERIMENT == 2
+                if (c_r0 + c_r1 + d_r0 + d_r1 == 1.2345e38f) count0 += 1;
 #endif
                 scale[0] = next_scale[0];
                 scale[1] = next_scale[1];
@@ -1214,10 +1221,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             trace[kTraceEpiWaitAcc] = wait_acc;
             trace[kTraceEpiWaitFree] = wait_free;
             trace[kTraceEpiWaitW] = wait_w;
-            if (wg == 0) {
-                trace[5] = cyc_drain;     // TMEM fragment loads until landed
-                trace[6] = cyc_release;   // fence + warp sync + arrive
-            }
         }
         if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
     }
