@@ -737,6 +737,31 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
     return ok != 0;
 }
 
+// The whole warp polls the barrier (one warp-wide probe per iteration, no parking, no
+// lane-0 branch and broadcast): for the per-tile waits on the critical path.  Bounded like mbar_wait.
+template <bool DIAG>
+__device__ __forceinline__ bool warp_hot_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              long long& cycles) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long begin = DIAG ? clock64() : 0;
+    uint64_t deadline = 0;
+    bool ok = true;
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_test_wait(bar, parity)) break;
+        if ((spin & 4095u) == 0u) {
+            const uint64_t now = global_timer_ns();
+            if (deadline == 0) deadline = now + kWaitLimitNs;
+            if (*abort_flag != 0 || now > deadline) {
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+        }
+    }
+    if (DIAG) cycles += clock64() - begin;
+    return __all_sync(0xffffffffu, ok);
+}
+
 template <int MODE, bool DIAG>
 __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_constant__ FusedParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -1024,7 +1049,18 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     }
                 }
             }
-            int count0 = 0, count1 = 0;   // candidates of row 2g / 2g+1 in this warp's segment (warp-uniform)
+            // Candidate compaction: even lanes finish row 2g, odd lanes row 2g+1, so one ballot per
+            // 16-lane half serves both rows and every thread keeps the running count of its own row.
+            const unsigned row_mask = own_i == 0 ? 0x55555555u : 0xaaaaaaaau;
+            const unsigned row_below = row_mask & ((1u << lane) - 1u);
+            const uint32_t score_slots = smem_u32(&sh.cand_scores[slot][own_r][quarter * kSegCap]);
+            const uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
+            int own_count = 0;
+            // tiles [interior_lo, interior_hi) lie inside the row's key range: there the threshold alone
+            // decides (a NaN threshold rejects everything for rows that are switched off)
+            const int interior_lo = (row_lo + kTileKeys - 1) / kTileKeys;
+            const int interior_hi = row_hi / kTileKeys;
+            const float pass_threshold = row_on ? threshold : __int_as_float(0x7fc00000);
 
             // head weights of this thread's column pairs, both rows
             uint64_t w0[8], w1[8];
@@ -1091,13 +1127,12 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             };
             // threshold filter and warp-level compaction of the 32 scores of one 16-lane half.
             // Even lanes finish row 2g, odd lanes row 2g+1, so one ballot serves both rows.
-            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key, bool interior) {
+            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key) {
                 const float score = head_sum * scale;
                 const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
                 bool active;
-                if (MODE == kModeTopK && !DIAG && interior) {
-                    // the whole tile lies inside the row's key range: only the threshold decides
-                    active = row_on && score >= threshold;
+                if (MODE == kModeTopK && !DIAG && t >= interior_lo && t < interior_hi) {
+                    active = score >= pass_threshold;
                 } else {
                     const bool key_ok = key < p.keys;
                     const bool in_range = key_ok && range_key >= row_lo && range_key < row_hi;
@@ -1121,16 +1156,14 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
                 }
                 const unsigned ballot = __ballot_sync(0xffffffffu, active);
-                const unsigned even = ballot & 0x55555555u;
-                const unsigned odd = ballot & 0xaaaaaaaau;
-                const unsigned below = (1u << lane) - 1u;
-                const int position = own_i == 0 ? count0 + __popc(even & below) : count1 + __popc(odd & below);
-                count0 += __popc(even);
-                count1 += __popc(odd);
+                const int position = own_count + __popc(ballot & row_below);
+                own_count += __popc(ballot & row_mask);
                 if (active) {
                     if (position < kSegCap) {
-                        sh.cand_scores[slot][own_r][quarter * kSegCap + position] = ordered_bits(score);
-                        sh.cand_ids[slot][own_r][quarter * kSegCap + position] = encode_key(key);
+                        st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
+                        // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
+                        st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position),
+                                      static_cast<uint32_t>(t * 32 + h * 16 + own_lane));
                     } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
                         p.spill[own_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
                             pack_score_id(score, static_cast<uint32_t>(key));
@@ -1148,7 +1181,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             float scale[2], next_scale[2] = {0.0f, 0.0f};
             int range_key[2], next_range_key[2] = {0, 0};
             per_key(u.tile_begin, scale, range_key);
-            ok = warp_wait<DIAG, true>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, lane, wait_acc);
+            ok = warp_hot_wait<DIAG>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, wait_acc);
             if (!ok) break;
             tcgen05_fence_after_sync();
             tmem_load_frag(tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN), fx);
@@ -1156,7 +1189,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
                 const uint32_t upper_half = 16u << 16;
                 const bool more = t + 1 < u.tile_end;
-                const bool interior = t * kTileKeys >= row_lo && (t + 1) * kTileKeys <= row_hi;
                 if (more) per_key(t + 1, next_scale, next_range_key);
                 float a_r0, b_r0, a_r1, b_r1, c_r0, d_r0, c_r1, d_r1;
 
@@ -1173,9 +1205,9 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 tmem_load_wait(fx);                                   // (half 1, row 0)
                 tmem_load_frag(taddr + upper_half + kHeads, fy);
 #if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
-                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0], interior);
+                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0]);
 #elif ITK_EXPERIMENT == 2
-                if (a_r0 + a_r1 + b_r0 + b_r1 == 1.2345e38f) count0 += 1;
+                if (a_r0 + a_r1 + b_r0 + b_r1 == 1.2345e38f) own_count += 1;
 #endif
 #if ITK_EXPERIMENT != 1
                 partial(fx, w0, c_r0, d_r0);
@@ -1187,19 +1219,19 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
 #if ITK_EXPERIMENT != 1
                 partial(fy, w1, c_r1, d_r1);
 #else
-                if (fx[0] == 0x7fc12345u && fy[1] == 7u) count0 += 1;
+                if (fx[0] == 0x7fc12345u && fy[1] == 7u) own_count += 1;
 #endif
                 if (more) {
                     const int next = acc_iter + 1;
-                    ok = warp_wait<DIAG, true>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, lane, wait_acc);
+                    ok = warp_hot_wait<DIAG>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, wait_acc);
                     if (!ok) break;
                     tcgen05_fence_after_sync();
                     tmem_load_frag(tmem_lane + static_cast<uint32_t>((next & 1) * kUmmaN), fx);
                 }
 #if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
-                finish_half(1, t, quad_reduce(c_r0, c_r1, d_r0, d_r1), scale[1], range_key[1], interior);
+                finish_half(1, t, quad_reduce(c_r0, c_r1, d_r0, d_r1), scale[1], range_key[1]);
 #elif ITK_EXPERIMENT == 2
-                if (c_r0 + c_r1 + d_r0 + d_r1 == 1.2345e38f) count0 += 1;
+                if (c_r0 + c_r1 + d_r0 + d_r1 == 1.2345e38f) own_count += 1;
 #endif
                 scale[0] = next_scale[0];
                 scale[1] = next_scale[1];
@@ -1208,10 +1240,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) break;
             __syncwarp();
-            if (lane == 0 && MODE != kModeRepair) {
-                sh.counts[slot][wg * 2 + 0][quarter] = count0;
-                sh.counts[slot][wg * 2 + 1][quarter] = count1;
-                mbar_arrive(&sh.cand_ready[slot]);
+            if (MODE != kModeRepair) {
+                // lane 0 finishes row 2g, lane 1 row 2g+1: their running counts are the segment sizes
+                if (lane < 2) sh.counts[slot][own_r][quarter] = own_count;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh.cand_ready[slot]);
             }
             ++unit_iter;
         }

@@ -101,6 +101,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Stores through a 32-bit shared-memory address (no generic address arithmetic).
+__device__ __forceinline__ void st_shared_u32(uint32_t address, uint32_t value) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_u16(uint32_t address, uint32_t value) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(address), "h"(static_cast<uint16_t>(value)) : "memory");
+}
+
 // ------------------------------------------------------------------ TMA
 
 // Tiled 2-D load of one box into this CTA's shared memory; completion is
@@ -258,13 +267,15 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
 // non-negatives get the sign bit set.  Larger score <=> larger integer.
 __host__ __device__ __forceinline__ uint32_t ordered_bits(float value) {
 #ifdef __CUDA_ARCH__
-    uint32_t bits = __float_as_uint(value);
+    // adding +0 turns -0 into +0 and leaves every other value alone; the sign then selects the flip mask
+    const uint32_t bits = __float_as_uint(value + 0.0f);
+    return bits ^ (static_cast<uint32_t>(static_cast<int32_t>(bits) >> 31) | 0x80000000u);
 #else
     uint32_t bits;
     memcpy(&bits, &value, sizeof(bits));
-#endif
     if ((bits & 0x7fffffffu) == 0u) bits = 0u;
     return (bits & 0x80000000u) ? ~bits : (bits ^ 0x80000000u);
+#endif
 }
 
 __host__ __device__ __forceinline__ float ordered_to_float(uint32_t ordered) {
