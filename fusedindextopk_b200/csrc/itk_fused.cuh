@@ -1196,11 +1196,15 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 tmem_load_frag(taddr + kHeads, fy);
 #if ITK_EXPERIMENT != 1
                 partial(fx, w0, a_r0, b_r0);
+#else
+                if (fx[3] == 0x7fc12345u) own_count += 1;
 #endif
                 tmem_load_wait(fy);                                   // (half 0, row 1)
                 tmem_load_frag(taddr + upper_half, fx);
 #if ITK_EXPERIMENT != 1
                 partial(fy, w1, a_r1, b_r1);
+#else
+                if (fy[3] == 0x7fc12345u) own_count += 1;
 #endif
                 tmem_load_wait(fx);                                   // (half 1, row 0)
                 tmem_load_frag(taddr + upper_half + kHeads, fy);
@@ -1211,6 +1215,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
 #endif
 #if ITK_EXPERIMENT != 1
                 partial(fx, w0, c_r0, d_r0);
+#else
+                if (fx[3] == 0x7fc12345u) own_count += 1;
 #endif
                 tmem_load_wait(fy);                                   // (half 1, row 1): buffer fully read
                 tcgen05_fence_before_sync();
