@@ -45,6 +45,22 @@
 #define ITK_EXPERIMENT 0
 #endif
 
+// Heartbeat builds (-DITK_HEARTBEAT, diagnostic kernels only): lane 0 of every warp records the last
+// point it reached in trace[32 + warp], so that a host thread can read a stuck kernel's state from
+// mapped host memory.
+#ifdef ITK_HEARTBEAT
+#define ITK_BEAT(code)                                                                                        \
+    do {                                                                                                      \
+        if (DIAG && p.trace != nullptr && lane == 0)                                                          \
+            *reinterpret_cast<volatile long long*>(p.trace + static_cast<long long>(blockIdx.x) * kTraceFields + \
+                                                   32 + warp) = (code);                                        \
+    } while (0)
+#else
+#define ITK_BEAT(code) do { } while (0)
+#endif
+
+#include <type_traits>
+
 namespace itk {
 
 constexpr int kHeads = 64;
@@ -64,13 +80,14 @@ constexpr int kSpillSegCap = 1408;             // global spill entries per (row,
 constexpr int kSpillRow = kSegments * kSpillSegCap;  // 5632 u64 per row
 constexpr int kRepairChunk = 16384;
 
-constexpr int kThreads = 512;
+// Warps 0-3: TMA producer, UMMA issuer, two consumer warps; warps 4-19: epilogue; warps 20-23: consumers.
+constexpr int kThreads = 768;
 constexpr int kEpilogueWarp0 = 4;
-constexpr int kEpilogueThreads = 256;
+constexpr int kEpilogueThreads = 512;
 constexpr int kEpilogueWarps = kEpilogueThreads / 32;
-constexpr int kEpilogueRegisters = 144;        // per-thread budget of the two epilogue warpgroups
-constexpr int kOtherRegisters = 112;            // ... and of the producer / issuer / consumer warpgroups
-static_assert(256 * kEpilogueRegisters + 256 * kOtherRegisters <= 65536, "register pool of one SM");
+// 65536 / 768 rounded down to the allocation unit of 8 gives every thread 80 registers.  The pool that
+// setmaxnreg redistributes is what the CTA got at launch (768 x 80), not the whole register file, and
+// no split in units of 8 per warpgroup suits both the epilogue and the consumers, so the budget is uniform.
 constexpr int kConsumerThreads = 192;
 constexpr int kConsumerWarps = kConsumerThreads / 32;
 
@@ -84,7 +101,11 @@ constexpr int kModeRepair = 2;
 constexpr int kStatusWaitExpired = 1;
 
 // Per-CTA phase trace of diagnostic builds (clock64 cycles unless noted).
+#ifdef ITK_HEARTBEAT
+constexpr int kTraceFields = 64;
+#else
 constexpr int kTraceFields = 32;
+#endif
 constexpr int kTraceMmaTotal = 0, kTraceMmaWaitAcc = 1, kTraceMmaWaitKv = 2, kTraceMmaWaitQ = 3, kTraceMmaTiles = 4;
 constexpr int kTraceTmaTotal = 8, kTraceTmaWaitKv = 9, kTraceTmaWaitQ = 10;
 constexpr int kTraceEpiTotal = 12, kTraceEpiWaitAcc = 13, kTraceEpiWaitFree = 14, kTraceEpiWaitW = 15;  // +4 for warpgroup 1
@@ -161,16 +182,16 @@ static_assert(kFusedSmemBytes <= 232448, "fused kernel exceeds the 227 KB shared
 static_assert(kSegCap % 32 == 0 && kSpillSegCap % 32 == 0, "segment capacities are warp multiples");
 
 // mbar_wait that adds the cycles it took to `cycles` in diagnostic builds.
-template <bool DIAG, bool HOT = false>
+template <bool DIAG, uint32_t PARK_NS = kWaitParkNs>
 __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                            long long& cycles) {
     if (DIAG) {
         const long long begin = clock64();
-        const bool ok = mbar_wait<HOT>(bar, parity, abort_flag);
+        const bool ok = mbar_wait<PARK_NS>(bar, parity, abort_flag);
         cycles += clock64() - begin;
         return ok;
     }
-    return mbar_wait<HOT>(bar, parity, abort_flag);
+    return mbar_wait<PARK_NS>(bar, parity, abort_flag);
 }
 
 // ------------------------------------------------------------------ work units
@@ -283,7 +304,7 @@ struct RowCandidates {
 //     and are re-read in every pass (only when a threshold is far too low).
 constexpr int kSmemSlots = (kSegCap + kConsumerThreads - 1) / kConsumerThreads;   // 4
 constexpr int kOwnSmem = kSegments * kSmemSlots;                                   // 16
-constexpr int kSpillRegs = 8;
+constexpr int kSpillRegs = 4;
 constexpr int kSpillCached = kSpillRegs * kConsumerThreads;
 
 struct OwnCandidates {
@@ -727,31 +748,126 @@ __device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c)
     return d;
 }
 
+// ------------------------------------------------------------------ epilogue helpers
+
+// What the epilogue needs to know about one query row of a unit.
+struct RowState {
+    int lo, hi;          // key range of the row inside the unit's key slice
+    float threshold;
+    bool on;             // the row takes part in this launch
+    long long slot;      // row index in the per-shard arrays (thresholds, spill, repair pairs)
+};
+
+template <int MODE>
+__device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row0, int nrows, int shard,
+                                                   int unit_key_lo, int unit_key_hi, int r) {
+    RowState state{0, 0, __int_as_float(0xff800000), r < nrows, 0};
+    if (state.on) {
+        const int row = row0 + r;
+        state.slot = static_cast<long long>(shard) * p.rows + row;
+        const int start = __ldg(p.k_start + row);
+        const int end = __ldg(p.k_end + row);
+        if (MODE == kModeSample) {
+            state.lo = start;
+            state.hi = end;
+            state.on = end - start > p.target_candidates;
+        } else {
+            state.lo = max(start, unit_key_lo);
+            state.hi = min(min(end, p.keys), unit_key_hi);
+            if (MODE == kModeTopK) {
+                const int valid = state.hi - state.lo;
+                if (valid > kTopK) state.threshold = __ldg(p.thresholds + state.slot);
+                state.on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
+            } else {
+                state.on = p.failure_flags[state.slot] != 0;
+            }
+        }
+    }
+    return state;
+}
+
+// Filter decision for a tile that is not known to lie inside the row's key range (first and last
+// tiles of a row, every tile of the sample and repair modes, diagnostic builds).  Kept out of line so
+// that the interior-tile path of the epilogue stays a handful of instructions; the row parameters are
+// re-read here instead of living in registers across the tile loop.  Repair mode stores the dense
+// pair and returns false.
+template <int MODE, bool DIAG>
+__device__ __noinline__ bool boundary_filter(const FusedParams& p, int row0, int nrows, int shard, int unit_key_lo,
+                                             int unit_key_hi, int r, int key, int range_key, float score) {
+    const RowState row = load_row_state<MODE>(p, row0, nrows, shard, unit_key_lo, unit_key_hi, r);
+    const bool key_ok = key < p.keys;
+    const bool in_range = key_ok && range_key >= row.lo && range_key < row.hi;
+    if (DIAG) {
+        if (r < nrows && key_ok && p.diag_logits != nullptr) {
+            const bool shown = MODE == kModeSample ? true : in_range;
+            p.diag_logits[static_cast<long long>(row0 + r) * p.diag_stride + key] =
+                shown ? score : __int_as_float(0xff800000);
+        }
+    }
+    if (MODE == kModeRepair) {
+        if (row.on && key_ok && key >= unit_key_lo && key < unit_key_hi) {
+            p.repair_pairs[row.slot * kRepairChunk + (key - unit_key_lo)] =
+                in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
+        }
+        return false;
+    }
+    bool active = row.on && in_range;
+    if (DIAG && (p.debug_skip & 2)) active = false;
+    if (MODE == kModeTopK) active = active && score >= row.threshold;
+    else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
+    return active;
+}
+
+// Candidate stores of a tile whose candidates do not all fit the shared-memory segment any more:
+// positions below the capacity still go to shared memory, the next kSpillSegCap to the global spill.
+__device__ __noinline__ void store_with_overflow(const FusedParams& p, long long row_slot, int quarter, bool active,
+                                                 int position, float score, int key, uint32_t score_slots,
+                                                 uint32_t id_slots, uint32_t id) {
+    if (!active) return;
+    if (position < kSegCap) {
+        st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
+        st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), id);
+    } else if (p.spill != nullptr && position < kSegCap + kSpillSegCap) {
+        p.spill[row_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
+            pack_score_id(score, static_cast<uint32_t>(key));
+    }
+}
+
 // Lane 0 waits on the barrier, the warp then reconverges: one poller per warp.
-template <bool DIAG, bool HOT = false>
+template <bool DIAG, uint32_t PARK_NS = kWaitParkNs>
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane,
                                           long long& cycles) {
     int ok = 1;
-    if (lane == 0) ok = timed_wait<DIAG, HOT>(bar, parity, abort_flag, cycles) ? 1 : 0;
+    if (lane == 0) ok = timed_wait<DIAG, PARK_NS>(bar, parity, abort_flag, cycles) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     return ok != 0;
 }
 
-// The whole warp polls the barrier (one warp-wide probe per iteration, no parking, no
-// lane-0 branch and broadcast): for the per-tile waits on the critical path.  Bounded like mbar_wait.
+// Per-tile wait of an epilogue warp.  The whole warp probes the barrier (no lane-0 branch and
+// broadcast).  A first probe that fails parks the warp in the hardware for a short time: with four
+// epilogue warps per scheduler the issue slots are the scarce resource, so a waiting warp must not
+// spin.  Lanes of one probe can disagree when the phase completes while the probe is in flight, so
+// every decision is taken by a warp vote and the warp leaves only when all of its lanes have seen
+// the phase.  Bounded like mbar_wait.
+constexpr uint32_t kTileParkNs = 2000;
+// The UMMA issuer usually waits for the epilogue (an accumulator buffer to come back).  It shares its
+// scheduler with four epilogue warps, so it parks between probes instead of spinning; the park is short
+// because the hand-off it waits for is one tile (a microsecond or so) away.
+constexpr uint32_t kIssuerParkNs = 200;
+
 template <bool DIAG>
-__device__ __forceinline__ bool warp_hot_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                              long long& cycles) {
-    if (mbar_test_wait(bar, parity)) return true;
+__device__ __forceinline__ bool warp_tile_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               long long& cycles) {
+    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
     const long long begin = DIAG ? clock64() : 0;
     uint64_t deadline = 0;
     bool ok = true;
     for (uint32_t spin = 1;; ++spin) {
-        if (mbar_test_wait(bar, parity)) break;
-        if ((spin & 4095u) == 0u) {
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity, kTileParkNs))) break;
+        if ((spin & 63u) == 0u) {
             const uint64_t now = global_timer_ns();
             if (deadline == 0) deadline = now + kWaitLimitNs;
-            if (*abort_flag != 0 || now > deadline) {
+            if (__any_sync(0xffffffffu, *abort_flag != 0 || now > deadline)) {
                 *abort_flag = 1;
                 ok = false;
                 break;
@@ -759,7 +875,7 @@ __device__ __forceinline__ bool warp_hot_wait(uint64_t* bar, uint32_t parity, vo
         }
     }
     if (DIAG) cycles += clock64() - begin;
-    return __all_sync(0xffffffffu, ok);
+    return ok;
 }
 
 template <int MODE, bool DIAG>
@@ -803,11 +919,10 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = sh.tmem_base;
+    ITK_BEAT(2);
 
     const bool is_epilogue = warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + kEpilogueWarps;
     if (!is_epilogue) {
-    // Register budget per warpgroup: producer / issuer / consumer warpgroups give registers back ...
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegisters));
     if (warp == 0) {
         // ============================================================ TMA producer
         if (lane == 0) {
@@ -823,6 +938,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 if (!ok) break;
                 mbar_arrive_expect_tx(&sh.q_full, kQBytes);
                 tma_load_2d(smem_q, &p.map_q, &sh.q_full, 0, u.block * kUmmaN);
+                ITK_BEAT(10);
                 const int ws = q_iter & 1;
                 ok = timed_wait<DIAG>(&sh.w_empty[ws], ((q_iter >> 1) & 1) ^ 1, abort_flag, wait_q);
                 if (!ok) break;
@@ -840,6 +956,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     mbar_arrive_expect_tx(&sh.kv_full[stage], kKvBytes);
                     tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0, t * kTileKeys);
 #endif
+                    ITK_BEAT(100 + kv_iter);
                 }
                 ++q_iter;
             }
@@ -872,6 +989,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 if (u.tile_end == u.tile_begin) continue;
                 ok = timed_wait<DIAG>(&sh.q_full, q_iter & 1, abort_flag, wait_q);
                 if (!ok) break;
+                ITK_BEAT(10);
                 // The tensor pipe accepts only a couple of UMMAs ahead of the one it executes, so
                 // every cycle this thread spends between two batches of issues is a bubble.  The
                 // barriers of tile t+1 are therefore probed while the UMMAs of tile t execute
@@ -881,12 +999,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
                     const int buffer = kv_iter & 1;
                     const int stage = kv_iter % kKvStages;
+                    ITK_BEAT(1000 + kv_iter * 10 + 1);
                     if (!acc_ready) {
-                        ok = timed_wait<DIAG, true>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
+                        ok = timed_wait<DIAG, kIssuerParkNs>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
                         if (!ok) break;
                     }
                     if (!kv_ready) {
-                        ok = timed_wait<DIAG, true>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
+                        ok = timed_wait<DIAG, kHotWait>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
                         if (!ok) break;
                     }
                     tcgen05_fence_after_sync();
@@ -904,6 +1023,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     umma_f8(tmem_d, desc_kv + 6, desc_q + 6, idesc, 1u);
                     // a single commit per tile frees the key stage and publishes the accumulator
                     umma_commit(&sh.tile_done[stage]);
+                    ITK_BEAT(1000 + kv_iter * 10 + 2);
                 }
                 if (!ok) break;
                 umma_commit(&sh.q_empty);
@@ -925,7 +1045,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     } else {
         // ============================================================ Top-K / threshold consumers
         if (MODE != kModeRepair) {
-            const int cwarp = warp < kEpilogueWarp0 ? warp - 2 : warp - 12 + 2;   // warps 2,3,12..15 -> 0..5
+            const int cwarp = warp < kEpilogueWarp0 ? warp - 2 : warp - (kEpilogueWarp0 + kEpilogueWarps) + 2;   // warps 2,3,20..23 -> 0..5
             const int ctid = cwarp * 32 + lane;
             int unit_iter = 0;
             bool ok = true;
@@ -941,6 +1061,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const int slot = unit_iter & 1;
                 if (has_tiles) {
                     // one thread polls; the others sleep in the named barrier until it is through
+                    ITK_BEAT(10 + 100 * unit_iter);
                     if (ctid == 0) {
                         const bool got = timed_wait<DIAG>(&sh.cand_ready[slot], (unit_iter >> 1) & 1, abort_flag, wait_ready);
                         sh.sel_failed = got ? 0 : -1;
@@ -949,12 +1070,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     ok = sh.sel_failed != -1;
                     consumer_sync();
                     if (!ok) break;
+                    ITK_BEAT(11 + 100 * unit_iter);
                 }
                 const long long select_begin = DIAG ? clock64() : 0;
                 if (MODE == kModeTopK) {
                     for (int r = 0; r < u.nrows; ++r) {
                         if (DIAG && (p.debug_skip & 1)) continue;
-#if ITK_EXPERIMENT == 6
+#if ITK_EXPERIMENT >= 6
                         continue;
 #endif
                         consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
@@ -962,6 +1084,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 } else if (cwarp < u.nrows) {
                     sample_threshold_row(sh, p, u, cwarp, slot, has_tiles, lane);   // one warp per row
                 }
+                ITK_BEAT(12 + 100 * unit_iter);
                 if (DIAG) select_cycles += clock64() - select_begin;
                 if (has_tiles) {
                     consumer_sync();
@@ -984,26 +1107,23 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         }
     }
     } else {
-        // ... and the two epilogue warpgroups (warps 4-11) take most of the register file.
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegisters));
         // ============================================================ epilogue
-        // Every tile is shared by both warpgroups: warpgroup g owns query rows 2g and 2g+1
-        // (accumulator columns [128g, 128g+128)); a warp reads the 32 TMEM lanes (= keys) of
-        // its quarter, which is also its candidate segment.  Accumulators come out of TMEM in
-        // the 16x256b fragment layout: thread t of a warp holds, for lanes l = t/4 and l+8 of
-        // a 16-lane half, the column pairs 8n + 2(t%4) + {0,1}, n = 0..7, of one query row.
-        // So a thread only ever needs 16 of the 64 head weights of each of its two rows, kept
-        // in registers for the whole unit: no shared-memory traffic in the hot loop.  The
-        // four threads of a quad then combine their partial head sums with two shuffles.
+        // Sixteen warps share every tile: warp (quarter, row) reads the 32 TMEM lanes (= keys) of
+        // its lane quarter, which is also its candidate segment, and the 64 accumulator columns
+        // (= heads) of one query row.  Accumulators come out of TMEM in the 16x256b fragment
+        // layout, 32 columns at a time: thread t of a warp holds, for lanes l = t/4 and l+8 of a
+        // 16-lane half, the column pairs 8n + 2(t%4) + {0,1}, n = 0..3.  So a thread needs only 16
+        // of the row's 64 head weights, kept in registers for the whole unit: no shared-memory
+        // traffic in the hot loop.  The four threads of a quad combine their partial head sums
+        // with two shuffles, after which every thread owns the score of exactly one key of the
+        // tile.  Four warps per scheduler hide one another's TMEM and arithmetic latencies.
         const int ew = warp - kEpilogueWarp0;
-        const int wg = ew >> 2;
         const int quarter = ew & 3;             // = warp % 4, the TMEM lane quarter this warp may read
+        const int own_r = ew >> 2;              // query row of the unit this warp finishes
         const int quad = lane & 3;              // column-pair selector inside the fragment
-        const int own_i = quad & 1;             // which of the warpgroup's two rows this thread finishes
-        const int own_lane = (lane >> 2) + 8 * (quad >> 1);   // lane inside a 16-lane half it finishes
+        const int own_lane = (lane >> 2) + 8 * quad;   // key (TMEM lane) of the quarter this thread finishes
         const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(wg * 2 * kHeads);
-        const float minus_inf = __int_as_float(0xff800000);
+                                   static_cast<uint32_t>(own_r * kHeads);
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
@@ -1021,72 +1141,39 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             ok = warp_wait<DIAG>(&sh.w_full[slot], use_parity, abort_flag, lane, wait_w);
             if (!ok) break;
+            ITK_BEAT(11 + 100000 * unit_iter);
 
-            // the row this thread finishes: range, threshold, whether it is wanted at all
-            const int own_r = wg * 2 + own_i;
-            int row_lo = 0, row_hi = 0;
-            float threshold = minus_inf;
-            bool row_on = own_r < u.nrows;
-            long long own_slot = 0;
-            if (row_on) {
-                const int row = u.row0 + own_r;
-                own_slot = static_cast<long long>(u.shard) * p.rows + row;
-                const int start = __ldg(p.k_start + row);
-                const int end = __ldg(p.k_end + row);
-                if (MODE == kModeSample) {
-                    row_lo = start;
-                    row_hi = end;
-                    row_on = end - start > p.target_candidates;
-                } else {
-                    row_lo = max(start, u.key_lo);
-                    row_hi = min(min(end, p.keys), u.key_hi);
-                    if (MODE == kModeTopK) {
-                        const int valid = row_hi - row_lo;
-                        if (valid > kTopK) threshold = __ldg(p.thresholds + own_slot);
-                        row_on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
-                    } else {
-                        row_on = p.failure_flags[own_slot] != 0;
-                    }
-                }
-            }
-            // Candidate compaction: even lanes finish row 2g, odd lanes row 2g+1, so one ballot per
-            // 16-lane half serves both rows and every thread keeps the running count of its own row.
-            const unsigned row_mask = own_i == 0 ? 0x55555555u : 0xaaaaaaaau;
-            const unsigned row_below = row_mask & ((1u << lane) - 1u);
+            // candidate segment of (row, quarter) and the number of candidates in it (warp-uniform)
             const uint32_t score_slots = smem_u32(&sh.cand_scores[slot][own_r][quarter * kSegCap]);
             const uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
-            int own_count = 0;
-            // tiles [interior_lo, interior_hi) lie inside the row's key range: there the threshold alone
-            // decides (a NaN threshold rejects everything for rows that are switched off)
-            const int interior_lo = (row_lo + kTileKeys - 1) / kTileKeys;
-            const int interior_hi = row_hi / kTileKeys;
-            const float pass_threshold = row_on ? threshold : __int_as_float(0x7fc00000);
+            int count = 0;
+            // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
+            // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
+            // that keep every key); a row that is switched off has an empty range.
+            const RowState row = load_row_state<MODE>(p, u.row0, u.nrows, u.shard, u.key_lo, u.key_hi, own_r);
+            const int row_lo = row.lo;
+            const unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
+            const float threshold = row.threshold;
 
-            // head weights of this thread's column pairs, both rows
-            uint64_t w0[8], w1[8];
+            // head weights of this thread's column pairs
+            uint64_t w[8];
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                w0[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][(wg * 2 + 0) * kHeads + 8 * n + 2 * quad]);
-                w1[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][(wg * 2 + 1) * kHeads + 8 * n + 2 * quad]);
-            }
+            for (int n = 0; n < 8; ++n)
+                w[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][own_r * kHeads + 8 * n + 2 * quad]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.w_empty[slot]);   // weights are in registers now
+            ITK_BEAT(12 + 100000 * unit_iter);
 
-            // scale and range key of the two keys this thread finishes in tile t (one per 16-lane half)
-            const auto per_key = [&](int t, float (&scale)[2], int (&range_key)[2]) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
-                    const bool key_ok = key < p.keys;
-                    scale[h] = key_ok ? __ldg(p.kv_scales + key) : 0.0f;
-                    range_key[h] = key;
-                    if (MODE == kModeSample) range_key[h] = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
-                }
+            // scale and range key of the key this thread finishes in tile t
+            const auto per_key = [&](int t, float& scale, int& range_key) {
+                const int key = t * kTileKeys + quarter * 32 + own_lane;
+                const bool key_ok = key < p.keys;
+                scale = key_ok ? __ldg(p.kv_scales + key) : 0.0f;
+                if (MODE == kModeSample) range_key = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
             };
-            // partial head sums of one fragment load: lanes l and l+8, this thread's 16 heads.
             // ReLU is applied in place on the fragment registers, which are consecutive pairs
             // already, so the packed multiply-add can read them without any move.
-            const auto relu_fma = [](uint32_t& x0, uint32_t& x1, uint64_t w, uint64_t& acc) {
+            const auto relu_fma = [](uint32_t& x0, uint32_t& x1, uint64_t wpair, uint64_t& acc) {
                 asm("{\n\t"
                     ".reg .b64 t;\n\t"
                     "max.f32 %0, %0, 0f00000000;\n\t"
@@ -1095,26 +1182,23 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     "fma.rn.f32x2 %2, t, %3, %2;\n\t"
                     "}"
                     : "+f"(*reinterpret_cast<float*>(&x0)), "+f"(*reinterpret_cast<float*>(&x1)), "+l"(acc)
-                    : "l"(w));
+                    : "l"(wpair));
             };
-            const auto partial = [&](uint32_t (&r)[32], const uint64_t (&w)[8], float& lane_a, float& lane_b) {
-                uint64_t a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+            // one fragment (32 columns, lanes l and l+8) into the packed accumulators of the two lanes
+            const auto partial = [&](uint32_t (&r)[16], int w0, uint64_t (&acc_a)[2], uint64_t (&acc_b)[2]) {
 #pragma unroll
-                for (int n = 0; n < 8; n += 2) {
-                    relu_fma(r[4 * n + 0], r[4 * n + 1], w[n], a0);
-                    relu_fma(r[4 * n + 2], r[4 * n + 3], w[n], b0);
-                    relu_fma(r[4 * n + 4], r[4 * n + 5], w[n + 1], a1);
-                    relu_fma(r[4 * n + 6], r[4 * n + 7], w[n + 1], b1);
+                for (int n = 0; n < 4; ++n) {
+                    relu_fma(r[4 * n + 0], r[4 * n + 1], w[w0 + n], acc_a[n & 1]);
+                    relu_fma(r[4 * n + 2], r[4 * n + 3], w[w0 + n], acc_b[n & 1]);
                 }
-                float x0, x1, x2, x3;
-                unpack_pair(a0, x0, x1);
-                unpack_pair(a1, x2, x3);
-                lane_a = (x0 + x1) + (x2 + x3);
-                unpack_pair(b0, x0, x1);
-                unpack_pair(b1, x2, x3);
-                lane_b = (x0 + x1) + (x2 + x3);
             };
-            // Quad reduce-scatter of (lane a,row 0), (lane a,row 1), (lane b,row 0), (lane b,row 1):
+            const auto head_sum = [](const uint64_t (&acc)[2]) -> float {
+                float x0, x1, x2, x3;
+                unpack_pair(acc[0], x0, x1);
+                unpack_pair(acc[1], x2, x3);
+                return (x0 + x1) + (x2 + x3);
+            };
+            // Quad reduce-scatter of the four partial sums (lanes l, l+8, l+16, l+24 of the quarter):
             // thread `quad` ends up with the complete head sum number `quad`.
             const auto quad_reduce = [&](float v0, float v1, float v2, float v3) -> float {
                 const bool odd = (quad & 1) != 0;
@@ -1125,137 +1209,140 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const bool upper = (quad & 2) != 0;
                 return (upper ? keep_b : keep_a) + __shfl_xor_sync(0xffffffffu, upper ? keep_a : keep_b, 2);
             };
-            // threshold filter and warp-level compaction of the 32 scores of one 16-lane half.
-            // Even lanes finish row 2g, odd lanes row 2g+1, so one ballot serves both rows.
-            const auto finish_half = [&](int h, int t, float head_sum, float scale, int range_key) {
-                const float score = head_sum * scale;
-                const int key = t * kTileKeys + quarter * 32 + h * 16 + own_lane;
-                bool active;
-                if (MODE == kModeTopK && !DIAG && t >= interior_lo && t < interior_hi) {
-                    active = score >= pass_threshold;
-                } else {
+            // threshold filter and warp-level compaction of the 32 scores of this warp in one tile
+            // Filter and warp-level compaction of the 32 scores of this warp in one tile.
+            const auto finish = [&](int t, float sum, float scale, int sample_key) {
+                const float score = sum * scale;
+                const int key = t * kTileKeys + quarter * 32 + own_lane;
+                const int range_key = MODE == kModeSample ? sample_key : key;   // the sampled key's position in the context
+                const bool in_range = static_cast<unsigned>(range_key - row_lo) < row_span;
+                if (DIAG) {
                     const bool key_ok = key < p.keys;
-                    const bool in_range = key_ok && range_key >= row_lo && range_key < row_hi;
-                    if (DIAG) {
-                        if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
-                            const bool shown = MODE == kModeSample ? true : in_range;
-                            p.diag_logits[static_cast<long long>(u.row0 + own_r) * p.diag_stride + key] =
-                                shown ? score : minus_inf;
-                        }
+                    if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
+                        const bool shown = MODE == kModeSample ? true : (range_key >= row.lo && range_key < row.hi);
+                        p.diag_logits[static_cast<long long>(u.row0 + own_r) * p.diag_stride + key] =
+                            shown ? score : __int_as_float(0xff800000);
                     }
-                    if (MODE == kModeRepair) {
-                        if (row_on && key_ok && key >= u.key_lo && key < u.key_hi) {
-                            p.repair_pairs[own_slot * kRepairChunk + (key - u.key_lo)] =
-                                in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
-                        }
-                        return;
-                    }
-                    active = row_on && in_range;
-                    if (DIAG && (p.debug_skip & 2)) active = false;
-                    if (MODE == kModeTopK) active = active && score >= threshold;
-                    else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
                 }
+                if (MODE == kModeRepair) {
+                    if (row.on && key < p.keys && key >= u.key_lo && key < u.key_hi) {
+                        p.repair_pairs[row.slot * kRepairChunk + (key - u.key_lo)] =
+                            (range_key >= row.lo && range_key < row.hi) ? pack_score_id(score, static_cast<uint32_t>(key))
+                                                                        : 0ull;
+                    }
+                    return;
+                }
+                bool active = in_range;
+                if (DIAG && (p.debug_skip & 2)) active = false;
+                if (MODE == kModeTopK) active = active && score >= threshold;
+                else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
                 const unsigned ballot = __ballot_sync(0xffffffffu, active);
-                const int position = own_count + __popc(ballot & row_below);
-                own_count += __popc(ballot & row_mask);
-                if (active) {
-                    if (position < kSegCap) {
-                        st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
-                        // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
-                        st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position),
-                                      static_cast<uint32_t>(t * 32 + h * 16 + own_lane));
-                    } else if (MODE == kModeTopK && position < kSegCap + kSpillSegCap) {
-                        p.spill[own_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
+                const int position = count + __popc(ballot & ((1u << lane) - 1u));
+                count += __popc(ballot);
+                if (active && position < kSegCap) {
+                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
+                    // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
+                    st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
+                }
+                if (MODE == kModeTopK && count > kSegCap) {
+                    // warp-uniform and rare: the segment is full, later candidates go to the global spill
+                    if (active && position >= kSegCap && position < kSegCap + kSpillSegCap) {
+                        const long long row_slot = static_cast<long long>(u.shard) * p.rows + u.row0 + own_r;
+                        p.spill[row_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
                             pack_score_id(score, static_cast<uint32_t>(key));
                     }
                 }
             };
 
-            // Software pipeline over the four fragment loads of a tile, (half 0,row 0), (half 0,row 1),
-            // (half 1,row 0), (half 1,row 1): while one fragment is reduced on the CUDA cores the
-            // next is on its way out of TMEM (TMEM read bandwidth, about 350 cycles per tile, hides
-            // under the arithmetic).  The accumulator buffer goes back to the UMMA issuer as soon
-            // as the fourth fragment has landed; the first fragment of the next tile is requested
-            // before the last filter step so that its latency is covered too.
-            uint32_t fx[32], fy[32];
-            float scale[2], next_scale[2] = {0.0f, 0.0f};
-            int range_key[2], next_range_key[2] = {0, 0};
+            // Four fragment loads per tile, (half 0, heads 0-31), (half 0, heads 32-63), (half 1, heads
+            // 0-31), (half 1, heads 32-63), through one 16-register buffer: the register budget has no
+            // room for a second one, and the other three epilogue warps of the scheduler cover the TMEM
+            // latency.  The accumulator buffer goes back to the UMMA issuer as soon as the fourth
+            // fragment has landed; the first fragment of the next tile is requested before the filter step.
+            uint32_t fa[16];
+            float scale, next_scale = 0.0f;
+            int range_key = 0, next_range_key = 0;   // sample mode only
             per_key(u.tile_begin, scale, range_key);
-            ok = warp_hot_wait<DIAG>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, wait_acc);
+            ok = warp_tile_wait<DIAG>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, wait_acc);
             if (!ok) break;
             tcgen05_fence_after_sync();
-            tmem_load_frag(tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN), fx);
+            tmem_load_frag16(tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN), fa);
             for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
+                ITK_BEAT(100 * acc_iter + 20);
                 const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
                 const uint32_t upper_half = 16u << 16;
                 const bool more = t + 1 < u.tile_end;
                 if (more) per_key(t + 1, next_scale, next_range_key);
-                float a_r0, b_r0, a_r1, b_r1, c_r0, d_r0, c_r1, d_r1;
+                uint64_t acc_a[2] = {0, 0}, acc_b[2] = {0, 0};
 
-                tmem_load_wait(fx);                                   // (half 0, row 0)
-                tmem_load_frag(taddr + kHeads, fy);
+                tmem_load_wait16(fa);                                 // (half 0, heads 0-31)
+                ITK_BEAT(100 * acc_iter + 21);
 #if ITK_EXPERIMENT != 1
-                partial(fx, w0, a_r0, b_r0);
+                partial(fa, 0, acc_a, acc_b);
 #else
-                if (fx[3] == 0x7fc12345u) own_count += 1;
+                if (fa[3] == 0x7fc12345u) count += 1;
 #endif
-                tmem_load_wait(fy);                                   // (half 0, row 1)
-                tmem_load_frag(taddr + upper_half, fx);
+                tmem_load_frag16(taddr + 32, fa);
+                tmem_load_wait16(fa);                                 // (half 0, heads 32-63)
+                ITK_BEAT(100 * acc_iter + 22);
 #if ITK_EXPERIMENT != 1
-                partial(fy, w1, a_r1, b_r1);
+                partial(fa, 4, acc_a, acc_b);
 #else
-                if (fy[3] == 0x7fc12345u) own_count += 1;
+                if (fa[3] == 0x7fc12345u) count += 1;
 #endif
-                tmem_load_wait(fx);                                   // (half 1, row 0)
-                tmem_load_frag(taddr + upper_half + kHeads, fy);
-#if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
-                finish_half(0, t, quad_reduce(a_r0, a_r1, b_r0, b_r1), scale[0], range_key[0]);
-#elif ITK_EXPERIMENT == 2
-                if (a_r0 + a_r1 + b_r0 + b_r1 == 1.2345e38f) own_count += 1;
-#endif
+                tmem_load_frag16(taddr + upper_half, fa);
+                const float sum0 = head_sum(acc_a), sum1 = head_sum(acc_b);   // lanes l and l+8 of the quarter
+                acc_a[0] = acc_a[1] = acc_b[0] = acc_b[1] = 0;
+                tmem_load_wait16(fa);                                 // (half 1, heads 0-31)
+                ITK_BEAT(100 * acc_iter + 23);
 #if ITK_EXPERIMENT != 1
-                partial(fx, w0, c_r0, d_r0);
+                partial(fa, 0, acc_a, acc_b);
 #else
-                if (fx[3] == 0x7fc12345u) own_count += 1;
+                if (fa[3] == 0x7fc12345u) count += 1;
 #endif
-                tmem_load_wait(fy);                                   // (half 1, row 1): buffer fully read
+                tmem_load_frag16(taddr + upper_half + 32, fa);
+                tmem_load_wait16(fa);                                 // (half 1, heads 32-63): buffer fully read
+                ITK_BEAT(100 * acc_iter + 24);
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh.acc_empty[acc_iter & 1]);
+                ITK_BEAT(100 * acc_iter + 25);
 #if ITK_EXPERIMENT != 1
-                partial(fy, w1, c_r1, d_r1);
+                partial(fa, 4, acc_a, acc_b);
 #else
-                if (fx[0] == 0x7fc12345u && fy[1] == 7u) own_count += 1;
+                if (fa[3] == 0x7fc12345u) count += 1;
 #endif
                 if (more) {
                     const int next = acc_iter + 1;
-                    ok = warp_hot_wait<DIAG>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, wait_acc);
+                    ok = warp_tile_wait<DIAG>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, wait_acc);
                     if (!ok) break;
                     tcgen05_fence_after_sync();
-                    tmem_load_frag(tmem_lane + static_cast<uint32_t>((next & 1) * kUmmaN), fx);
+                    tmem_load_frag16(tmem_lane + static_cast<uint32_t>((next & 1) * kUmmaN), fa);
                 }
+                ITK_BEAT(100 * acc_iter + 26);
 #if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
-                finish_half(1, t, quad_reduce(c_r0, c_r1, d_r0, d_r1), scale[1], range_key[1]);
+                finish(t, quad_reduce(sum0, sum1, head_sum(acc_a), head_sum(acc_b)), scale, range_key);
+#elif ITK_EXPERIMENT == 7   // no filter / compaction
+                if (quad_reduce(sum0, sum1, head_sum(acc_a), head_sum(acc_b)) * scale >= threshold) count += 1;
 #elif ITK_EXPERIMENT == 2
-                if (c_r0 + c_r1 + d_r0 + d_r1 == 1.2345e38f) own_count += 1;
+                if (sum0 + sum1 + head_sum(acc_a) + head_sum(acc_b) == 1.2345e38f) count += 1;
 #endif
-                scale[0] = next_scale[0];
-                scale[1] = next_scale[1];
-                range_key[0] = next_range_key[0];
-                range_key[1] = next_range_key[1];
+                scale = next_scale;
+                range_key = next_range_key;
+                ITK_BEAT(100 * acc_iter + 27);
             }
             if (!ok) break;
-            __syncwarp();
             if (MODE != kModeRepair) {
-                // lane 0 finishes row 2g, lane 1 row 2g+1: their running counts are the segment sizes
-                if (lane < 2) sh.counts[slot][own_r][quarter] = own_count;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh.cand_ready[slot]);
+                __syncwarp();   // every lane's candidates are written before lane 0 publishes the segment
+                if (lane == 0) {
+                    sh.counts[slot][own_r][quarter] = count;
+                    mbar_arrive(&sh.cand_ready[slot]);
+                }
             }
             ++unit_iter;
         }
-        if (DIAG && p.trace != nullptr && quarter == 0 && lane == 0) {
-            long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields + 4 * wg;
+        if (DIAG && p.trace != nullptr && quarter == 0 && own_r < 2 && lane == 0) {
+            long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields + 4 * own_r;
             trace[kTraceEpiTotal] = clock64() - role_begin;
             trace[kTraceEpiWaitAcc] = wait_acc;
             trace[kTraceEpiWaitFree] = wait_free;
@@ -1265,6 +1352,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     }
 
     // ---------------------------------------------------------------- teardown
+    ITK_BEAT(900000);
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) {

@@ -45,7 +45,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // thread does not spend issue slots on a hot spin loop.
 constexpr uint32_t kWaitParkNs = 20000;
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t park_ns = kWaitParkNs) {
     uint32_t done;
     asm volatile(
         "{\n\t"
@@ -54,7 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitParkNs)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(park_ns)
         : "memory");
     return done != 0;
 }
@@ -81,14 +81,18 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity.  Returns false when the limit
 // expired or another thread of the CTA already gave up (*abort_flag != 0); the
-// caller then leaves its role loop.  HOT = true polls without parking.
-template <bool HOT = false>
+// caller then leaves its role loop.  PARK_NS = 0 polls without parking, otherwise a
+// failed probe suspends the thread for up to PARK_NS nanoseconds.
+constexpr uint32_t kHotWait = 0;
+
+template <uint32_t PARK_NS = kWaitParkNs>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (HOT ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    constexpr bool kHot = PARK_NS == kHotWait;
+    if (mbar_test_wait(bar, parity)) return true;
     uint64_t deadline = 0;
     for (uint32_t spin = 1;; ++spin) {
-        if (HOT ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
-        if ((spin & (HOT ? 1023u : 15u)) == 0u) {
+        if (kHot ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity, PARK_NS)) return true;
+        if ((spin & (kHot ? 1023u : 15u)) == 0u) {
             if (*abort_flag != 0) return false;
             const uint64_t now = global_timer_ns();
             if (deadline == 0) {
@@ -99,6 +103,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             }
         }
     }
+}
+
+// Mask of the lanes below the calling one.
+__device__ __forceinline__ uint32_t lanemask_lt() {
+    uint32_t mask;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
+    return mask;
 }
 
 // Stores through a 32-bit shared-memory address (no generic address arithmetic).
@@ -232,6 +243,27 @@ __device__ __forceinline__ void tmem_load_frag(uint32_t tmem_address, uint32_t (
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(tmem_address)
         : "memory");
+}
+
+// Half-width fragment: 16x256b.x4 = 32 columns, 16 registers (thread t: r[4n], r[4n+1] = lane t/4,
+// columns 8n + 2(t%4) + {0,1}; r[4n+2], r[4n+3] = lane t/4 + 8, same columns; n = 0..3).
+__device__ __forceinline__ void tmem_load_frag16(uint32_t tmem_address, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(tmem_address)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                   "+r"(r[15])
+                 :
+                 : "memory");
 }
 
 // Waits for this thread's outstanding TMEM loads.  The registers are listed as
