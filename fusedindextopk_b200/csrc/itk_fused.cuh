@@ -1121,9 +1121,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         const int quarter = ew & 3;             // = warp % 4, the TMEM lane quarter this warp may read
         const int own_r = ew >> 2;              // query row of the unit this warp finishes
         const int quad = lane & 3;              // column-pair selector inside the fragment
-        const int own_lane = (lane >> 2) + 8 * quad;   // key (TMEM lane) of the quarter this thread finishes
-        const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(own_r * kHeads);
+        int own_lane = (lane >> 2) + 8 * quad;   // key (TMEM lane) of the quarter this thread finishes
+        uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(own_r * kHeads);
+        keep_in_register(own_lane);
+        keep_in_register(tmem_lane);
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
@@ -1144,16 +1146,22 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             ITK_BEAT(11 + 100000 * unit_iter);
 
             // candidate segment of (row, quarter) and the number of candidates in it (warp-uniform)
-            const uint32_t score_slots = smem_u32(&sh.cand_scores[slot][own_r][quarter * kSegCap]);
-            const uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
+            uint32_t score_slots = smem_u32(&sh.cand_scores[slot][own_r][quarter * kSegCap]);
+            uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
+            keep_in_register(score_slots);
+            keep_in_register(id_slots);
             int count = 0;
             // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
             // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
             // that keep every key); a row that is switched off has an empty range.
             const RowState row = load_row_state<MODE>(p, u.row0, u.nrows, u.shard, u.key_lo, u.key_hi, own_r);
-            const int row_lo = row.lo;
-            const unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
-            const float threshold = row.threshold;
+            int row_lo = row.lo;
+            unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
+            float threshold = row.threshold;
+            // the compiler would otherwise re-derive these per tile from thread and unit indices
+            keep_in_register(row_lo);
+            keep_in_register(row_span);
+            keep_in_register(threshold);
 
             // head weights of this thread's column pairs
             uint64_t w[8];

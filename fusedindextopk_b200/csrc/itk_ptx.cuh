@@ -105,6 +105,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Makes a value opaque to the compiler, which then keeps it in a register instead of
+// recomputing it from its inputs at every use inside a hot loop.
+__device__ __forceinline__ void keep_in_register(int& value) { asm volatile("" : "+r"(value)); }
+__device__ __forceinline__ void keep_in_register(unsigned& value) { asm volatile("" : "+r"(value)); }
+__device__ __forceinline__ void keep_in_register(float& value) { asm volatile("" : "+f"(value)); }
+
 // Mask of the lanes below the calling one.
 __device__ __forceinline__ uint32_t lanemask_lt() {
     uint32_t mask;
