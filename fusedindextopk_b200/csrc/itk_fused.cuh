@@ -90,6 +90,9 @@ constexpr int kEpilogueWarps = kEpilogueThreads / 32;
 // no split in units of 8 per warpgroup suits both the epilogue and the consumers, so the budget is uniform.
 constexpr int kConsumerThreads = 192;
 constexpr int kConsumerWarps = kConsumerThreads / 32;
+constexpr int kRadixHists = kConsumerWarps / 2;
+constexpr int kScoreBins = 256;
+constexpr int kBinListCap = 512;
 
 constexpr uint32_t kQBytes = kUmmaN * kHeadDim;       // 32768
 constexpr uint32_t kKvBytes = kTileKeys * kHeadDim;   // 16384
@@ -152,7 +155,16 @@ struct __align__(16) FusedShared {
     uint32_t cand_scores[2][kBlockQ][kRowCap];
     uint16_t cand_ids[2][kBlockQ][kRowCap];
     int counts[2][kBlockQ][kSegments];
-    int hist[kConsumerWarps][256];   // one digit histogram per consumer warp
+    // Score histogram of every candidate row, filled by the epilogue as it finds the candidates:
+    // kScoreBins bins of the distance to the row threshold, two 16-bit counters per word.
+    uint32_t row_hist[2][kBlockQ][kScoreBins / 2];
+    // The selection's scratch: the scores of the bin that holds the cutoff or, when that bin is too
+    // full, the digit histograms of the radix selection (one per pair of consumer warps).
+    union {
+        int hist[kRadixHists][256];
+        uint32_t bin_scores[kBinListCap];
+    };
+    int bin_count;
     int warp_greater[kConsumerWarps];
     int warp_equal[kConsumerWarps];
     uint32_t sel_ref;
@@ -380,6 +392,123 @@ __device__ __forceinline__ void for_excess_spill(const RowCandidates& c, const O
     for (int e = kSpillCached + ctid; e < total; e += kConsumerThreads) visit(spill_entry(c, own, e));
 }
 
+// Histogram bin of a candidate: its distance (in ordered score bits) to the row threshold on a
+// logarithmic scale, eight bins per octave.  Monotone in the score; the relative width of 1/8 keeps the
+// bin that holds the Top-K cutoff down to a small fraction of the candidates below the cutoff.
+__device__ __forceinline__ int score_bin(uint32_t distance) {
+    const uint32_t d = max(distance, 8u);
+    const int e = 31 - __clz(d);                         // 3 .. 31
+    return (e - 2) * 8 + static_cast<int>((d >> (e - 3)) & 7u);   // 8 .. 239
+}
+
+// Distances [lo, lo + width) that score_bin maps to `bin`.
+__device__ __forceinline__ void bin_range(int bin, uint32_t& lo, uint32_t& width) {
+    if (bin <= 8) {          // distances below 8 are clamped into bin 8
+        lo = 0u;
+        width = 9u;
+    } else {
+        const int e = (bin >> 3) + 2;
+        lo = (8u + static_cast<uint32_t>(bin & 7)) << (e - 3);
+        width = 1u << (e - 3);
+    }
+}
+
+// Selection from the histogram that the epilogue filled: warp 0 finds the bin that holds the rank-th
+// largest score, all threads gather the scores of that bin (two instructions per candidate: the bin
+// is a range of scores), and warp 0 takes the exact cutoff among them bit by bit.  Returns false (and
+// leaves the outputs alone) when the bin holds more than kBinListCap scores; the caller then falls
+// back to the radix selection.  Called by all consumer threads; needs rank_in <= number of candidates.
+__device__ __forceinline__ bool bin_select(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own,
+                                           const uint32_t* row_hist, uint32_t threshold_bits, int ctid, int rank_in,
+                                           uint32_t& cutoff, int& equal_needed) {
+    const int lane = ctid & 31;
+    if (ctid < 32) {
+        // lane l owns bins 8l .. 8l+7; `above` = candidates in bins owned by higher lanes
+        int bins[8];
+        int mine = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t word = row_hist[lane * 4 + j];
+            bins[2 * j] = static_cast<int>(word & 0xffffu);
+            bins[2 * j + 1] = static_cast<int>(word >> 16);
+            mine += bins[2 * j] + bins[2 * j + 1];
+        }
+        int suffix = mine;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const int other = __shfl_down_sync(0xffffffffu, suffix, offset);
+            if (lane + offset < 32) suffix += other;
+        }
+        int above = suffix - mine;
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+            const int through = above + bins[j];
+            if (above < rank_in && rank_in <= through) {
+                sh.sel_bin = lane * 8 + j;
+                sh.sel_greater = above;
+                sh.sel_total = bins[j];
+            }
+            above = through;
+        }
+        if (lane == 0) sh.bin_count = 0;
+    }
+    consumer_sync();
+    const int in_bin = sh.sel_total;
+    const int need = rank_in - sh.sel_greater;       // how many of the bin's scores belong to the top rank_in
+    if (in_bin > kBinListCap) return false;
+    uint32_t lo, width;
+    bin_range(sh.sel_bin, lo, width);
+    const uint32_t base = threshold_bits + lo;       // the bin holds the scores base + [0, width)
+    const auto gather = [&](uint32_t score) {
+        const uint32_t offset = score - base;
+        if (offset < width) {
+            const int at = atomicAdd(&sh.bin_count, 1);
+            if (at < kBinListCap) sh.bin_scores[at] = offset;
+        }
+    };
+    for_own_scores(own, gather);
+    for_excess_spill(c, own, ctid, [&](uint64_t pair) { gather(static_cast<uint32_t>(pair >> 32)); });
+    consumer_sync();
+    if (ctid < 32) {
+        // the need-th largest offset of the list, most significant bit first: a bit is kept when at
+        // least `rank` of the offsets that agree with the prefix so far have it set
+        constexpr int kPerLane = kBinListCap / 32;
+        uint32_t own_offsets[kPerLane];
+        uint32_t live = 0u;
+#pragma unroll
+        for (int m = 0; m < kPerLane; ++m) {
+            const int i = lane + 32 * m;
+            own_offsets[m] = i < in_bin ? sh.bin_scores[i] : 0u;
+            live |= i < in_bin ? 1u << m : 0u;
+        }
+        const int bits = 32 - __clz(width - 1u | 1u);
+        uint32_t prefix = 0u, mask = bits == 32 ? 0u : 0xffffffffu << bits;
+        int rank = need;
+#pragma unroll 1
+        for (int bit = bits - 1; bit >= 0; --bit) {
+            const uint32_t probe = 1u << bit;
+            const uint32_t want = prefix | probe;
+            const uint32_t care = mask | probe;
+            int above = 0;
+#pragma unroll
+            for (int m = 0; m < kPerLane; ++m)
+                above += static_cast<int>(live >> m & 1u) & static_cast<int>((own_offsets[m] & care) == want);
+            above = __reduce_add_sync(0xffffffffu, above);
+            if (above >= rank) prefix |= probe;
+            else rank -= above;
+            mask |= probe;
+        }
+        if (lane == 0) {
+            sh.sel_ref = base + prefix;
+            sh.sel_ecount = rank;      // offsets equal to the cutoff that still belong to the top rank_in
+        }
+    }
+    consumer_sync();
+    cutoff = sh.sel_ref;
+    equal_needed = sh.sel_ecount;
+    return true;
+}
+
 // Radix selection over the ordered score bits of one row, up to 8 bits per round.
 // On return `cutoff` is the rank-th largest score and `equal_needed` the number of
 // candidates equal to it that belong to the top `rank_in`.  Needs rank_in <= number of
@@ -390,7 +519,7 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
                                              int ctid, int rank_in, uint32_t& cutoff, int& equal_needed) {
     const int lane = ctid & 31;
     const int cwarp = ctid >> 5;
-    int* my_hist = sh.hist[cwarp];
+    int* my_hist = sh.hist[cwarp % kRadixHists];
     if (ctid == 0) {
         int s = 0;
         while (s < kSegments - 1 && c.counts[s] == 0) ++s;
@@ -416,8 +545,10 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
         const int width = min(8, bits);
         const int shift = bits - width;
         const uint32_t digit_mask = (1u << width) - 1u;
-        for (int bin = lane; bin < 256; bin += 32) my_hist[bin] = 0;
-        __syncwarp();
+        consumer_sync();   // the histograms are shared by two warps: nobody may still read the last round
+        if (cwarp < kRadixHists)
+            for (int bin = lane; bin < 256; bin += 32) my_hist[bin] = 0;
+        consumer_sync();
         for_own_scores(own, [&](uint32_t score) {
             if ((score & mask) == prefix) atomicAdd(&my_hist[(score >> shift) & digit_mask], 1);
         });
@@ -435,7 +566,7 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
             for (int j = 0; j < 8; ++j) {
                 int sum = 0;
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; ++w) sum += sh.hist[w][ctid * 8 + j];
+                for (int w = 0; w < kRadixHists; ++w) sum += sh.hist[w][ctid * 8 + j];
                 bins[j] = sum;
                 mine += sum;
             }
@@ -466,77 +597,62 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
     equal_needed = rank;
 }
 
-// Writes the selected candidates of one row: everything above `cutoff`, then
-// `equal_needed` of the candidates equal to it (any of them); with take_all every
-// candidate.  Two passes without atomics: per-warp totals first, then each warp writes
-// behind the totals of the warps before it, lanes ordered by ballot.
+// Writes the selected candidates of one row: everything above `cutoff`, then `equal_needed` of the
+// candidates equal to it (any of them); with take_all every candidate.  Every thread counts its
+// candidates above the cutoff, a scan over the threads gives it a contiguous range of output
+// positions, and it writes its candidates there; the few candidates equal to the cutoff draw
+// tickets for the positions behind.
 __device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own, int ctid,
                                          uint32_t cutoff, int equal_needed, int greater_total, bool take_all,
                                          int32_t* out_ids, uint64_t* out_pairs) {
     const int lane = ctid & 31;
     const int cwarp = ctid >> 5;
     const int total_spill = own.spill_first[kSegments];
-    int greater = 0, equal = 0;
-    const auto tally = [&](uint32_t score) {
-        greater += (take_all || score > cutoff) ? 1 : 0;
-        equal += (!take_all && score == cutoff) ? 1 : 0;
-    };
+    int greater = 0;
+    const auto tally = [&](uint32_t score) { greater += (take_all || score > cutoff) ? 1 : 0; };
     for_own_scores(own, tally);
     for_excess_spill(c, own, ctid, [&](uint64_t pair) { tally(static_cast<uint32_t>(pair >> 32)); });
-    greater = __reduce_add_sync(0xffffffffu, greater);
-    equal = __reduce_add_sync(0xffffffffu, equal);
-    if (lane == 0) {
-        sh.warp_greater[cwarp] = greater;
-        sh.warp_equal[cwarp] = equal;
-    }
-    consumer_sync();
-    int next_greater = 0, next_equal = 0;
+    int inclusive = greater;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-        next_greater += w < cwarp ? sh.warp_greater[w] : 0;
-        next_equal += w < cwarp ? sh.warp_equal[w] : 0;
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if (lane >= offset) inclusive += other;
     }
-    const unsigned below = (1u << lane) - 1u;
-    const auto place = [&](bool live, uint32_t score) -> int {
-        const bool is_greater = live && (take_all || score > cutoff);
-        const bool is_equal = live && !take_all && score == cutoff;
-        const unsigned ballot_g = __ballot_sync(0xffffffffu, is_greater);
-        const unsigned ballot_e = __ballot_sync(0xffffffffu, is_equal);
-        int position = -1;
-        if (is_greater) {
-            position = next_greater + __popc(ballot_g & below);
-        } else if (is_equal) {
-            const int e = next_equal + __popc(ballot_e & below);
-            if (e < equal_needed) position = greater_total + e;
-        }
-        next_greater += __popc(ballot_g);
-        next_equal += __popc(ballot_e);
-        return position < kTopK ? position : -1;
+    if (lane == 31) sh.warp_greater[cwarp] = inclusive;
+    if (ctid == 0) sh.sel_ecount = 0;
+    consumer_sync();
+    int position = inclusive - greater;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) position += w < cwarp ? sh.warp_greater[w] : 0;
+    const auto write = [&](int at, uint32_t score, int key) {
+        if (at >= kTopK) return;
+        if (out_ids != nullptr) out_ids[at] = key;
+        if (out_pairs != nullptr) out_pairs[at] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
     };
-    const auto write = [&](int position, uint32_t score, int key) {
-        if (out_ids != nullptr) out_ids[position] = key;
-        if (out_pairs != nullptr) out_pairs[position] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
+    // `key()` is only evaluated for the candidates that are written
+    const auto place = [&](uint32_t score, auto&& key) {
+        if (take_all || score > cutoff) {
+            write(position++, score, key());
+        } else if (score == cutoff) {
+            const int ticket = atomicAdd(&sh.sel_ecount, 1);
+            if (ticket < equal_needed) write(greater_total + ticket, score, key());
+        }
     };
 #pragma unroll
     for (int j = 0; j < kOwnSmem; ++j) {
-        const int s = j / kSmemSlots;
-        const int i = ctid + (j % kSmemSlots) * kConsumerThreads;
-        const int position = place((own.smem_live >> j & 1u) != 0u, own.smem_score[j]);
-        if (position >= 0) write(position, own.smem_score[j], decode_key(c.ids[s * kSegCap + i], s));
+        if (own.smem_live >> j & 1u) {
+            const int segment = j / kSmemSlots;
+            const int i = ctid + (j % kSmemSlots) * kConsumerThreads;
+            place(own.smem_score[j], [&]() { return decode_key(c.ids[segment * kSegCap + i], segment); });
+        }
     }
 #pragma unroll
     for (int k = 0; k < kSpillRegs; ++k) {
-        if (k * kConsumerThreads < total_spill) {
-            const int position = place((own.spill_live >> k & 1u) != 0u, own.spill_score[k]);
-            if (position >= 0) write(position, own.spill_score[k], static_cast<int>(own.spill_key[k]));
-        }
+        if (own.spill_live >> k & 1u) place(own.spill_score[k], [&]() { return static_cast<int>(own.spill_key[k]); });
     }
-    for (int base = kSpillCached + cwarp * 32; base < total_spill; base += kConsumerThreads) {
-        const int e = base + lane;
-        const bool live = e < total_spill;
-        const uint64_t pair = live ? spill_entry(c, own, e) : 0ull;
-        const int position = place(live, static_cast<uint32_t>(pair >> 32));
-        if (position >= 0) write(position, static_cast<uint32_t>(pair >> 32), static_cast<int>(static_cast<uint32_t>(pair)));
+    for (int e = kSpillCached + ctid; e < total_spill; e += kConsumerThreads) {
+        const uint64_t pair = spill_entry(c, own, e);
+        place(static_cast<uint32_t>(pair >> 32), [&]() { return static_cast<int>(static_cast<uint32_t>(pair)); });
     }
 }
 
@@ -601,6 +717,7 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
             p.failure_flags[row_slot] = 1;
             if (p.out_counts != nullptr) p.out_counts[row_slot] = 0;
         }
+        for (int i = ctid; i < kScoreBins / 2; i += kConsumerThreads) sh.row_hist[slot][r][i] = 0u;
         consumer_sync();
         return;
     }
@@ -627,7 +744,9 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
     } else {
         uint32_t cutoff;
         int equal_needed;
-        radix_select(sh, c, view, ctid, kTopK, cutoff, equal_needed);
+        const float threshold = valid > kTopK ? __ldg(p.thresholds + row_slot) : __int_as_float(0xff800000);
+        if (!bin_select(sh, c, view, sh.row_hist[slot][r], ordered_bits(threshold), ctid, kTopK, cutoff, equal_needed))
+            radix_select(sh, c, view, ctid, kTopK, cutoff, equal_needed);
         if (phase != nullptr) {
             const long long now = clock64();
             phase[1] += now - stamp;
@@ -639,6 +758,7 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
         p.failure_flags[row_slot] = 0;
         if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
     }
+    for (int i = ctid; i < kScoreBins / 2; i += kConsumerThreads) sh.row_hist[slot][r][i] = 0u;   // for the slot's next unit
     consumer_sync();
     if (phase != nullptr) phase[2] += clock64() - stamp;
 }
@@ -892,6 +1012,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
 
+    for (int i = static_cast<int>(threadIdx.x); i < 2 * kBlockQ * kScoreBins / 2; i += kThreads)
+        (&sh.row_hist[0][0][0])[i] = 0u;
     if (threadIdx.x == 0) {
         for (int i = 0; i < kKvStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
@@ -1150,6 +1272,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
             keep_in_register(score_slots);
             keep_in_register(id_slots);
+            const uint32_t hist_slots = smem_u32(&sh.row_hist[slot][own_r][0]);
             int count = 0;
             // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
             // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
@@ -1159,9 +1282,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
             float threshold = row.threshold;
             // the compiler would otherwise re-derive these per tile from thread and unit indices
+            unsigned threshold_bits = ordered_bits(threshold);
             keep_in_register(row_lo);
             keep_in_register(row_span);
             keep_in_register(threshold);
+            keep_in_register(threshold_bits);
 
             // head weights of this thread's column pairs
             uint64_t w[8];
@@ -1247,8 +1372,14 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const unsigned ballot = __ballot_sync(0xffffffffu, active);
                 const int position = count + __popc(ballot & ((1u << lane) - 1u));
                 count += __popc(ballot);
+                const uint32_t score_bits = ordered_bits(score);
+                if (MODE == kModeTopK && active) {
+                    // one more candidate in its bin of the row's score histogram (16-bit counters)
+                    const int bin = score_bin(score_bits - threshold_bits);
+                    red_shared_add_u32(hist_slots + 4u * static_cast<uint32_t>(bin >> 1), 1u << ((bin & 1) * 16));
+                }
                 if (active && position < kSegCap) {
-                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
+                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), score_bits);
                     // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
                     st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
                 }

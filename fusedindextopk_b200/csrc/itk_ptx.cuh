@@ -127,6 +127,11 @@ __device__ __forceinline__ void st_shared_u16(uint32_t address, uint32_t value) 
     asm volatile("st.shared.u16 [%0], %1;" ::"r"(address), "h"(static_cast<uint16_t>(value)) : "memory");
 }
 
+// Shared-memory add without a return value.
+__device__ __forceinline__ void red_shared_add_u32(uint32_t address, uint32_t value) {
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
+}
+
 // ------------------------------------------------------------------ TMA
 
 // Tiled 2-D load of one box into this CTA's shared memory; completion is
