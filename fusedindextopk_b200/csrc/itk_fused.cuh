@@ -74,25 +74,22 @@ constexpr int kTmemColumns = kAccBuffers * kUmmaN;  // 512 = all of TMEM
 constexpr int kTopK = 2048;
 
 constexpr int kSegments = 4;                   // one per TMEM lane quarter: segment = (key >> 5) & 3
-constexpr int kSegCap = 640;                   // shared-memory candidates per (row, segment)
-constexpr int kRowCap = kSegments * kSegCap;   // 2560
+constexpr int kSegCap = 1280;                  // shared-memory candidates per (row, segment)
+constexpr int kRowCap = kSegments * kSegCap;   // 5120
 constexpr int kSpillSegCap = 1408;             // global spill entries per (row, segment)
 constexpr int kSpillRow = kSegments * kSpillSegCap;  // 5632 u64 per row
 constexpr int kRepairChunk = 16384;
 
-// Warps 0-3: TMA producer, UMMA issuer, two consumer warps; warps 4-19: epilogue; warps 20-23: consumers.
-constexpr int kThreads = 768;
+// Warp 0: TMA producer; warp 1: UMMA issuer; warps 2-3: idle (they complete the first warpgroup);
+// warps 4-19: epilogue and per-row selection.  65536 / 640 rounded down to the allocation unit of 8
+// gives every thread 96 registers.
+constexpr int kThreads = 640;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kEpilogueThreads = 512;
 constexpr int kEpilogueWarps = kEpilogueThreads / 32;
-// 65536 / 768 rounded down to the allocation unit of 8 gives every thread 80 registers.  The pool that
-// setmaxnreg redistributes is what the CTA got at launch (768 x 80), not the whole register file, and
-// no split in units of 8 per warpgroup suits both the epilogue and the consumers, so the budget is uniform.
-constexpr int kConsumerThreads = 192;
-constexpr int kConsumerWarps = kConsumerThreads / 32;
-constexpr int kRadixHists = kConsumerWarps / 2;
 constexpr int kScoreBins = 256;
-constexpr int kBinListCap = 512;
+constexpr int kBinListCap = 64;     // scores of the histogram bin that holds the cutoff; more: radix fallback
+constexpr int kRankDirect = 48;    // lists up to this size are ranked without a second histogram level
 
 constexpr uint32_t kQBytes = kUmmaN * kHeadDim;       // 32768
 constexpr uint32_t kKvBytes = kTileKeys * kHeadDim;   // 16384
@@ -111,7 +108,7 @@ constexpr int kTraceFields = 32;
 #endif
 constexpr int kTraceMmaTotal = 0, kTraceMmaWaitAcc = 1, kTraceMmaWaitKv = 2, kTraceMmaWaitQ = 3, kTraceMmaTiles = 4;
 constexpr int kTraceTmaTotal = 8, kTraceTmaWaitKv = 9, kTraceTmaWaitQ = 10;
-constexpr int kTraceEpiTotal = 12, kTraceEpiWaitAcc = 13, kTraceEpiWaitFree = 14, kTraceEpiWaitW = 15;  // +4 for warpgroup 1
+constexpr int kTraceEpiTotal = 12, kTraceEpiWaitAcc = 13, kTraceEpiSelect = 14, kTraceEpiWaitW = 15;  // +4 for query row 1
 constexpr int kTraceConTotal = 20, kTraceConWaitReady = 21, kTraceConSelect = 22, kTraceConUnits = 23;
 constexpr int kTraceSm = 24, kTraceNsBegin = 25, kTraceNsEnd = 26;
 
@@ -150,31 +147,28 @@ struct FusedParams {
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
 };
 
+// Per-row scratch of the selection.
+struct RowSelect {
+    int hist[256];                      // second-level histogram / digit histogram of the radix fallback
+    uint32_t bin_scores[kBinListCap];   // the scores of the histogram bin that holds the cutoff
+    int position;     // next free output position of the row
+    int bin_count;
+    int tickets;
+    int bin;          // radix fallback: digit of the round
+    int above;
+    uint32_t reference;
+    uint32_t differing;
+};
+
 struct __align__(16) FusedShared {
     float weights[2][kBlockQ * kHeads];
-    uint32_t cand_scores[2][kBlockQ][kRowCap];
-    uint16_t cand_ids[2][kBlockQ][kRowCap];
-    int counts[2][kBlockQ][kSegments];
-    // Score histogram of every candidate row, filled by the epilogue as it finds the candidates:
+    uint32_t cand_scores[kBlockQ][kRowCap];
+    uint16_t cand_ids[kBlockQ][kRowCap];
+    int counts[kBlockQ][kSegments];
+    // Score histogram of every row's candidates, filled by the epilogue as it finds them:
     // kScoreBins bins of the distance to the row threshold, two 16-bit counters per word.
-    uint32_t row_hist[2][kBlockQ][kScoreBins / 2];
-    // The selection's scratch: the scores of the bin that holds the cutoff or, when that bin is too
-    // full, the digit histograms of the radix selection (one per pair of consumer warps).
-    union {
-        int hist[kRadixHists][256];
-        uint32_t bin_scores[kBinListCap];
-    };
-    int bin_count;
-    int warp_greater[kConsumerWarps];
-    int warp_equal[kConsumerWarps];
-    uint32_t sel_ref;
-    uint32_t sel_or;
-    int sel_bin;
-    int sel_greater;
-    int sel_failed;
-    int sel_total;
-    int sel_gcount;
-    int sel_ecount;
+    uint32_t row_hist[kBlockQ][kScoreBins / 2];
+    RowSelect select[kBlockQ];
     uint32_t tmem_base;
     int abort;
     uint64_t kv_full[kKvStages];
@@ -184,8 +178,7 @@ struct __align__(16) FusedShared {
     uint64_t w_full[2];
     uint64_t w_empty[2];
     uint64_t acc_empty[kAccBuffers];
-    uint64_t cand_ready[2];
-    uint64_t cand_free[2];
+    uint64_t row_bar[kBlockQ];       // barrier of the four epilogue warps of a query row
 };
 
 constexpr size_t kSmemTileBytes = kQBytes + kKvStages * kKvBytes;
@@ -273,11 +266,47 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
 
 // ------------------------------------------------------------------ consumer helpers
 
-__device__ __forceinline__ void consumer_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+// ------------------------------------------------------------------ per-row selection
+
+// The four epilogue warps that score one query row (one per TMEM lane quarter) also select its
+// Top-K when the unit's last tile is done: 128 threads per row, the four rows of a unit side by side.
+constexpr int kRowThreads = 128;
+constexpr uint32_t kRowParkNs = 40;   // the row barrier waits are short: the four warps work in step
+
+// Barrier of the four warps of one query row: an mbarrier that the 128 threads arrive on and then
+// wait for, so that the wait is bounded like every other wait of the kernel.  When the limit
+// expires (or another role already gave up) the abort flag is set and the call returns as if the
+// barrier had completed: the results are garbage then, but every later wait sees the flag, the
+// kernel ends and the host reads the failure from the status word.
+struct RowBarrier {
+    uint64_t* bar;
+    uint32_t phase;
+    volatile int* abort_flag;
+    long long* lap;        // diagnostic builds: cycle counters of the selection steps (else null)
+    long long lap_start;
+    int hw_id;
+};
+
+// Adds the cycles since the previous lap to counter `index` (diagnostic builds only).
+__device__ __forceinline__ void lap(RowBarrier& rb, int index) {
+    if (rb.lap != nullptr) {
+        const long long now = clock64();
+        rb.lap[index] += now - rb.lap_start;
+        rb.lap_start = now;
+    }
 }
 
-// Key index of shared-memory candidate `packed` stored in segment `segment`.
+__device__ __forceinline__ void row_sync(RowBarrier& rb) {
+#ifdef ITK_ROW_BARSYNC
+    asm volatile("bar.sync %0, %1;" ::"r"(rb.hw_id), "n"(kRowThreads) : "memory");
+#else
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);   // one arrival per warp
+    if (!mbar_wait<kHotWait>(rb.bar, rb.phase & 1u, rb.abort_flag)) *rb.abort_flag = 1;
+    ++rb.phase;
+#endif
+}
+
 __device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
     return static_cast<int>(((packed >> 5) << 7) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
 }
@@ -291,250 +320,210 @@ __device__ __forceinline__ uint16_t encode_key(int key) {
 __device__ __forceinline__ int warp_reserve(int* counter, bool active, int lane) {
     const unsigned mask = __ballot_sync(0xffffffffu, active);
     if (mask == 0u) return -1;
-    const int leader = __ffs(static_cast<int>(mask)) - 1;
+    const int leader = __ffs(mask) - 1;
     int base = 0;
     if (lane == leader) base = atomicAdd(counter, __popc(mask));
     base = __shfl_sync(0xffffffffu, base, leader);
     return active ? base + __popc(mask & ((1u << lane) - 1u)) : -1;
 }
 
-// The view the consumer has of one row's candidates: counted shared-memory
-// segments plus the row's spill region in global memory.
-struct RowCandidates {
-    const uint32_t* scores;   // [kRowCap]
-    const uint16_t* ids;      // [kRowCap]
-    const int* counts;        // [kSegments], may exceed the capacities
-    const uint64_t* spill;    // [kSegments][kSpillSegCap], null when the mode has no spill
+// The view a warp has of the candidates it owns during the selection: the segment it filled itself
+// (its TMEM lane quarter) and that segment's spill region in global memory.
+struct RowView {
+    const uint32_t* scores;        // [kSegCap] of the warp's segment
+    const uint16_t* ids;           // [kSegCap]
+    const uint64_t* spill;         // [kSpillSegCap] of the warp's segment
+    int in_smem;                   // candidates of the segment in shared memory
+    int in_spill;                  // ... and in the spill region
+    int segment;
 };
 
-// Every consumer thread keeps "its" candidates of the row in registers for the whole
-// selection, so the radix rounds touch neither shared nor global memory for them:
-//   * shared-memory candidate i of a segment belongs to thread i % 192, slot i / 192
-//     (at most kSegCap / 192 rounded up = 4 slots per segment, 16 in all);
-//   * spill entry e (the segments' spill regions concatenated) belongs to thread e % 192,
-//     slot e / 192, for the first 192 * kSpillRegs entries; later ones stay in global memory
-//     and are re-read in every pass (only when a threshold is far too low).
-constexpr int kSmemSlots = (kSegCap + kConsumerThreads - 1) / kConsumerThreads;   // 4
-constexpr int kOwnSmem = kSegments * kSmemSlots;                                   // 16
-constexpr int kSpillRegs = 4;
-constexpr int kSpillCached = kSpillRegs * kConsumerThreads;
-
-struct OwnCandidates {
-    uint32_t smem_score[kOwnSmem];
-    uint32_t spill_score[kSpillRegs];
-    uint32_t spill_key[kSpillRegs];
-    uint32_t smem_live;               // bit j: smem_score[j] holds a candidate
-    uint32_t spill_live;              // bit k: spill_score[k] holds a candidate
-    int spill_first[kSegments + 1];   // prefix sums of the per-segment spill counts
-};
-
-__device__ __forceinline__ uint64_t spill_entry(const RowCandidates& c, const OwnCandidates& own, int e) {
-    int segment = 0;
-    int begin = 0;
-#pragma unroll
-    for (int i = 1; i < kSegments; ++i) {
-        if (e >= own.spill_first[i]) {
-            segment = i;
-            begin = own.spill_first[i];
-        }
-    }
-    return c.spill[segment * kSpillSegCap + (e - begin)];
+// Histogram bin of a candidate: the binary exponent of its distance to the row threshold (in value,
+// not in bit patterns: scores may straddle zero).  One bin per octave covers every float, so the
+// histogram needs no knowledge of the scale of the scores; the octave that holds the Top-K cutoff is
+// resolved by a second histogram over the next eight bits of the distance.
+__device__ __forceinline__ uint32_t distance_bits(uint32_t score_bits, float threshold) {
+    return __float_as_uint(ordered_to_float(score_bits) - threshold);   // >= +0 for every candidate
 }
 
-__device__ __forceinline__ void load_own(const RowCandidates& c, OwnCandidates& own, int ctid) {
-    own.smem_live = 0u;
-    own.spill_live = 0u;
-    own.spill_first[0] = 0;
-#pragma unroll
-    for (int s = 0; s < kSegments; ++s) {
-        const int count = c.counts[s];
-        const int in_smem = min(count, kSegCap);
-        const int spilled = c.spill == nullptr ? 0 : min(max(count - kSegCap, 0), kSpillSegCap);
-        own.spill_first[s + 1] = own.spill_first[s] + spilled;
-#pragma unroll
-        for (int k = 0; k < kSmemSlots; ++k) {
-            const int i = ctid + k * kConsumerThreads;
-            const bool live = i < in_smem;
-            own.smem_score[s * kSmemSlots + k] = live ? c.scores[s * kSegCap + i] : 0u;
-            own.smem_live |= live ? 1u << (s * kSmemSlots + k) : 0u;
-        }
-    }
-    const int total = own.spill_first[kSegments];
-#pragma unroll
-    for (int k = 0; k < kSpillRegs; ++k) {
-        const int e = ctid + k * kConsumerThreads;
-        uint64_t pair = 0ull;
-        if (e < total) {
-            pair = spill_entry(c, own, e);
-            own.spill_live |= 1u << k;
-        }
-        own.spill_score[k] = static_cast<uint32_t>(pair >> 32);
-        own.spill_key[k] = static_cast<uint32_t>(pair);
-    }
-}
-
-// visit(score) for every candidate this thread owns in registers.
+// visit(score) for every candidate of the calling lane (candidate i of the segment belongs to lane
+// i % 32).  The passes of a selection run once per unit, far apart in time, so their instructions
+// come from a cold instruction cache: they are kept as short rolled loops over shared memory rather
+// than unrolled passes over a register cache, which took several times longer.
+// Four candidates are loaded before the first is visited: a visit may contain a shared-memory atomic,
+// above which the compiler cannot move the next load, and a lone warp cannot hide a load per step.
+// Missing candidates are passed as the score 0, which is below every real score (finite scores map
+// to ordered bits above 0x00800000) and whose distance to a threshold is a NaN pattern that belongs
+// to no bin, so a visit needs no liveness test.
 template <typename Visit>
-__device__ __forceinline__ void for_own_scores(const OwnCandidates& own, Visit&& visit) {
-#pragma unroll
-    for (int j = 0; j < kOwnSmem; ++j)
-        if (own.smem_live >> j & 1u) visit(own.smem_score[j]);
-#pragma unroll
-    for (int k = 0; k < kSpillRegs; ++k)
-        if (own.spill_live >> k & 1u) visit(own.spill_score[k]);
-}
-
-// visit(pair) for the spill entries beyond the register cache, split over the threads.
-template <typename Visit>
-__device__ __forceinline__ void for_excess_spill(const RowCandidates& c, const OwnCandidates& own, int ctid,
-                                                 Visit&& visit) {
-    const int total = own.spill_first[kSegments];
-    for (int e = kSpillCached + ctid; e < total; e += kConsumerThreads) visit(spill_entry(c, own, e));
-}
-
-// Histogram bin of a candidate: its distance (in ordered score bits) to the row threshold on a
-// logarithmic scale, eight bins per octave.  Monotone in the score; the relative width of 1/8 keeps the
-// bin that holds the Top-K cutoff down to a small fraction of the candidates below the cutoff.
-__device__ __forceinline__ int score_bin(uint32_t distance) {
-    const uint32_t d = max(distance, 8u);
-    const int e = 31 - __clz(d);                         // 3 .. 31
-    return (e - 2) * 8 + static_cast<int>((d >> (e - 3)) & 7u);   // 8 .. 239
-}
-
-// Distances [lo, lo + width) that score_bin maps to `bin`.
-__device__ __forceinline__ void bin_range(int bin, uint32_t& lo, uint32_t& width) {
-    if (bin <= 8) {          // distances below 8 are clamped into bin 8
-        lo = 0u;
-        width = 9u;
-    } else {
-        const int e = (bin >> 3) + 2;
-        lo = (8u + static_cast<uint32_t>(bin & 7)) << (e - 3);
-        width = 1u << (e - 3);
+__device__ __forceinline__ void for_scores(const RowView& v, int lane, Visit&& visit) {
+    const uint32_t* scores = v.scores;
+    const int in_smem = v.in_smem;
+#pragma unroll 1
+    for (int i = lane; i < in_smem; i += 128) {
+        const uint32_t s0 = scores[i];
+        const uint32_t s1 = i + 32 < in_smem ? scores[i + 32] : 0u;
+        const uint32_t s2 = i + 64 < in_smem ? scores[i + 64] : 0u;
+        const uint32_t s3 = i + 96 < in_smem ? scores[i + 96] : 0u;
+        visit(s0);
+        visit(s1);
+        visit(s2);
+        visit(s3);
     }
+#pragma unroll 1
+    for (int e = lane; e < v.in_spill; e += 32) visit(static_cast<uint32_t>(v.spill[e] >> 32));
 }
 
-// Selection from the histogram that the epilogue filled: warp 0 finds the bin that holds the rank-th
-// largest score, all threads gather the scores of that bin (two instructions per candidate: the bin
-// is a range of scores), and warp 0 takes the exact cutoff among them bit by bit.  Returns false (and
-// leaves the outputs alone) when the bin holds more than kBinListCap scores; the caller then falls
-// back to the radix selection.  Called by all consumer threads; needs rank_in <= number of candidates.
-__device__ __forceinline__ bool bin_select(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own,
-                                           const uint32_t* row_hist, uint32_t threshold_bits, int ctid, int rank_in,
-                                           uint32_t& cutoff, int& equal_needed) {
-    const int lane = ctid & 31;
-    if (ctid < 32) {
-        // lane l owns bins 8l .. 8l+7; `above` = candidates in bins owned by higher lanes
-        int bins[8];
-        int mine = 0;
+// Lane l owns entries 8l .. 8l+7 of a 256-entry histogram (counts[j] = entry 8l + j).  Finds the
+// entry that holds the rank-th largest candidate, counting from the top: returns true in the lane
+// that owns it, with its index, the number of candidates above it and its own count.
+__device__ __forceinline__ bool find_rank(const int (&counts)[8], int lane, int rank, int& entry, int& above_out,
+                                          int& inside) {
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mine += counts[j];
+    int suffix = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_down_sync(0xffffffffu, suffix, offset);
+        if (lane + offset < 32) suffix += other;
+    }
+    int above = suffix - mine;
+    bool found = false;
+#pragma unroll
+    for (int j = 7; j >= 0; --j) {
+        const int through = above + counts[j];
+        if (above < rank && rank <= through) {
+            found = true;
+            entry = lane * 8 + j;
+            above_out = above;
+            inside = counts[j];
+        }
+        above = through;
+    }
+    return found;
+}
+
+// Warp-wide result of find_rank: every lane gets the values of the lane that found the entry.
+__device__ __forceinline__ void share_rank(bool found, int& entry, int& above, int& inside) {
+    const unsigned who = __ballot_sync(0xffffffffu, found);
+    const int source = __ffs(who) - 1;
+    entry = __shfl_sync(0xffffffffu, entry, source);
+    above = __shfl_sync(0xffffffffu, above, source);
+    inside = __shfl_sync(0xffffffffu, inside, source);
+}
+
+// Selection from the histogram that the epilogue filled while it found the candidates.  The octave
+// (of the distance to the threshold) that holds the rank-th largest score is read off that histogram;
+// the candidates of that octave are histogrammed again by the next eight bits of the distance; the
+// handful of scores in the sub-bin that holds the cutoff are gathered and ranked against one another.
+// The small steps (reading a histogram, ranking the list) are done by every warp redundantly, which
+// costs a few dozen instructions and saves a barrier and a broadcast each.  Returns false (outputs
+// untouched) when the last list holds more than kBinListCap scores (many equal or nearly equal
+// scores); the caller then falls back to the radix selection.  Called by the 128 threads of a row
+// after the barrier that publishes the row's counts; rs.hist and rs.bin_count are zero on entry;
+// needs rank_in <= number of candidates.
+__device__ __forceinline__ bool bin_select(RowSelect& rs, const RowView& v, const uint32_t* row_hist, float threshold,
+                                           RowBarrier& rb, int tid, int rank_in, uint32_t& cutoff,
+                                           int& equal_needed) {
+    const int lane = tid & 31;
+    int octave_entry, above, in_list;
+    {
+        int counts[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t word = row_hist[lane * 4 + j];
-            bins[2 * j] = static_cast<int>(word & 0xffffu);
-            bins[2 * j + 1] = static_cast<int>(word >> 16);
-            mine += bins[2 * j] + bins[2 * j + 1];
+            counts[2 * j] = static_cast<int>(word & 0xffffu);
+            counts[2 * j + 1] = static_cast<int>(word >> 16);
         }
-        int suffix = mine;
-#pragma unroll
-        for (int offset = 1; offset < 32; offset <<= 1) {
-            const int other = __shfl_down_sync(0xffffffffu, suffix, offset);
-            if (lane + offset < 32) suffix += other;
-        }
-        int above = suffix - mine;
-#pragma unroll
-        for (int j = 7; j >= 0; --j) {
-            const int through = above + bins[j];
-            if (above < rank_in && rank_in <= through) {
-                sh.sel_bin = lane * 8 + j;
-                sh.sel_greater = above;
-                sh.sel_total = bins[j];
-            }
-            above = through;
-        }
-        if (lane == 0) sh.bin_count = 0;
+        const bool found = find_rank(counts, lane, rank_in, octave_entry, above, in_list);
+        share_rank(found, octave_entry, above, in_list);
     }
-    consumer_sync();
-    const int in_bin = sh.sel_total;
-    const int need = rank_in - sh.sel_greater;       // how many of the bin's scores belong to the top rank_in
-    if (in_bin > kBinListCap) return false;
-    uint32_t lo, width;
-    bin_range(sh.sel_bin, lo, width);
-    const uint32_t base = threshold_bits + lo;       // the bin holds the scores base + [0, width)
-    const auto gather = [&](uint32_t score) {
-        const uint32_t offset = score - base;
-        if (offset < width) {
-            const int at = atomicAdd(&sh.bin_count, 1);
-            if (at < kBinListCap) sh.bin_scores[at] = offset;
-        }
-    };
-    for_own_scores(own, gather);
-    for_excess_spill(c, own, ctid, [&](uint64_t pair) { gather(static_cast<uint32_t>(pair >> 32)); });
-    consumer_sync();
-    if (ctid < 32) {
-        // the need-th largest offset of the list, most significant bit first: a bit is kept when at
-        // least `rank` of the offsets that agree with the prefix so far have it set
-        constexpr int kPerLane = kBinListCap / 32;
-        uint32_t own_offsets[kPerLane];
-        uint32_t live = 0u;
+    lap(rb, 1);
+    const uint32_t octave = static_cast<uint32_t>(octave_entry);
+    int sub_bin = -1;            // -1: the whole octave is the list
+    // octave 255 (infinite distances: the threshold is -inf) holds no usable order; the radix
+    // selection sorts such rows out
+    if (octave >= 255u) return false;
+    if (in_list > kRankDirect) {
+        // second level: the next eight bits of the distance inside the octave
+        for_scores(v, lane, [&](uint32_t score) {
+            const uint32_t d = distance_bits(score, threshold);
+            if (d >> 23 == octave) atomicAdd(&rs.hist[(d >> 15) & 255u], 1);
+        });
+        lap(rb, 8);
+        row_sync(rb);
+        lap(rb, 9);
+        int counts[8];
 #pragma unroll
-        for (int m = 0; m < kPerLane; ++m) {
-            const int i = lane + 32 * m;
-            own_offsets[m] = i < in_bin ? sh.bin_scores[i] : 0u;
-            live |= i < in_bin ? 1u << m : 0u;
+        for (int j = 0; j < 8; ++j) counts[j] = rs.hist[lane * 8 + j];
+        int above2 = 0;
+        const bool found = find_rank(counts, lane, rank_in - above, sub_bin, above2, in_list);
+        share_rank(found, sub_bin, above2, in_list);
+        above += above2;
+        lap(rb, 2);
+    }
+    if (in_list > kBinListCap) return false;
+    const int need = rank_in - above;       // how many of the list's scores belong to the top rank_in
+    // gather the list: the candidates whose distance starts with (octave) or (octave, sub-bin)
+    const int list_shift = sub_bin < 0 ? 23 : 15;
+    const uint32_t list_prefix = sub_bin < 0 ? octave : (octave << 8 | static_cast<uint32_t>(sub_bin));
+    for_scores(v, lane, [&](uint32_t score) {
+        if (distance_bits(score, threshold) >> list_shift == list_prefix) {
+            const int at = atomicAdd(&rs.bin_count, 1);
+            if (at < kBinListCap) rs.bin_scores[at] = score;
         }
-        const int bits = 32 - __clz(width - 1u | 1u);
-        uint32_t prefix = 0u, mask = bits == 32 ? 0u : 0xffffffffu << bits;
-        int rank = need;
+    });
+    lap(rb, 10);
+    row_sync(rb);
+    lap(rb, 3);
+    // The need-th largest of the list: the score with fewer than `need` scores above it and at least
+    // `need` scores above or equal to it.  Every warp ranks the whole list (two entries per lane).
+    uint32_t found_cutoff = 0u;
+    int found_equal = 0;
+    bool found = false;
 #pragma unroll 1
-        for (int bit = bits - 1; bit >= 0; --bit) {
-            const uint32_t probe = 1u << bit;
-            const uint32_t want = prefix | probe;
-            const uint32_t care = mask | probe;
-            int above = 0;
-#pragma unroll
-            for (int m = 0; m < kPerLane; ++m)
-                above += static_cast<int>(live >> m & 1u) & static_cast<int>((own_offsets[m] & care) == want);
-            above = __reduce_add_sync(0xffffffffu, above);
-            if (above >= rank) prefix |= probe;
-            else rank -= above;
-            mask |= probe;
+    for (int k = 0; k < kBinListCap / 32; ++k) {
+        const int i = lane + 32 * k;
+        const uint32_t mine = i < in_list ? rs.bin_scores[i] : 0u;
+        int greater = 0, equal = 0;
+#pragma unroll 4
+        for (int j = 0; j < in_list; ++j) {
+            const uint32_t other = rs.bin_scores[j];
+            greater += other > mine ? 1 : 0;
+            equal += other == mine ? 1 : 0;
         }
-        if (lane == 0) {
-            sh.sel_ref = base + prefix;
-            sh.sel_ecount = rank;      // offsets equal to the cutoff that still belong to the top rank_in
+        if (i < in_list && greater < need && need <= greater + equal) {
+            found = true;
+            found_cutoff = mine;
+            found_equal = need - greater;
         }
     }
-    consumer_sync();
-    cutoff = sh.sel_ref;
-    equal_needed = sh.sel_ecount;
+    const unsigned who = __ballot_sync(0xffffffffu, found);
+    const int source = __ffs(who) - 1;
+    cutoff = __shfl_sync(0xffffffffu, found_cutoff, source);
+    equal_needed = __shfl_sync(0xffffffffu, found_equal, source);
+    lap(rb, 4);
     return true;
 }
 
-// Radix selection over the ordered score bits of one row, up to 8 bits per round.
-// On return `cutoff` is the rank-th largest score and `equal_needed` the number of
-// candidates equal to it that belong to the top `rank_in`.  Needs rank_in <= number of
-// candidates.  Called by all consumer threads.  The leading bits that all candidates
-// share are found first and skipped; every warp counts into its own histogram, so
-// the only contention on the shared-memory atomics is inside a warp.
-__device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own,
-                                             int ctid, int rank_in, uint32_t& cutoff, int& equal_needed) {
-    const int lane = ctid & 31;
-    const int cwarp = ctid >> 5;
-    int* my_hist = sh.hist[cwarp % kRadixHists];
-    if (ctid == 0) {
-        int s = 0;
-        while (s < kSegments - 1 && c.counts[s] == 0) ++s;
-        sh.sel_ref = c.scores[s * kSegCap];   // any candidate of the row
-        sh.sel_or = 0u;
-    }
-    consumer_sync();
-    const uint32_t reference = sh.sel_ref;
+// Radix selection over the ordered score bits of one row, up to 8 bits per round: the fallback for
+// rows whose cutoff bin is too full (many equal or nearly equal scores).  On return `cutoff` is the
+// rank-th largest score and `equal_needed` the number of candidates equal to it that belong to the
+// top `rank_in`.  The leading bits that all candidates share are found first and skipped.
+__device__ __forceinline__ void radix_select(RowSelect& rs, const RowView& v, RowBarrier& rb, int tid, int rank_in,
+                                             uint32_t& cutoff, int& equal_needed) {
+    const int lane = tid & 31;
+    if (tid == 0) rs.differing = 0u;
+    if (lane == 0 && v.in_smem > 0) rs.reference = v.scores[0];   // any candidate of the row (a row has more than
+    row_sync(rb);                                                  // kTopK candidates here, so some segment has one)
+    const uint32_t reference = rs.reference;
     uint32_t differing = 0u;
-    for_own_scores(own, [&](uint32_t score) { differing |= score ^ reference; });
-    for_excess_spill(c, own, ctid, [&](uint64_t pair) { differing |= static_cast<uint32_t>(pair >> 32) ^ reference; });
+    for_scores(v, lane, [&](uint32_t score) { differing |= score ^ reference; });
     differing = __reduce_or_sync(0xffffffffu, differing);
-    if (lane == 0 && differing != 0u) atomicOr(&sh.sel_or, differing);
-    consumer_sync();
-    differing = sh.sel_or;
+    if (lane == 0 && differing != 0u) atomicOr(&rs.differing, differing);
+    row_sync(rb);
+    differing = rs.differing;
 
     int bits = differing == 0u ? 0 : 32 - __clz(differing);   // low bits in which candidates may differ
     uint32_t mask = bits == 32 ? 0u : 0xffffffffu << bits;
@@ -545,120 +534,118 @@ __device__ __forceinline__ void radix_select(FusedShared& sh, const RowCandidate
         const int width = min(8, bits);
         const int shift = bits - width;
         const uint32_t digit_mask = (1u << width) - 1u;
-        consumer_sync();   // the histograms are shared by two warps: nobody may still read the last round
-        if (cwarp < kRadixHists)
-            for (int bin = lane; bin < 256; bin += 32) my_hist[bin] = 0;
-        consumer_sync();
-        for_own_scores(own, [&](uint32_t score) {
-            if ((score & mask) == prefix) atomicAdd(&my_hist[(score >> shift) & digit_mask], 1);
+        for (int bin = tid; bin < 256; bin += kRowThreads) rs.hist[bin] = 0;
+        row_sync(rb);
+        for_scores(v, lane, [&](uint32_t score) {
+            if ((score & mask) == prefix) atomicAdd(&rs.hist[(score >> shift) & digit_mask], 1);
         });
-        for_excess_spill(c, own, ctid, [&](uint64_t pair) {
-            const uint32_t score = static_cast<uint32_t>(pair >> 32);
-            if ((score & mask) == prefix) atomicAdd(&my_hist[(score >> shift) & digit_mask], 1);
-        });
-        consumer_sync();
-        if (ctid < 32) {
-            // lane l owns bins 8l .. 8l+7 (summed over the warps' histograms); `above` =
-            // candidates in bins owned by higher lanes
+        row_sync(rb);
+        if (tid < 32) {
             int bins[8];
             int mine = 0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                int sum = 0;
-#pragma unroll
-                for (int w = 0; w < kRadixHists; ++w) sum += sh.hist[w][ctid * 8 + j];
-                bins[j] = sum;
-                mine += sum;
+                bins[j] = rs.hist[lane * 8 + j];
+                mine += bins[j];
             }
             int suffix = mine;
 #pragma unroll
             for (int offset = 1; offset < 32; offset <<= 1) {
                 const int other = __shfl_down_sync(0xffffffffu, suffix, offset);
-                if (ctid + offset < 32) suffix += other;
+                if (lane + offset < 32) suffix += other;
             }
             int above = suffix - mine;
 #pragma unroll
             for (int j = 7; j >= 0; --j) {
                 const int through = above + bins[j];
                 if (above < rank && rank <= through) {
-                    sh.sel_bin = ctid * 8 + j;
-                    sh.sel_greater = above;
+                    rs.bin = lane * 8 + j;
+                    rs.above = above;
                 }
                 above = through;
             }
         }
-        consumer_sync();
-        prefix |= static_cast<uint32_t>(sh.sel_bin) << shift;
-        rank -= sh.sel_greater;
+        row_sync(rb);
+        prefix |= static_cast<uint32_t>(rs.bin) << shift;
+        rank -= rs.above;
         mask |= digit_mask << shift;
         bits = shift;
+        row_sync(rb);   // everybody has read the round's result before the histogram is cleared again
     }
     cutoff = prefix;
     equal_needed = rank;
 }
 
 // Writes the selected candidates of one row: everything above `cutoff`, then `equal_needed` of the
-// candidates equal to it (any of them); with take_all every candidate.  Every thread counts its
-// candidates above the cutoff, a scan over the threads gives it a contiguous range of output
-// positions, and it writes its candidates there; the few candidates equal to the cutoff draw
-// tickets for the positions behind.
-__device__ __forceinline__ void emit_row(FusedShared& sh, const RowCandidates& c, const OwnCandidates& own, int ctid,
-                                         uint32_t cutoff, int equal_needed, int greater_total, bool take_all,
-                                         int32_t* out_ids, uint64_t* out_pairs) {
-    const int lane = ctid & 31;
-    const int cwarp = ctid >> 5;
-    const int total_spill = own.spill_first[kSegments];
+// candidates equal to it (any of them); cutoff 0 takes every candidate.  Every warp counts its
+// candidates above the cutoff, reserves that many output positions with one atomic add and fills
+// them in ballot order, 32 candidates at a time, so that the stores of a warp instruction fall into
+// a few sectors.  The few candidates equal to the cutoff draw tickets for the positions behind.
+// rs.position and rs.tickets must be 0 on entry (a row barrier before the call publishes that).
+__device__ __forceinline__ void emit_row(RowSelect& rs, const RowView& v, int lane, uint32_t cutoff, int equal_needed,
+                                         int greater_total, int32_t* out_ids, uint64_t* out_pairs,
+                                         RowBarrier* timer = nullptr) {
     int greater = 0;
-    const auto tally = [&](uint32_t score) { greater += (take_all || score > cutoff) ? 1 : 0; };
-    for_own_scores(own, tally);
-    for_excess_spill(c, own, ctid, [&](uint64_t pair) { tally(static_cast<uint32_t>(pair >> 32)); });
-    int inclusive = greater;
-#pragma unroll
-    for (int offset = 1; offset < 32; offset <<= 1) {
-        const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-        if (lane >= offset) inclusive += other;
-    }
-    if (lane == 31) sh.warp_greater[cwarp] = inclusive;
-    if (ctid == 0) sh.sel_ecount = 0;
-    consumer_sync();
-    int position = inclusive - greater;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) position += w < cwarp ? sh.warp_greater[w] : 0;
+    for_scores(v, lane, [&](uint32_t score) { greater += score > cutoff ? 1 : 0; });
+    greater = __reduce_add_sync(0xffffffffu, greater);
+    if (timer != nullptr) lap(*timer, 12);
+    int position = 0;
+    if (lane == 0 && greater > 0) position = atomicAdd(&rs.position, greater);
+    position = __shfl_sync(0xffffffffu, position, 0);
+    if (timer != nullptr) lap(*timer, 13);
+    const unsigned below = (1u << lane) - 1u;
     const auto write = [&](int at, uint32_t score, int key) {
         if (at >= kTopK) return;
         if (out_ids != nullptr) out_ids[at] = key;
         if (out_pairs != nullptr) out_pairs[at] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
     };
-    // `key()` is only evaluated for the candidates that are written
+    // One candidate per lane (score 0: none); `key()` is only evaluated for the candidates that are written.
     const auto place = [&](uint32_t score, auto&& key) {
-        if (take_all || score > cutoff) {
-            write(position++, score, key());
-        } else if (score == cutoff) {
-            const int ticket = atomicAdd(&sh.sel_ecount, 1);
+        const bool is_greater = score > cutoff;
+        const unsigned ballot = __ballot_sync(0xffffffffu, is_greater);
+        if (is_greater) {
+            write(position + __popc(ballot & below), score, key());
+        } else if (score == cutoff && cutoff != 0u) {
+            const int ticket = atomicAdd(&rs.tickets, 1);
             if (ticket < equal_needed) write(greater_total + ticket, score, key());
         }
+        position += __popc(ballot);
     };
+    {
+        // four candidates (score and id) are loaded before the first is placed, see for_scores
+        const uint32_t* scores = v.scores;
+        const uint16_t* ids = v.ids;
+        const int in_smem = v.in_smem, segment = v.segment;
+#pragma unroll 1
+        for (int base = 0; base < in_smem; base += 128) {
+            uint32_t score[4];
+            uint32_t id[4];
 #pragma unroll
-    for (int j = 0; j < kOwnSmem; ++j) {
-        if (own.smem_live >> j & 1u) {
-            const int segment = j / kSmemSlots;
-            const int i = ctid + (j % kSmemSlots) * kConsumerThreads;
-            place(own.smem_score[j], [&]() { return decode_key(c.ids[segment * kSegCap + i], segment); });
+            for (int k = 0; k < 4; ++k) {
+                const int i = base + 32 * k + lane;
+                const bool live = i < in_smem;
+                score[k] = live ? scores[i] : 0u;
+                id[k] = live ? ids[i] : 0u;
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (base + 32 * k < in_smem) place(score[k], [&]() { return decode_key(id[k], segment); });
+            }
         }
     }
-#pragma unroll
-    for (int k = 0; k < kSpillRegs; ++k) {
-        if (own.spill_live >> k & 1u) place(own.spill_score[k], [&]() { return static_cast<int>(own.spill_key[k]); });
-    }
-    for (int e = kSpillCached + ctid; e < total_spill; e += kConsumerThreads) {
-        const uint64_t pair = spill_entry(c, own, e);
+#pragma unroll 1
+    for (int base = 0; base < v.in_spill; base += 32) {
+        const int e = base + lane;
+        const uint64_t pair = e < v.in_spill ? v.spill[e] : 0ull;
         place(static_cast<uint32_t>(pair >> 32), [&]() { return static_cast<int>(static_cast<uint32_t>(pair)); });
     }
 }
 
-// Exact Top-2048 of one row from its candidates (kModeTopK consumer).
-__device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                 int slot, bool has_tiles, int ctid, long long* phase = nullptr) {
+// Exact Top-2048 of one row from its candidates.  Called by the 128 threads of row r after the
+// row's four segment counts are in shared memory and the row barrier has been passed; returns with
+// the row barrier passed again (the candidate buffers and the histogram may be reused).
+__device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
+                                                bool has_tiles, RowBarrier& rb, int tid) {
     const int row = u.row0 + r;
     const long long row_slot = static_cast<long long>(u.shard) * p.rows + row;
     const int start = max(__ldg(p.k_start + row), u.key_lo);
@@ -669,115 +656,100 @@ __device__ __forceinline__ void consume_topk_row(FusedShared& sh, const FusedPar
 
     if (out_pairs == nullptr && valid <= p.top_k_min_valid) {
         // every valid key is selected; no scores are needed
-        for (int i = ctid; i < kTopK; i += kConsumerThreads) out_ids[i] = i < valid ? start + i : -1;
-        if (ctid == 0) p.failure_flags[row_slot] = 0;
+        for (int i = tid; i < kTopK; i += kRowThreads) out_ids[i] = i < valid ? start + i : -1;
+        if (tid == 0) p.failure_flags[row_slot] = 0;
         return;
     }
+    const auto fill_empty = [&](int from) {
+        for (int i = from + tid; i < kTopK; i += kRowThreads) {
+            if (out_ids != nullptr) out_ids[i] = -1;
+            if (out_pairs != nullptr) out_pairs[i] = 0ull;
+        }
+    };
     if (!has_tiles) {
         // pairs requested but the row has no key in this shard
-        for (int i = ctid; i < kTopK; i += kConsumerThreads) {
-            if (out_ids != nullptr) out_ids[i] = -1;
-            out_pairs[i] = 0ull;
-        }
-        if (ctid == 0) {
+        fill_empty(0);
+        if (tid == 0) {
             p.failure_flags[row_slot] = 0;
             if (p.out_counts != nullptr) p.out_counts[row_slot] = 0;
         }
         return;
     }
 
-    RowCandidates c;
-    c.scores = sh.cand_scores[slot][r];
-    c.ids = sh.cand_ids[slot][r];
-    c.counts = sh.counts[slot][r];
-    c.spill = p.spill + row_slot * kSpillRow;
-
-    if (ctid == 0) {
-        int total = 0;
-        int overflow = 0;
-        for (int s = 0; s < kSegments; ++s) {
-            total += c.counts[s];
-            overflow |= c.counts[s] > kSegCap + kSpillSegCap;
-        }
-        const int wanted = min(valid, kTopK);
-        sh.sel_total = total;
-        sh.sel_failed = (overflow || total < wanted) ? 1 : 0;
-        sh.sel_gcount = 0;
-        sh.sel_ecount = 0;
+    RowSelect& rs = sh.select[r];
+    const int lane = tid & 31;
+    const int segment = tid >> 5;
+    int total = 0;
+    bool overflow = false;
+#pragma unroll
+    for (int s = 0; s < kSegments; ++s) {
+        total += sh.counts[r][s];
+        overflow = overflow || sh.counts[r][s] > kSegCap + kSpillSegCap;
     }
-    consumer_sync();
-    const int total = sh.sel_total;
-    const bool failed = sh.sel_failed != 0;
-    if (failed) {
-        for (int i = ctid; i < kTopK; i += kConsumerThreads) {
-            if (out_ids != nullptr) out_ids[i] = -1;
-            if (out_pairs != nullptr) out_pairs[i] = 0ull;
-        }
-        if (ctid == 0) {
+    RowView view;
+    view.segment = segment;
+    view.scores = sh.cand_scores[r] + segment * kSegCap;
+    view.ids = sh.cand_ids[r] + segment * kSegCap;
+    view.spill = p.spill + row_slot * kSpillRow + segment * kSpillSegCap;
+    view.in_smem = min(sh.counts[r][segment], kSegCap);
+    view.in_spill = min(max(sh.counts[r][segment] - kSegCap, 0), kSpillSegCap);
+    const int wanted = min(valid, kTopK);
+    uint32_t* row_hist = sh.row_hist[r];
+    if (overflow || total < wanted) {
+        // too many candidates for the buffers or too few for a full answer: the repair pass redoes the row
+        fill_empty(0);
+        if (tid == 0) {
             p.failure_flags[row_slot] = 1;
             if (p.out_counts != nullptr) p.out_counts[row_slot] = 0;
         }
-        for (int i = ctid; i < kScoreBins / 2; i += kConsumerThreads) sh.row_hist[slot][r][i] = 0u;
-        consumer_sync();
-        return;
-    }
-    OwnCandidates view;
-    long long stamp = phase != nullptr ? clock64() : 0;
-    load_own(c, view, ctid);
-    if (phase != nullptr) {
-        // the cached entries are only complete once their loads have returned
-        uint32_t touch = 0;
-#pragma unroll
-        for (int k = 0; k < kSpillRegs; ++k) touch |= view.spill_score[k];
-        if (touch == 0x80000001u) phase[3] += 1;
-        const long long now = clock64();
-        phase[0] += now - stamp;
-        stamp = now;
-    }
-    if (total <= kTopK) {
-        // only reachable when valid <= 2048 (threshold forced to -inf): take everything
-        emit_row(sh, c, view, ctid, 0u, 0, 0, true, out_ids, out_pairs);
-        for (int i = total + ctid; i < kTopK; i += kConsumerThreads) {
-            if (out_ids != nullptr) out_ids[i] = -1;
-            if (out_pairs != nullptr) out_pairs[i] = 0ull;
-        }
     } else {
-        uint32_t cutoff;
-        int equal_needed;
-        const float threshold = valid > kTopK ? __ldg(p.thresholds + row_slot) : __int_as_float(0xff800000);
-        if (!bin_select(sh, c, view, sh.row_hist[slot][r], ordered_bits(threshold), ctid, kTopK, cutoff, equal_needed))
-            radix_select(sh, c, view, ctid, kTopK, cutoff, equal_needed);
-        if (phase != nullptr) {
-            const long long now = clock64();
-            phase[1] += now - stamp;
-            stamp = now;
+        if (rb.lap != nullptr) rb.lap_start = clock64();
+        if (total <= kTopK) {
+            // only reachable when valid <= 2048 (threshold forced to -inf): take everything
+            emit_row(rs, view, lane, 0u, 0, 0, out_ids, out_pairs);
+            fill_empty(total);
+        } else {
+            uint32_t cutoff;
+            int equal_needed;
+            const float threshold = valid > kTopK ? __ldg(p.thresholds + row_slot) : __int_as_float(0xff800000);
+            if (!bin_select(rs, view, row_hist, threshold, rb, tid, kTopK, cutoff, equal_needed))
+                radix_select(rs, view, rb, tid, kTopK, cutoff, equal_needed);
+            emit_row(rs, view, lane, cutoff, equal_needed, kTopK - equal_needed, out_ids, out_pairs, &rb);
+            lap(rb, 11);
         }
-        emit_row(sh, c, view, ctid, cutoff, equal_needed, kTopK - equal_needed, false, out_ids, out_pairs);
+        if (tid == 0) {
+            p.failure_flags[row_slot] = 0;
+            if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
+        }
     }
-    if (ctid == 0) {
-        p.failure_flags[row_slot] = 0;
-        if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
+    for (int i = tid; i < kScoreBins / 2; i += kRowThreads) row_hist[i] = 0u;   // for the next unit
+    row_sync(rb);
+    // the selection's scratch is clean again for the row's next selection, whose first barrier
+    // (the one that publishes the counts) orders these stores before any use
+    for (int i = tid; i < 256; i += kRowThreads) rs.hist[i] = 0;
+    if (tid == 0) {
+        rs.position = 0;
+        rs.tickets = 0;
+        rs.bin_count = 0;
     }
-    for (int i = ctid; i < kScoreBins / 2; i += kConsumerThreads) sh.row_hist[slot][r][i] = 0u;   // for the slot's next unit
-    consumer_sync();
-    if (phase != nullptr) phase[2] += clock64() - stamp;
+    if (!(overflow || total < wanted) && total > kTopK) lap(rb, 6);
 }
 
-// Threshold of one row = rank-th largest valid sampled score (kModeSample consumer).
-// One warp per row, no block-level synchronisation: the warp walks the row's candidates in
-// shared memory once per score bit (most significant differing bit first), counts the
-// candidates that agree with the prefix found so far and have the bit set, and keeps or
-// clears the bit so that exactly rank-1 candidates stay above the prefix.
+// Threshold of one row = rank-th largest valid sampled score (kModeSample).  One warp per row, no
+// block-level synchronisation: the warp walks the row's candidates in shared memory once per score
+// bit (most significant differing bit first), counts the candidates that agree with the prefix found
+// so far and have the bit set, and keeps or clears the bit so that exactly rank-1 candidates stay
+// above the prefix.
 __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                     int slot, bool has_tiles, int lane) {
+                                                     bool has_tiles, int lane) {
     const int row = u.row0 + r;
     const int start = __ldg(p.k_start + row);
     const int end = __ldg(p.k_end + row);
     const float minus_inf = __int_as_float(0xff800000);
     float result = minus_inf;
     if (has_tiles && end - start > p.target_candidates) {
-        const uint32_t* scores = sh.cand_scores[slot][r];
-        const int* counts = sh.counts[slot][r];
+        const uint32_t* scores = sh.cand_scores[r];
+        const int* counts = sh.counts[r];
         int total = 0;
         bool overflow = false;
         uint32_t reference = 0u;
@@ -789,9 +761,9 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
         }
         if (!overflow && total >= p.sample_rank) {
             // candidate g of the row (segments concatenated) belongs to lane g % 32; the first
-            // kCached of a lane's candidates live in registers, the rest is re-read from shared
+            // kOwn of a lane's candidates live in registers, the rest is re-read from shared
             // memory four at a time (a single warp is latency-bound, so loads must overlap)
-            constexpr int kCached = 16;
+            constexpr int kOwn = 16;
             const int first1 = counts[0], first2 = first1 + counts[1], first3 = first2 + counts[2];
             const auto fetch = [&](int g) -> uint32_t {
                 int segment = 0, begin = 0;
@@ -800,17 +772,17 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
                 if (g >= first3) { segment = 3; begin = first3; }
                 return scores[segment * kSegCap + (g - begin)];
             };
-            uint32_t own[kCached];
+            uint32_t own[kOwn];
             uint32_t live = 0u;
 #pragma unroll
-            for (int m = 0; m < kCached; ++m) {
+            for (int m = 0; m < kOwn; ++m) {
                 const int g = lane + 32 * m;
                 own[m] = g < total ? fetch(g) : 0u;
                 live |= g < total ? 1u << m : 0u;
             }
             const auto for_rest = [&](auto&& visit) {
 #pragma unroll 1
-                for (int g = lane + 32 * kCached; g < total; g += 128) {
+                for (int g = lane + 32 * kOwn; g < total; g += 128) {
                     uint32_t x[4];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) x[k] = g + 32 * k < total ? fetch(g + 32 * k) : 0u;
@@ -820,7 +792,7 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
             };
             uint32_t differing = 0u;
 #pragma unroll
-            for (int m = 0; m < kCached; ++m) differing |= (live >> m & 1u) ? own[m] ^ reference : 0u;
+            for (int m = 0; m < kOwn; ++m) differing |= (live >> m & 1u) ? own[m] ^ reference : 0u;
             for_rest([&](bool valid, uint32_t score) { differing |= valid ? score ^ reference : 0u; });
             differing = __reduce_or_sync(0xffffffffu, differing);
             const int bits = differing == 0u ? 0 : 32 - __clz(differing);
@@ -834,7 +806,7 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
                 const uint32_t care = mask | probe;
                 int above = 0;
 #pragma unroll
-                for (int m = 0; m < kCached; ++m)
+                for (int m = 0; m < kOwn; ++m)
                     above += static_cast<int>(live >> m & 1u) & static_cast<int>((own[m] & care) == want);
                 for_rest([&](bool valid, uint32_t score) {
                     above += static_cast<int>(valid) & static_cast<int>((score & care) == want);
@@ -1012,8 +984,14 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
 
-    for (int i = static_cast<int>(threadIdx.x); i < 2 * kBlockQ * kScoreBins / 2; i += kThreads)
-        (&sh.row_hist[0][0][0])[i] = 0u;
+    for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * kScoreBins / 2; i += kThreads)
+        (&sh.row_hist[0][0])[i] = 0u;
+    for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * 256; i += kThreads) sh.select[i >> 8].hist[i & 255] = 0;
+    if (threadIdx.x < kBlockQ) {
+        sh.select[threadIdx.x].position = 0;
+        sh.select[threadIdx.x].tickets = 0;
+        sh.select[threadIdx.x].bin_count = 0;
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kKvStages; ++i) {
             mbar_init(&sh.kv_full[i], 1);
@@ -1021,12 +999,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         }
         mbar_init(&sh.q_full, 1);
         mbar_init(&sh.q_empty, 1);
+        for (int i = 0; i < kBlockQ; ++i) mbar_init(&sh.row_bar[i], kRowThreads / 32);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh.w_full[i], 1);
             mbar_init(&sh.w_empty[i], kEpilogueWarps);
             mbar_init(&sh.acc_empty[i], kEpilogueWarps);
-            mbar_init(&sh.cand_ready[i], kEpilogueWarps);
-            mbar_init(&sh.cand_free[i], 1);
         }
         sh.abort = 0;
         fence_mbar_init();
@@ -1164,69 +1141,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) atomicOr(p.status, kStatusWaitExpired);
         }
-    } else {
-        // ============================================================ Top-K / threshold consumers
-        if (MODE != kModeRepair) {
-            const int cwarp = warp < kEpilogueWarp0 ? warp - 2 : warp - (kEpilogueWarp0 + kEpilogueWarps) + 2;   // warps 2,3,20..23 -> 0..5
-            const int ctid = cwarp * 32 + lane;
-            int unit_iter = 0;
-            bool ok = true;
-            long long wait_ready = 0, select_cycles = 0;
-            long long phase[4] = {0, 0, 0, 0};
-            const long long role_begin = DIAG ? clock64() : 0;
-            if (DIAG && p.trace != nullptr && ctid == 0)
-                p.trace[static_cast<long long>(blockIdx.x) * kTraceFields + kTraceNsBegin] = global_timer_ns();
-            for (int iter = 0; ok; ++iter) {
-                Unit u;
-                if (!load_unit<MODE>(p, iter, u)) break;
-                const bool has_tiles = u.tile_end > u.tile_begin;
-                const int slot = unit_iter & 1;
-                if (has_tiles) {
-                    // one thread polls; the others sleep in the named barrier until it is through
-                    ITK_BEAT(10 + 100 * unit_iter);
-                    if (ctid == 0) {
-                        const bool got = timed_wait<DIAG>(&sh.cand_ready[slot], (unit_iter >> 1) & 1, abort_flag, wait_ready);
-                        sh.sel_failed = got ? 0 : -1;
-                    }
-                    consumer_sync();
-                    ok = sh.sel_failed != -1;
-                    consumer_sync();
-                    if (!ok) break;
-                    ITK_BEAT(11 + 100 * unit_iter);
-                }
-                const long long select_begin = DIAG ? clock64() : 0;
-                if (MODE == kModeTopK) {
-                    for (int r = 0; r < u.nrows; ++r) {
-                        if (DIAG && (p.debug_skip & 1)) continue;
-#if ITK_EXPERIMENT >= 6
-                        continue;
-#endif
-                        consume_topk_row(sh, p, u, r, slot, has_tiles, ctid, DIAG ? phase : nullptr);
-                    }
-                } else if (cwarp < u.nrows) {
-                    sample_threshold_row(sh, p, u, cwarp, slot, has_tiles, lane);   // one warp per row
-                }
-                ITK_BEAT(12 + 100 * unit_iter);
-                if (DIAG) select_cycles += clock64() - select_begin;
-                if (has_tiles) {
-                    consumer_sync();
-                    if (ctid == 0) mbar_arrive(&sh.cand_free[slot]);
-                    ++unit_iter;
-                }
-            }
-            if (DIAG && p.trace != nullptr && ctid == 0) {
-                long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
-                trace[kTraceConTotal] = clock64() - role_begin;
-                trace[kTraceConWaitReady] = wait_ready;
-                trace[kTraceConSelect] = select_cycles;
-                trace[kTraceConUnits] = unit_iter;
-                trace[27] = phase[0];   // spill caching
-                trace[28] = phase[1];   // radix rounds
-                trace[29] = phase[2];   // emit
-                trace[kTraceNsEnd] = global_timer_ns();
-            }
-            if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
-        }
     }
     } else {
         // ============================================================ epilogue
@@ -1251,28 +1165,47 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
-        long long wait_acc = 0, wait_free = 0, wait_w = 0;
+        long long wait_acc = 0, wait_w = 0, select_cycles = 0;
         const long long role_begin = DIAG ? clock64() : 0;
+        if (DIAG && p.trace != nullptr && ew == 0 && lane == 0)
+            p.trace[static_cast<long long>(blockIdx.x) * kTraceFields + kTraceNsBegin] = global_timer_ns();
+        // What the row's four warps do when the unit's candidates are complete (or the unit has no tile
+        // at all): exact Top-K of the row, or its sampled threshold.  All four warps of a row call it.
+        long long laps[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+        RowBarrier rb{&sh.row_bar[own_r], 0u, abort_flag, DIAG ? laps : nullptr, 0, own_r + 1};
+        const auto finish_row = [&](const Unit& u, bool has_tiles) {
+            const long long begin = DIAG ? clock64() : 0;
+            if (own_r < u.nrows) {
+                if (MODE == kModeTopK) {
+#if ITK_EXPERIMENT < 6
+                    if (!(DIAG && (p.debug_skip & 1))) select_topk_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
+#endif
+                } else if (MODE == kModeSample) {
+                    if (quarter == 0) sample_threshold_row(sh, p, u, own_r, has_tiles, lane);
+                }
+            }
+            if (MODE == kModeSample) row_sync(rb);   // the row's buffers may be written again
+            if (DIAG) select_cycles += clock64() - begin;
+        };
         for (int iter = 0; ok; ++iter) {
             Unit u;
             if (!load_unit<MODE>(p, iter, u)) break;
-            if (u.tile_end == u.tile_begin) continue;
-            const int slot = unit_iter & 1;
-            const uint32_t use_parity = (unit_iter >> 1) & 1;
-            if (MODE != kModeRepair) {
-                ok = warp_wait<DIAG>(&sh.cand_free[slot], use_parity ^ 1, abort_flag, lane, wait_free);
-                if (!ok) break;
+            if (u.tile_end == u.tile_begin) {
+                finish_row(u, false);
+                continue;
             }
+            const int slot = unit_iter & 1;   // weight buffer of the unit
+            const uint32_t use_parity = (unit_iter >> 1) & 1;
             ok = warp_wait<DIAG>(&sh.w_full[slot], use_parity, abort_flag, lane, wait_w);
             if (!ok) break;
             ITK_BEAT(11 + 100000 * unit_iter);
 
             // candidate segment of (row, quarter) and the number of candidates in it (warp-uniform)
-            uint32_t score_slots = smem_u32(&sh.cand_scores[slot][own_r][quarter * kSegCap]);
-            uint32_t id_slots = smem_u32(&sh.cand_ids[slot][own_r][quarter * kSegCap]);
+            uint32_t score_slots = smem_u32(&sh.cand_scores[own_r][quarter * kSegCap]);
+            uint32_t id_slots = smem_u32(&sh.cand_ids[own_r][quarter * kSegCap]);
             keep_in_register(score_slots);
             keep_in_register(id_slots);
-            const uint32_t hist_slots = smem_u32(&sh.row_hist[slot][own_r][0]);
+            const uint32_t hist_slots = smem_u32(&sh.row_hist[own_r][0]);
             int count = 0;
             // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
             // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
@@ -1282,11 +1215,9 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
             float threshold = row.threshold;
             // the compiler would otherwise re-derive these per tile from thread and unit indices
-            unsigned threshold_bits = ordered_bits(threshold);
             keep_in_register(row_lo);
             keep_in_register(row_span);
             keep_in_register(threshold);
-            keep_in_register(threshold_bits);
 
             // head weights of this thread's column pairs
             uint64_t w[8];
@@ -1375,8 +1306,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const uint32_t score_bits = ordered_bits(score);
                 if (MODE == kModeTopK && active) {
                     // one more candidate in its bin of the row's score histogram (16-bit counters)
-                    const int bin = score_bin(score_bits - threshold_bits);
-                    red_shared_add_u32(hist_slots + 4u * static_cast<uint32_t>(bin >> 1), 1u << ((bin & 1) * 16));
+                    const uint32_t bin = __float_as_uint(ordered_to_float(score_bits) - threshold) >> 23;
+                    red_shared_add_u32(hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
                 }
                 if (active && position < kSegCap) {
                     st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), score_bits);
@@ -1472,20 +1403,34 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) break;
             if (MODE != kModeRepair) {
-                __syncwarp();   // every lane's candidates are written before lane 0 publishes the segment
-                if (lane == 0) {
-                    sh.counts[slot][own_r][quarter] = count;
-                    mbar_arrive(&sh.cand_ready[slot]);
-                }
+                if (lane == 0) sh.counts[own_r][quarter] = count;
+                row_sync(rb);   // the four segments of the row are complete and counted
             }
+            finish_row(u, true);
             ++unit_iter;
         }
         if (DIAG && p.trace != nullptr && quarter == 0 && own_r < 2 && lane == 0) {
             long long* trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields + 4 * own_r;
             trace[kTraceEpiTotal] = clock64() - role_begin;
             trace[kTraceEpiWaitAcc] = wait_acc;
-            trace[kTraceEpiWaitFree] = wait_free;
+            trace[kTraceEpiSelect] = select_cycles;
             trace[kTraceEpiWaitW] = wait_w;
+            if (own_r == 0) {
+                long long* cta_trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
+                cta_trace[27] = laps[0];   // candidate caching
+                cta_trace[28] = laps[1];   // octave from the histogram
+                cta_trace[29] = laps[2];   // second-level histogram
+                cta_trace[30] = laps[3];   // list gathering
+                cta_trace[31] = laps[4];   // list ranking
+                cta_trace[20] = laps[11];  // emission: placing
+                cta_trace[22] = laps[12];  // emission: counting
+                cta_trace[23] = laps[13];  // emission: position reservation
+                cta_trace[21] = laps[6];   // clean-up and last barrier
+                cta_trace[5] = laps[8];    // second level: histogram pass
+                cta_trace[6] = laps[9];    // second level: barrier
+                cta_trace[7] = laps[10];   // gathering pass
+                cta_trace[kTraceNsEnd] = global_timer_ns();
+            }
         }
         if (!ok && lane == 0) atomicOr(p.status, kStatusWaitExpired);
     }
