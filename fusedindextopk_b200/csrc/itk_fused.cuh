@@ -109,7 +109,6 @@ constexpr int kTraceFields = 32;
 constexpr int kTraceMmaTotal = 0, kTraceMmaWaitAcc = 1, kTraceMmaWaitKv = 2, kTraceMmaWaitQ = 3, kTraceMmaTiles = 4;
 constexpr int kTraceTmaTotal = 8, kTraceTmaWaitKv = 9, kTraceTmaWaitQ = 10;
 constexpr int kTraceEpiTotal = 12, kTraceEpiWaitAcc = 13, kTraceEpiSelect = 14, kTraceEpiWaitW = 15;  // +4 for query row 1
-constexpr int kTraceConTotal = 20, kTraceConWaitReady = 21, kTraceConSelect = 22, kTraceConUnits = 23;
 constexpr int kTraceSm = 24, kTraceNsBegin = 25, kTraceNsEnd = 26;
 
 struct FusedParams {
@@ -271,10 +270,10 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
 // The four epilogue warps that score one query row (one per TMEM lane quarter) also select its
 // Top-K when the unit's last tile is done: 128 threads per row, the four rows of a unit side by side.
 constexpr int kRowThreads = 128;
-constexpr uint32_t kRowParkNs = 40;   // the row barrier waits are short: the four warps work in step
 
-// Barrier of the four warps of one query row: an mbarrier that the 128 threads arrive on and then
-// wait for, so that the wait is bounded like every other wait of the kernel.  When the limit
+// Barrier of the four warps of one query row: an mbarrier that the four warps arrive on and all
+// 128 threads then poll, so that the wait is bounded like every other wait of the kernel (the waits
+// are short: the four warps work in step, and nothing else wants the issue slots meanwhile).  When the limit
 // expires (or another role already gave up) the abort flag is set and the call returns as if the
 // barrier had completed: the results are garbage then, but every later wait sees the flag, the
 // kernel ends and the host reads the failure from the status word.
@@ -284,7 +283,6 @@ struct RowBarrier {
     volatile int* abort_flag;
     long long* lap;        // diagnostic builds: cycle counters of the selection steps (else null)
     long long lap_start;
-    int hw_id;
 };
 
 // Adds the cycles since the previous lap to counter `index` (diagnostic builds only).
@@ -297,14 +295,10 @@ __device__ __forceinline__ void lap(RowBarrier& rb, int index) {
 }
 
 __device__ __forceinline__ void row_sync(RowBarrier& rb) {
-#ifdef ITK_ROW_BARSYNC
-    asm volatile("bar.sync %0, %1;" ::"r"(rb.hw_id), "n"(kRowThreads) : "memory");
-#else
     __syncwarp();
     if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);   // one arrival per warp
     if (!mbar_wait<kHotWait>(rb.bar, rb.phase & 1u, rb.abort_flag)) *rb.abort_flag = 1;
     ++rb.phase;
-#endif
 }
 
 __device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
@@ -878,53 +872,6 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
     return state;
 }
 
-// Filter decision for a tile that is not known to lie inside the row's key range (first and last
-// tiles of a row, every tile of the sample and repair modes, diagnostic builds).  Kept out of line so
-// that the interior-tile path of the epilogue stays a handful of instructions; the row parameters are
-// re-read here instead of living in registers across the tile loop.  Repair mode stores the dense
-// pair and returns false.
-template <int MODE, bool DIAG>
-__device__ __noinline__ bool boundary_filter(const FusedParams& p, int row0, int nrows, int shard, int unit_key_lo,
-                                             int unit_key_hi, int r, int key, int range_key, float score) {
-    const RowState row = load_row_state<MODE>(p, row0, nrows, shard, unit_key_lo, unit_key_hi, r);
-    const bool key_ok = key < p.keys;
-    const bool in_range = key_ok && range_key >= row.lo && range_key < row.hi;
-    if (DIAG) {
-        if (r < nrows && key_ok && p.diag_logits != nullptr) {
-            const bool shown = MODE == kModeSample ? true : in_range;
-            p.diag_logits[static_cast<long long>(row0 + r) * p.diag_stride + key] =
-                shown ? score : __int_as_float(0xff800000);
-        }
-    }
-    if (MODE == kModeRepair) {
-        if (row.on && key_ok && key >= unit_key_lo && key < unit_key_hi) {
-            p.repair_pairs[row.slot * kRepairChunk + (key - unit_key_lo)] =
-                in_range ? pack_score_id(score, static_cast<uint32_t>(key)) : 0ull;
-        }
-        return false;
-    }
-    bool active = row.on && in_range;
-    if (DIAG && (p.debug_skip & 2)) active = false;
-    if (MODE == kModeTopK) active = active && score >= row.threshold;
-    else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
-    return active;
-}
-
-// Candidate stores of a tile whose candidates do not all fit the shared-memory segment any more:
-// positions below the capacity still go to shared memory, the next kSpillSegCap to the global spill.
-__device__ __noinline__ void store_with_overflow(const FusedParams& p, long long row_slot, int quarter, bool active,
-                                                 int position, float score, int key, uint32_t score_slots,
-                                                 uint32_t id_slots, uint32_t id) {
-    if (!active) return;
-    if (position < kSegCap) {
-        st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), ordered_bits(score));
-        st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), id);
-    } else if (p.spill != nullptr && position < kSegCap + kSpillSegCap) {
-        p.spill[row_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
-            pack_score_id(score, static_cast<uint32_t>(key));
-    }
-}
-
 // Lane 0 waits on the barrier, the warp then reconverges: one poller per warp.
 template <bool DIAG, uint32_t PARK_NS = kWaitParkNs>
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane,
@@ -1172,7 +1119,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         // What the row's four warps do when the unit's candidates are complete (or the unit has no tile
         // at all): exact Top-K of the row, or its sampled threshold.  All four warps of a row call it.
         long long laps[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-        RowBarrier rb{&sh.row_bar[own_r], 0u, abort_flag, DIAG ? laps : nullptr, 0, own_r + 1};
+        RowBarrier rb{&sh.row_bar[own_r], 0u, abort_flag, DIAG ? laps : nullptr, 0};
         const auto finish_row = [&](const Unit& u, bool has_tiles) {
             const long long begin = DIAG ? clock64() : 0;
             if (own_r < u.nrows) {
