@@ -931,6 +931,15 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
 
+    if (MODE == kModeRepair) {
+        // The usual case is that the fast path flagged no row: find that out with one parallel scan
+        // of the flags before any barrier, TMEM or descriptor is set up.
+        int any = 0;
+        const int flags = p.shards * p.rows;
+        for (int i = static_cast<int>(threadIdx.x); i < flags; i += kThreads) any |= p.failure_flags[i];
+        if (__syncthreads_or(any) == 0) return;
+    }
+
     for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * kScoreBins / 2; i += kThreads)
         (&sh.row_hist[0][0])[i] = 0u;
     for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * 256; i += kThreads) sh.select[i >> 8].hist[i & 255] = 0;

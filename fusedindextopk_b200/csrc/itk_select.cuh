@@ -97,6 +97,16 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
     const int tx = threadIdx.x;
     const int lane = tx & 31;
 
+    if (p.row_mask != nullptr) {
+        // The usual case of the repair graph is that no row is flagged: look at all of this CTA's
+        // rows at once instead of paying one dependent global load per row.
+        int any = 0;
+        for (int row = static_cast<int>(blockIdx.x) + tx * static_cast<int>(gridDim.x); row < p.rows;
+             row += kPairThreads * static_cast<int>(gridDim.x))
+            any |= p.row_mask[row];
+        if (__syncthreads_or(any) == 0) return;
+    }
+
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
         __syncthreads();
         if (tx == 0) {
