@@ -38,6 +38,12 @@ def fused_index_topk(*args, **kwargs):
     return implementation(*args, **kwargs)
 
 
+def fused_index_topk_host(*args, **kwargs):
+    from .operator import fused_index_topk_host as implementation
+
+    return implementation(*args, **kwargs)
+
+
 def make_workspace(*args, **kwargs):
     from .operator import make_workspace as implementation
 
@@ -52,5 +58,6 @@ def create_variant(options=None):
 
 __all__ = [
     "ExecutionContext", "PrefillCase", "PrefillInputs", "PreparedGraph", "RunMode", "StageNode", "StageSpec",
-    "VariantDescriptor", "VariantPlugin", "create_variant", "execute_graph", "fused_index_topk", "make_workspace",
+    "VariantDescriptor", "VariantPlugin", "create_variant", "execute_graph", "fused_index_topk",
+    "fused_index_topk_host", "make_workspace",
 ]

@@ -305,3 +305,127 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
             _WORKSPACES[key] = workspace
     _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
     return run_operator(workspace, q, kv, kv_scales, weights, k_start, k_end)
+
+
+# --------------------------------------------------------------------------- host buffers
+
+
+class HostPipeline:
+    """The operator for callers whose tensors live in pinned host memory.
+
+    Query rows are independent, so the call is cut into a few row chunks that flow through three
+    streams: host-to-device copies of chunk c+1, the operator on chunk c and the device-to-host
+    copy of the ids of chunk c-1 overlap (the PCIe link is full duplex and the copy engines run
+    beside the SMs).  Keys and scales are copied once, ahead of the first chunk.  Chunks are whole
+    multiples of 148 work units (592 rows) where the row count allows, so that every chunk fills
+    the persistent kernel's CTAs evenly; the short chunk goes first, which also shortens the
+    time before the first kernel can start.  Everything is allocated here, nothing per call.
+    """
+
+    UNIT_ROWS = 148 * _lib.BLOCK_Q
+
+    def __init__(self, rows: int, keys: int, device: Any, *, chunk_units: int = 2, seed: int = 0):
+        import torch
+
+        self.rows, self.keys, self.device = rows, keys, device
+        step = max(1, chunk_units) * self.UNIT_ROWS
+        bounds = []
+        first = rows % step or min(rows, step)
+        begin = 0
+        while begin < rows:
+            size = first if begin == 0 else min(step, rows - begin)
+            bounds.append((begin, begin + size))
+            begin += size
+        self.bounds = bounds
+        f8, i32, f32 = torch.float8_e4m3fn, torch.int32, torch.float32
+        self.q = torch.empty((rows, _lib.HEADS, _lib.HEAD_DIM), device=device, dtype=f8)
+        self.kv = torch.empty((keys, _lib.HEAD_DIM), device=device, dtype=f8)
+        self.kv_scales = torch.empty((keys,), device=device, dtype=f32)
+        self.weights = torch.empty((rows, _lib.HEADS), device=device, dtype=f32)
+        self.k_start = torch.empty((rows,), device=device, dtype=i32)
+        self.k_end = torch.empty((rows,), device=device, dtype=i32)
+        self.workspaces = [make_workspace(hi - lo, keys, device, seed=seed) for lo, hi in bounds]
+        self.copy_in = torch.cuda.Stream(device=device)
+        self.compute = torch.cuda.Stream(device=device)
+        self.copy_out = torch.cuda.Stream(device=device)
+
+    def __call__(self, q, kv_pair, weights, k_start, k_end, out) -> Any:
+        """All arguments are pinned host tensors; ``out`` is int32 ``[Q, 2048]`` and is returned.
+
+        The copies and kernels are ordered after the work already queued on the caller's current
+        stream, and that stream waits for the last copy into ``out``.
+        """
+
+        import torch
+
+        kv, kv_scales = kv_pair
+        for tensor in (q, kv, kv_scales, weights, k_start, k_end, out):
+            _require(not tensor.is_cuda and tensor.is_pinned() and tensor.is_contiguous(),
+                     "HostPipeline takes contiguous pinned host tensors")
+        _require(tuple(q.shape) == (self.rows, _lib.HEADS, _lib.HEAD_DIM) and q.dtype == torch.float8_e4m3fn,
+                 "q must be float8_e4m3fn [Q, 64, 128]")
+        _require(tuple(kv.shape) == (self.keys, _lib.HEAD_DIM) and kv.dtype == torch.float8_e4m3fn,
+                 "kv must be float8_e4m3fn [N, 128]")
+        _require(tuple(kv_scales.shape) == (self.keys,) and kv_scales.dtype == torch.float32, "kv_scales must be float32 [N]")
+        _require(tuple(weights.shape) == (self.rows, _lib.HEADS) and weights.dtype == torch.float32,
+                 "weights must be float32 [Q, 64]")
+        _require(tuple(k_start.shape) == (self.rows,) and tuple(k_end.shape) == (self.rows,)
+                 and k_start.dtype == torch.int32 and k_end.dtype == torch.int32, "k_start and k_end must be int32 [Q]")
+        _require(tuple(out.shape) == (self.rows, TOP_K) and out.dtype == torch.int32, "out must be int32 [Q, 2048]")
+        q_bytes, kv_bytes = q, kv
+        caller = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(caller)
+        for stream in (self.copy_in, self.compute, self.copy_out):
+            stream.wait_event(start)
+        with torch.cuda.stream(self.copy_in):
+            self.kv.copy_(kv_bytes, non_blocking=True)
+            self.kv_scales.copy_(kv_scales, non_blocking=True)
+        last = None
+        for (lo, hi), ws in zip(self.bounds, self.workspaces):
+            arrived, scored = torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(self.copy_in):
+                self.q[lo:hi].copy_(q_bytes[lo:hi], non_blocking=True)
+                self.weights[lo:hi].copy_(weights[lo:hi], non_blocking=True)
+                self.k_start[lo:hi].copy_(k_start[lo:hi], non_blocking=True)
+                self.k_end[lo:hi].copy_(k_end[lo:hi], non_blocking=True)
+                arrived.record(self.copy_in)
+            with torch.cuda.stream(self.compute):
+                self.compute.wait_event(arrived)
+                ids = run_operator(ws, self.q[lo:hi], self.kv, self.kv_scales, self.weights[lo:hi],
+                                   self.k_start[lo:hi], self.k_end[lo:hi])
+                scored.record(self.compute)
+            with torch.cuda.stream(self.copy_out):
+                self.copy_out.wait_event(scored)
+                out[lo:hi].copy_(ids, non_blocking=True)
+                last = torch.cuda.Event()
+                last.record(self.copy_out)
+        caller.wait_event(last)
+        return out
+
+    def check_status(self) -> None:
+        for ws in self.workspaces:
+            ws.check_status()
+
+
+_HOST_PIPELINES: dict[tuple, HostPipeline] = {}
+
+
+def fused_index_topk_host(q, kv_pair, weights, k_start, k_end, out, *, device: Any = None, seed: int = 0) -> Any:
+    """``fused_index_topk`` for pinned host tensors: chunked copies overlapped with the kernels.
+
+    Returns ``out`` (pinned int32 ``[Q, 2048]``); the caller's current stream is ordered after the last
+    copy, so synchronise that stream before reading ``out``.  One pipeline (device staging and
+    workspaces) is cached per (Q, N, device, seed).
+    """
+
+    import torch
+
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    rows, keys = int(q.shape[0]), int(kv_pair[0].shape[0])
+    key = (rows, keys, str(device), int(seed))
+    pipeline = _HOST_PIPELINES.get(key)
+    if pipeline is None:
+        pipeline = HostPipeline(rows, keys, device, seed=seed)
+        _HOST_PIPELINES[key] = pipeline
+    return pipeline(q, kv_pair, weights, k_start, k_end, out)

@@ -193,6 +193,31 @@ def test_public_callable_and_ab_fixtures_share_one_workspace(device):
     assert not torch.equal(results["A"][0].sort(dim=-1).values, results["B"][0].sort(dim=-1).values)
 
 
+def test_host_pipeline_matches_the_device_call(device):
+    """Pinned host tensors through the chunked three-stream pipeline give the device call's sets."""
+
+    from fusedindextopk_b200 import fused_index_topk
+    from fusedindextopk_b200.operator import HostPipeline
+
+    rows, keys = 1500, 8192      # two row chunks (316 + 1184), ragged tail block
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys)
+    gpu = inputs_to(host, device)
+    want = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end).clone()
+    pinned = [getattr(host, name).contiguous().pin_memory() for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")]
+    out = torch.full((rows, 2048), -7, dtype=torch.int32).pin_memory()
+    pipeline = HostPipeline(rows, keys, device)
+    assert len(pipeline.bounds) == 2 and pipeline.bounds[0] == (0, 316)
+    for _ in range(2):   # the second call reuses every buffer
+        out.fill_(-7)
+        result = pipeline(pinned[0], (pinned[1], pinned[2]), pinned[3], pinned[4], pinned[5], out)
+        torch.cuda.synchronize()
+        pipeline.check_status()
+        assert result is out
+        assert torch.equal(out.sort(dim=-1).values, want.cpu().sort(dim=-1).values)
+    with pytest.raises(ValueError):
+        pipeline(gpu.q, (pinned[1], pinned[2]), pinned[3], pinned[4], pinned[5], out)
+
+
 def test_plugin_graph_matches_reference_output_contract(device):
     from fusedindextopk_b200 import create_variant
 
