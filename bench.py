@@ -186,6 +186,8 @@ def main() -> None:
     parser.add_argument("--cpu-sample-rows", type=int, default=2048)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--e2e-chunk-units", type=int, default=2,
+                        help="row chunk of the host-buffer pipeline, in multiples of 148 work units (592 rows)")
     args = parser.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -325,7 +327,7 @@ def main() -> None:
         h2d_bytes = sum(t.numel() * t.element_size() for t in pinned.values())
         d2h_bytes = out_host.numel() * out_host.element_size()
         # the package's host-buffer entry: row chunks over three streams (copies in, kernels, ids out)
-        pipeline = HostPipeline(rows, keys, device, seed=host.case.seed)
+        pipeline = HostPipeline(rows, keys, device, seed=host.case.seed, chunk_units=args.e2e_chunk_units)
 
         def e2e_step():
             pipeline(pinned["q"], (pinned["kv"], pinned["kv_scales"]), pinned["weights"], pinned["k_start"],
