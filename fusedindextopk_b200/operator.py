@@ -328,15 +328,7 @@ class HostPipeline:
         import torch
 
         self.rows, self.keys, self.device = rows, keys, device
-        step = max(1, chunk_units) * self.UNIT_ROWS
-        bounds = []
-        first = rows % step or min(rows, step)
-        begin = 0
-        while begin < rows:
-            size = first if begin == 0 else min(step, rows - begin)
-            bounds.append((begin, begin + size))
-            begin += size
-        self.bounds = bounds
+        self.bounds = self.chunk_bounds(rows, chunk_units)
         f8, i32, f32 = torch.float8_e4m3fn, torch.int32, torch.float32
         self.q = torch.empty((rows, _lib.HEADS, _lib.HEAD_DIM), device=device, dtype=f8)
         self.kv = torch.empty((keys, _lib.HEAD_DIM), device=device, dtype=f8)
@@ -348,6 +340,22 @@ class HostPipeline:
         self.copy_in = torch.cuda.Stream(device=device)
         self.compute = torch.cuda.Stream(device=device)
         self.copy_out = torch.cuda.Stream(device=device)
+
+    @classmethod
+    def chunk_bounds(cls, rows: int, chunk_units: int = 2) -> list[tuple[int, int]]:
+        """Row ranges of the chunks: the remainder first, then whole multiples of 148 work units."""
+
+        if rows <= 0:
+            raise ValueError("rows must be positive")
+        step = max(1, chunk_units) * cls.UNIT_ROWS
+        bounds = []
+        first = rows % step or min(rows, step)
+        begin = 0
+        while begin < rows:
+            size = first if begin == 0 else min(step, rows - begin)
+            bounds.append((begin, begin + size))
+            begin += size
+        return bounds
 
     def __call__(self, q, kv_pair, weights, k_start, k_end, out) -> Any:
         """All arguments are pinned host tensors; ``out`` is int32 ``[Q, 2048]`` and is returned.

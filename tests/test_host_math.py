@@ -124,3 +124,21 @@ def test_workload_table_matches_benchmark_shapes():
         "c0": (8, 8192), "c1": (4096, 16384), "c2": (4096, 65536),
         "c3": (4096, 163840), "c3s": (64, 131072), "c4": (512, 32768),
     }
+
+
+def test_host_pipeline_chunks_cover_the_rows_in_whole_waves():
+    from fusedindextopk_b200.operator import HostPipeline
+
+    unit = HostPipeline.UNIT_ROWS
+    assert unit == 148 * 4
+    assert HostPipeline.chunk_bounds(4096, 2) == [(0, 544), (544, 1728), (1728, 2912), (2912, 4096)]
+    assert HostPipeline.chunk_bounds(1184, 2) == [(0, 1184)]
+    assert HostPipeline.chunk_bounds(5, 2) == [(0, 5)]
+    for rows in (1, 591, 592, 593, 4096, 10000):
+        for units in (1, 2, 3):
+            bounds = HostPipeline.chunk_bounds(rows, units)
+            assert bounds[0][0] == 0 and bounds[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(bounds, bounds[1:]))
+            assert all((hi - lo) % (units * unit) == 0 for lo, hi in bounds[1:])
+    with pytest.raises(ValueError):
+        HostPipeline.chunk_bounds(0)
