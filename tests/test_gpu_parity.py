@@ -136,7 +136,8 @@ def test_forced_spill_and_forced_repair(device, threshold):
 
 
 def test_spill_path_without_overflow(device):
-    """N = 8192 with threshold -inf fills every segment to exactly its smem + spill capacity."""
+    """N = 8192 with threshold -inf: 2048 candidates per segment, 1280 in shared memory and 768 spilled;
+    all distances to the threshold are infinite, so the selection takes its radix fallback."""
 
     host = make_workload_inputs("c0", query_tokens=8, context_tokens=8192)
     case = PrefillCase("spill", 8, 8192, 2048, 0)
