@@ -57,7 +57,7 @@ class FusedArgs(ctypes.Structure):
         ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p), ("debug_skip", c_int),
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
         ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
-        ("force_compute", c_int), ("max_ctas", c_int),
+        ("force_compute", c_int), ("max_ctas", c_int), ("thresholds_per_row", c_int),
     ]
 
 

@@ -321,6 +321,7 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.block_stride = a.block_stride;
     params.num_blocks = a.num_blocks;
     params.top_k_min_valid = a.force_compute ? 0 : kTopK;
+    params.row_thresholds = a.thresholds_per_row != 0 ? 1 : 0;
     const long long units = static_cast<long long>(a.num_blocks) * a.shards;
     return launch_fused<kModeTopK>(params, a.diag_logits != nullptr || a.trace != nullptr,
                                    fused_grid(device, units, a.max_ctas), stream);

@@ -144,6 +144,8 @@ struct FusedParams {
     int sample_rank;            // kModeSample
     int target_candidates;      // kModeSample
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
+    int row_thresholds;         // 1: thresholds are per row (shared by the row's shards); a shard that finds
+                                // fewer than 2048 candidates returns them all instead of failing
 };
 
 // Per-row scratch of the selection.
@@ -689,8 +691,9 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     view.in_spill = min(max(sh.counts[r][segment] - kSegCap, 0), kSpillSegCap);
     const int wanted = min(valid, kTopK);
     uint32_t* row_hist = sh.row_hist[r];
-    if (overflow || total < wanted) {
+    if (overflow || (total < wanted && !p.row_thresholds)) {
         // too many candidates for the buffers or too few for a full answer: the repair pass redoes the row
+        // (with per-row thresholds a shard may come up short: the merge of the shards checks the total)
         fill_empty(0);
         if (tid == 0) {
             p.failure_flags[row_slot] = 1;
@@ -705,7 +708,8 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
         } else {
             uint32_t cutoff;
             int equal_needed;
-            const float threshold = valid > kTopK ? __ldg(p.thresholds + row_slot) : __int_as_float(0xff800000);
+            const float threshold =
+                valid > kTopK ? __ldg(p.thresholds + (p.row_thresholds ? row : row_slot)) : __int_as_float(0xff800000);
             if (!bin_select(rs, view, row_hist, threshold, rb, tid, kTopK, cutoff, equal_needed))
                 radix_select(rs, view, rb, tid, kTopK, cutoff, equal_needed);
             emit_row(rs, view, lane, cutoff, equal_needed, kTopK - equal_needed, out_ids, out_pairs, &rb);
@@ -862,7 +866,7 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
             state.hi = min(min(end, p.keys), unit_key_hi);
             if (MODE == kModeTopK) {
                 const int valid = state.hi - state.lo;
-                if (valid > kTopK) state.threshold = __ldg(p.thresholds + state.slot);
+                if (valid > kTopK) state.threshold = __ldg(p.thresholds + (p.row_thresholds ? row : state.slot));
                 state.on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
             } else {
                 state.on = p.failure_flags[state.slot] != 0;

@@ -127,8 +127,13 @@ def make_workspace(
     block_stride: int = 1,
     with_pairs: bool = False,
     repair: bool = True,
+    key_shards: int | None = None,
 ) -> Workspace:
-    """Allocate every buffer once, outside any timed region."""
+    """Allocate every buffer once, outside any timed region.
+
+    ``key_shards`` > 1 cuts every query block's key range into that many work units (for calls with
+    too few query blocks to fill the GPU); ``None`` chooses it from Q, N and the SM count.
+    """
 
     import torch
 
@@ -168,7 +173,31 @@ def make_workspace(
             chunk_starts=empty((chunks, rows), i32),
             chunk_ends=empty((chunks, rows), i32),
         )
+    if key_shards is None:
+        key_shards = auto_key_shards(owned, keys, torch.cuda.get_device_properties(device).multi_processor_count)
+    if key_shards > 1 and not with_pairs:
+        shard_sizes = _lib.workspace_sizes(rows, keys, key_shards)
+        buffers.update(
+            shard_pairs=empty((key_shards, rows, TOP_K), i64),
+            shard_counts=torch.zeros((key_shards, rows), device=device, dtype=i32),
+            shard_flags=torch.zeros((key_shards, rows), device=device, dtype=u8),
+            shard_spill=empty((key_shards * rows, _lib.SPILL_U64_PER_ROW), i64),
+            merged_counts=torch.zeros(rows, device=device, dtype=i32),
+        )
+        assert buffers["shard_spill"].numel() * 8 == shard_sizes.spill_bytes
     return Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
+
+
+def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
+    """Key-range shards per query block for a call with ``query_blocks`` blocks of 4 rows.
+
+    One shard while the blocks alone fill half the SMs; otherwise as many shards as fit the SMs,
+    at most 8 (the merge kernel's source limit) and with at least 4096 keys per shard.
+    """
+
+    if query_blocks <= 0 or 2 * query_blocks > sm_count:
+        return 1
+    return max(1, min(_lib.MAX_PAIR_SOURCES, sm_count // query_blocks, keys // 4096))
 
 
 # --------------------------------------------------------------------------- stages
@@ -228,7 +257,30 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.block_begin, args.block_stride, args.num_blocks = ws.block_begin, ws.block_stride, ws.num_blocks
     args.force_compute = 1 if force_compute else 0
     args.max_ctas = max_ctas
-    check(load_library().itk_fused_topk(ctypes.byref(args), current_stream(torch, ws.device)))
+    sharded = "shard_pairs" in ws.buffers and not want_pairs and diag_logits is None
+    if sharded:
+        # every (query block, key shard) is a work unit; the shards share the row's threshold and
+        # return pairs, which the merge below turns into the row's ids
+        args.shards = int(ws.shard_pairs.shape[0])
+        args.thresholds_per_row = 1
+        args.out_ids = None
+        args.out_pairs, args.out_counts = ptr(ws.shard_pairs), ptr(ws.shard_counts)
+        args.failure_flags, args.spill = ptr(ws.shard_flags), ptr(ws.shard_spill)
+    library = load_library()
+    stream = current_stream(torch, ws.device)
+    check(library.itk_fused_topk(ctypes.byref(args), stream))
+    if sharded:
+        shards = args.shards
+        pair_table = _lib.pointer_table([ws.shard_pairs[s] for s in range(shards)])
+        count_table = _lib.pointer_table([ws.shard_counts[s] for s in range(shards)])
+        check(library.itk_merge_candidate_lists(pair_table, count_table, shards, ptr(ws.output_ids), None,
+                                                ptr(ws.merged_counts), ws.rows, stream))
+        # a row is complete when no shard overflowed and the union holds min(2048, valid keys) candidates
+        lo = k_start.clamp(min=key_lo)
+        hi = k_end.clamp(max=args.key_hi)
+        wanted = (hi - lo).clamp(min=0, max=TOP_K)
+        incomplete = ws.shard_flags.amax(dim=0).bool() | (ws.merged_counts < wanted)
+        ws.failure_flags.copy_(incomplete)
     return ws.output_ids
 
 
@@ -336,7 +388,7 @@ class HostPipeline:
         self.weights = torch.empty((rows, _lib.HEADS), device=device, dtype=f32)
         self.k_start = torch.empty((rows,), device=device, dtype=i32)
         self.k_end = torch.empty((rows,), device=device, dtype=i32)
-        self.workspaces = [make_workspace(hi - lo, keys, device, seed=seed) for lo, hi in bounds]
+        self.workspaces = [make_workspace(hi - lo, keys, device, seed=seed) for lo, hi in self.bounds]
         self.copy_in = torch.cuda.Stream(device=device)
         self.compute = torch.cuda.Stream(device=device)
         self.copy_out = torch.cuda.Stream(device=device)

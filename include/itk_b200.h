@@ -132,6 +132,9 @@ typedef struct itk_fused_args {
     int num_blocks;             /* owned blocks */
     int force_compute;          /* 1: score rows even when all their keys are selected anyway */
     int max_ctas;               /* 0 = one CTA per SM */
+    int thresholds_per_row;     /* with shards > 1: thresholds has [Q] entries (one per row, shared by its
+                                 * shards) and a shard that finds fewer than 2048 candidates returns them
+                                 * all instead of failing; the merge decides whether the row is complete */
 } itk_fused_args;
 int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream);
 

@@ -194,6 +194,39 @@ def test_public_callable_and_ab_fixtures_share_one_workspace(device):
     assert not torch.equal(results["A"][0].sort(dim=-1).values, results["B"][0].sort(dim=-1).values)
 
 
+@pytest.mark.parametrize("rows,keys,shards", [(8, 32768, 8), (24, 16384, 4), (7, 65536, 2)])
+def test_key_shards_inside_one_gpu_give_the_unsharded_sets(device, rows, keys, shards):
+    """Short-Q calls cut every query block's key range into work units that share the row thresholds;
+    the merged result must be the same exact Top-2048 (checked on the kernel's own scores)."""
+
+    host = make_workload_inputs("c3", query_tokens=rows, context_tokens=keys)
+    gpu = inputs_to(host, device)
+    tensors = (gpu.q, gpu.kv, gpu.kv_scales, gpu.weights, gpu.k_start, gpu.k_end)
+    case = PrefillCase("shards", rows, keys, 2048, 0)
+    plain = operator.make_workspace(rows, keys, device, key_shards=1)
+    cut = operator.make_workspace(rows, keys, device, key_shards=shards)
+    assert "shard_pairs" in cut.buffers and "shard_pairs" not in plain.buffers
+    want = operator.run_operator(plain, *tensors).clone()
+    got = operator.run_operator(cut, *tensors)
+    torch.cuda.synchronize()
+    plain.check_status()
+    cut.check_status()
+    assert int(cut.failure_flags.sum()) == 0
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(plain, *tensors, diag_logits=logits)
+    indices = got.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+    verdict = score_threshold_check(want.unsqueeze(1).contiguous().cpu(), logits.cpu(), case)
+    if verdict["rows_with_cutoff_ties"] == 0:
+        assert torch.equal(got.sort(dim=-1).values, want.sort(dim=-1).values)
+    # the automatic choice: few query blocks, many keys -> shards; enough blocks -> none
+    assert operator.auto_key_shards(16, 163840, 148) == 8
+    assert operator.auto_key_shards(64, 65536, 148) == 2
+    assert operator.auto_key_shards(1024, 16384, 148) == 1
+    assert operator.auto_key_shards(2, 8192, 148) == 2
+
+
 def test_host_pipeline_matches_the_device_call(device):
     """Pinned host tensors through the chunked three-stream pipeline give the device call's sets."""
 
