@@ -8,7 +8,7 @@
 //
 // as one 128 x 256 x 128 contraction on the tensor cores (four tcgen05.mma of
 // K = 32 into a TMEM accumulator), then the epilogue warps read the accumulator
-// back with tcgen05.ld, one TMEM lane = one key per thread, and form
+// back with tcgen05.ld (one warp per TMEM lane quarter and query row) and form
 //
 //     score[row, key] = (sum_h relu(acc) * w[row, h]) * kv_scale[key].
 //
@@ -16,18 +16,18 @@
 // the kernel mode:
 //   kModeTopK    keep (score, key) when the key is inside the row's range and
 //                score >= threshold[row]; candidates go to per-row shared-memory
-//                segments (overflow to a bounded global spill), and consumer
-//                warps of the same CTA radix-select the exact Top-2048 of the
-//                previous unit while the next unit's scores are produced;
-//   kModeSample  the "keys" are S gathered sample keys; consumer warps pick the
-//                rank-th largest valid sampled score of each row = its threshold;
+//                segments (overflow to a bounded global spill) and are counted in a
+//                per-row histogram; when the unit's last tile is done the four
+//                epilogue warps of a row select its exact Top-2048 in place;
+//   kModeSample  the "keys" are S gathered sample keys; one warp per row picks the
+//                rank-th largest valid sampled score = the row's threshold;
 //   kModeRepair  for rows flagged as failed, write every (score, key) of one
 //                16 K-key chunk to global memory for the exact repair reducers.
 //
-// Warp roles (512 threads): warp 0 TMA producer, warp 1 UMMA issuer and TMEM
-// owner, warps 4-11 epilogue (two warpgroups, one per TMEM accumulator buffer),
-// warps 2, 3, 12-15 Top-K consumers.  All hand-offs are mbarriers with bounded
-// waits; a wait that expires sets bit 0 of *status and the CTA drains.
+// Warp roles (640 threads): warp 0 TMA producer, warp 1 UMMA issuer and TMEM
+// owner, warps 2-3 idle, warps 4-19 epilogue and selection.  All hand-offs are
+// mbarriers with bounded waits; a wait that expires sets bit 0 of *status and
+// the CTA drains.
 //
 // Counterparts in the reference (sm_90a, WGMMA): the persistent kernel
 // kernel/csrc/include/fused_index_topk/long_fused_topk.cuh:64-672 and its
