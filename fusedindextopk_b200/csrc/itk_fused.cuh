@@ -40,7 +40,7 @@
 
 // Build-time experiment switch for timing studies (0 in every shipped build):
 //   1 = epilogue only drains TMEM and hands the buffer back, 2 = drain + head reduction, no filtering,
-//   6 = everything but the Top-K selection of the consumer warps.
+//   6 = everything but the per-row Top-K selection, 7 = additionally no filter / compaction.
 #ifndef ITK_EXPERIMENT
 #define ITK_EXPERIMENT 0
 #endif
@@ -265,7 +265,7 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
     return true;
 }
 
-// ------------------------------------------------------------------ consumer helpers
+// ------------------------------------------------------------------ selection helpers
 
 // ------------------------------------------------------------------ per-row selection
 

@@ -75,8 +75,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Wall-clock limit of one wait.  The longest legitimate wait is a consumer
-// waiting for one whole unit of score production (well under 100 ms).
+// Wall-clock limit of one wait.  The longest legitimate wait is the UMMA issuer or the
+// TMA producer waiting out the Top-K selection at the end of a unit (tens of microseconds).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // Waits for the phase with the given parity.  Returns false when the limit
