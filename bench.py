@@ -186,7 +186,7 @@ def main() -> None:
     parser.add_argument("--cpu-sample-rows", type=int, default=2048)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
-    parser.add_argument("--e2e-chunk-units", type=int, default=2,
+    parser.add_argument("--e2e-chunk-units", type=int, default=1,
                         help="row chunk of the host-buffer pipeline, in multiples of 148 work units (592 rows)")
     args = parser.parse_args()
 

@@ -371,13 +371,21 @@ class HostPipeline:
     beside the SMs).  Keys and scales are copied once, ahead of the first chunk.  Chunks are whole
     multiples of 148 work units (592 rows) where the row count allows, so that every chunk fills
     the persistent kernel's CTAs evenly; the short chunk goes first, which also shortens the
-    time before the first kernel can start.  Everything is allocated here, nothing per call.
+    time before the first kernel can start.  Everything is allocated here, nothing per call, and
+    repeated calls with the same host tensors replay one CUDA graph.
     """
 
     UNIT_ROWS = 148 * _lib.BLOCK_Q
 
-    def __init__(self, rows: int, keys: int, device: Any, *, chunk_units: int = 2, seed: int = 0):
+    def __init__(self, rows: int, keys: int, device: Any, *, chunk_units: int = 1, seed: int = 0,
+                 use_graph: bool = True):
         import torch
+
+        # From the second call with the same host tensors on, the whole pipeline (some sixty copies
+        # and launches on three streams) is replayed as one CUDA graph.
+        self.use_graph = use_graph
+        self._graphs: dict[tuple, Any] = {}
+        self._seen: set[tuple] = set()
 
         self.rows, self.keys, self.device = rows, keys, device
         self.bounds = self.chunk_bounds(rows, chunk_units)
@@ -394,7 +402,7 @@ class HostPipeline:
         self.copy_out = torch.cuda.Stream(device=device)
 
     @classmethod
-    def chunk_bounds(cls, rows: int, chunk_units: int = 2) -> list[tuple[int, int]]:
+    def chunk_bounds(cls, rows: int, chunk_units: int = 1) -> list[tuple[int, int]]:
         """Row ranges of the chunks: the remainder first, then whole multiples of 148 work units."""
 
         if rows <= 0:
@@ -432,6 +440,41 @@ class HostPipeline:
         _require(tuple(k_start.shape) == (self.rows,) and tuple(k_end.shape) == (self.rows,)
                  and k_start.dtype == torch.int32 and k_end.dtype == torch.int32, "k_start and k_end must be int32 [Q]")
         _require(tuple(out.shape) == (self.rows, TOP_K) and out.dtype == torch.int32, "out must be int32 [Q, 2048]")
+        tensors = (q, kv, kv_scales, weights, k_start, k_end, out)
+        if self.use_graph:
+            key = tuple(int(tensor.data_ptr()) for tensor in tensors)
+            graph = self._graphs.get(key)
+            if graph is None and key in self._seen and len(self._graphs) < 4:
+                graph = self._capture(tensors)
+                if graph is not None:
+                    self._graphs[key] = graph
+            self._seen.add(key)
+            if graph is not None:
+                graph.replay()
+                return out
+        self._enqueue(tensors)
+        return out
+
+    def _capture(self, tensors) -> Any:
+        """The pipeline as a CUDA graph, or None (graphs are then switched off) when capture fails."""
+
+        import torch
+
+        graph = torch.cuda.CUDAGraph()
+        try:
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph):
+                self._enqueue(tensors)
+            return graph
+        except Exception:   # noqa: BLE001 - any capture problem falls back to the stream version
+            self.use_graph = False
+            torch.cuda.synchronize(self.device)
+            return None
+
+    def _enqueue(self, tensors) -> None:
+        import torch
+
+        q, kv, kv_scales, weights, k_start, k_end, out = tensors
         q_bytes, kv_bytes = q, kv
         caller = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
@@ -461,7 +504,6 @@ class HostPipeline:
                 last = torch.cuda.Event()
                 last.record(self.copy_out)
         caller.wait_event(last)
-        return out
 
     def check_status(self) -> None:
         for ws in self.workspaces:

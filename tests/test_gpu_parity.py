@@ -233,15 +233,15 @@ def test_host_pipeline_matches_the_device_call(device):
     from fusedindextopk_b200 import fused_index_topk
     from fusedindextopk_b200.operator import HostPipeline
 
-    rows, keys = 1500, 8192      # two row chunks (316 + 1184), ragged tail block
+    rows, keys = 1500, 8192      # three row chunks (316 + 592 + 592), ragged tail block
     host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys)
     gpu = inputs_to(host, device)
     want = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end).clone()
     pinned = [getattr(host, name).contiguous().pin_memory() for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")]
     out = torch.full((rows, 2048), -7, dtype=torch.int32).pin_memory()
     pipeline = HostPipeline(rows, keys, device)
-    assert len(pipeline.bounds) == 2 and pipeline.bounds[0] == (0, 316)
-    for _ in range(2):   # the second call reuses every buffer
+    assert len(pipeline.bounds) == 3 and pipeline.bounds[0] == (0, 316)
+    for _ in range(3):   # the first call runs on the streams, the second captures a CUDA graph, the third replays it
         out.fill_(-7)
         result = pipeline(pinned[0], (pinned[1], pinned[2]), pinned[3], pinned[4], pinned[5], out)
         torch.cuda.synchronize()
