@@ -511,8 +511,8 @@ __device__ __forceinline__ void radix_select(RowSelect& rs, const RowView& v, Ro
                                              uint32_t& cutoff, int& equal_needed) {
     const int lane = tid & 31;
     if (tid == 0) rs.differing = 0u;
-    if (lane == 0 && v.in_smem > 0) rs.reference = v.scores[0];   // any candidate of the row (a row has more than
-    row_sync(rb);                                                  // kTopK candidates here, so some segment has one)
+    if (lane == 0 && v.in_smem > 0) rs.reference = v.scores[0];   // any candidate of the row (the row has at least
+    row_sync(rb);                                                  // rank_in >= 1 candidates, so some segment has one)
     const uint32_t reference = rs.reference;
     uint32_t differing = 0u;
     for_scores(v, lane, [&](uint32_t score) { differing |= score ^ reference; });
@@ -733,91 +733,40 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     if (!(overflow || total < wanted) && total > kTopK) lap(rb, 6);
 }
 
-// Threshold of one row = rank-th largest valid sampled score (kModeSample).  One warp per row, no
-// block-level synchronisation: the warp walks the row's candidates in shared memory once per score
-// bit (most significant differing bit first), counts the candidates that agree with the prefix found
-// so far and have the bit set, and keeps or clears the bit so that exactly rank-1 candidates stay
-// above the prefix.
+// Threshold of one row = rank-th largest valid sampled score (kModeSample): the radix selection over
+// the row's candidates by the row's four warps (a single warp walking the candidates once per score
+// bit took twice as long; it was four fifths of the sampling launch).  Called by the 128 threads of
+// the row after the barrier that publishes the counts.
 __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                     bool has_tiles, int lane) {
+                                                     bool has_tiles, RowBarrier& rb, int tid) {
     const int row = u.row0 + r;
     const int start = __ldg(p.k_start + row);
     const int end = __ldg(p.k_end + row);
-    const float minus_inf = __int_as_float(0xff800000);
-    float result = minus_inf;
+    float result = __int_as_float(0xff800000);
     if (has_tiles && end - start > p.target_candidates) {
-        const uint32_t* scores = sh.cand_scores[r];
-        const int* counts = sh.counts[r];
+        const int segment = tid >> 5;
         int total = 0;
         bool overflow = false;
-        uint32_t reference = 0u;
 #pragma unroll
-        for (int s = kSegments - 1; s >= 0; --s) {
-            total += counts[s];
-            overflow = overflow || counts[s] > kSegCap;
-            if (counts[s] > 0) reference = scores[s * kSegCap];
+        for (int s = 0; s < kSegments; ++s) {
+            total += sh.counts[r][s];
+            overflow = overflow || sh.counts[r][s] > kSegCap;
         }
-        if (!overflow && total >= p.sample_rank) {
-            // candidate g of the row (segments concatenated) belongs to lane g % 32; the first
-            // kOwn of a lane's candidates live in registers, the rest is re-read from shared
-            // memory four at a time (a single warp is latency-bound, so loads must overlap)
-            constexpr int kOwn = 16;
-            const int first1 = counts[0], first2 = first1 + counts[1], first3 = first2 + counts[2];
-            const auto fetch = [&](int g) -> uint32_t {
-                int segment = 0, begin = 0;
-                if (g >= first1) { segment = 1; begin = first1; }
-                if (g >= first2) { segment = 2; begin = first2; }
-                if (g >= first3) { segment = 3; begin = first3; }
-                return scores[segment * kSegCap + (g - begin)];
-            };
-            uint32_t own[kOwn];
-            uint32_t live = 0u;
-#pragma unroll
-            for (int m = 0; m < kOwn; ++m) {
-                const int g = lane + 32 * m;
-                own[m] = g < total ? fetch(g) : 0u;
-                live |= g < total ? 1u << m : 0u;
-            }
-            const auto for_rest = [&](auto&& visit) {
-#pragma unroll 1
-                for (int g = lane + 32 * kOwn; g < total; g += 128) {
-                    uint32_t x[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) x[k] = g + 32 * k < total ? fetch(g + 32 * k) : 0u;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) visit(g + 32 * k < total, x[k]);
-                }
-            };
-            uint32_t differing = 0u;
-#pragma unroll
-            for (int m = 0; m < kOwn; ++m) differing |= (live >> m & 1u) ? own[m] ^ reference : 0u;
-            for_rest([&](bool valid, uint32_t score) { differing |= valid ? score ^ reference : 0u; });
-            differing = __reduce_or_sync(0xffffffffu, differing);
-            const int bits = differing == 0u ? 0 : 32 - __clz(differing);
-            uint32_t mask = bits == 32 ? 0u : 0xffffffffu << bits;
-            uint32_t prefix = reference & mask;
-            int rank = p.sample_rank;
-#pragma unroll 1
-            for (int bit = bits - 1; bit >= 0; --bit) {
-                const uint32_t probe = 1u << bit;
-                const uint32_t want = prefix | probe;       // agrees with the prefix and has the bit set
-                const uint32_t care = mask | probe;
-                int above = 0;
-#pragma unroll
-                for (int m = 0; m < kOwn; ++m)
-                    above += static_cast<int>(live >> m & 1u) & static_cast<int>((own[m] & care) == want);
-                for_rest([&](bool valid, uint32_t score) {
-                    above += static_cast<int>(valid) & static_cast<int>((score & care) == want);
-                });
-                above = __reduce_add_sync(0xffffffffu, above);
-                if (above >= rank) prefix |= probe;   // the rank-th largest has this bit set
-                else rank -= above;                   // it lies among the candidates with the bit clear
-                mask |= probe;
-            }
-            result = ordered_to_float(prefix);
+        if (!overflow && total >= p.sample_rank) {   // the same decision in all 128 threads
+            RowView view;
+            view.segment = segment;
+            view.scores = sh.cand_scores[r] + segment * kSegCap;
+            view.ids = sh.cand_ids[r] + segment * kSegCap;
+            view.spill = nullptr;
+            view.in_smem = sh.counts[r][segment];
+            view.in_spill = 0;
+            uint32_t cutoff;
+            int equal_needed;
+            radix_select(sh.select[r], view, rb, tid, p.sample_rank, cutoff, equal_needed);
+            result = ordered_to_float(cutoff);
         }
     }
-    if (lane == 0) p.thresholds_out[row] = result;
+    if (tid == 0) p.thresholds_out[row] = result;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -1141,7 +1090,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     if (!(DIAG && (p.debug_skip & 1))) select_topk_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
 #endif
                 } else if (MODE == kModeSample) {
-                    if (quarter == 0) sample_threshold_row(sh, p, u, own_r, has_tiles, lane);
+                    sample_threshold_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
                 }
             }
             if (MODE == kModeSample) row_sync(rb);   // the row's buffers may be written again
