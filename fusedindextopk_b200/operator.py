@@ -175,7 +175,7 @@ def make_workspace(
         )
     if key_shards is None:
         key_shards = auto_key_shards(owned, keys, torch.cuda.get_device_properties(device).multi_processor_count)
-    if key_shards > 1 and not with_pairs:
+    if key_shards > 1:
         shard_sizes = _lib.workspace_sizes(rows, keys, key_shards)
         buffers.update(
             shard_pairs=empty((key_shards, rows, TOP_K), i64),
@@ -257,7 +257,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.block_begin, args.block_stride, args.num_blocks = ws.block_begin, ws.block_stride, ws.num_blocks
     args.force_compute = 1 if force_compute else 0
     args.max_ctas = max_ctas
-    sharded = "shard_pairs" in ws.buffers and not want_pairs and diag_logits is None
+    sharded = "shard_pairs" in ws.buffers and diag_logits is None
     if sharded:
         # every (query block, key shard) is a work unit; the shards share the row's threshold and
         # return pairs, which the merge below turns into the row's ids
@@ -273,13 +273,15 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         shards = args.shards
         pair_table = _lib.pointer_table([ws.shard_pairs[s] for s in range(shards)])
         count_table = _lib.pointer_table([ws.shard_counts[s] for s in range(shards)])
-        check(library.itk_merge_candidate_lists(pair_table, count_table, shards, ptr(ws.output_ids), None,
-                                                ptr(ws.merged_counts), ws.rows, stream))
+        check(library.itk_merge_candidate_lists(
+            pair_table, count_table, shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
+            ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows, stream))
         # a row is complete when no shard overflowed and the union holds min(2048, valid keys) candidates
         lo = k_start.clamp(min=key_lo)
         hi = k_end.clamp(max=args.key_hi)
         wanted = (hi - lo).clamp(min=0, max=TOP_K)
-        incomplete = ws.shard_flags.amax(dim=0).bool() | (ws.merged_counts < wanted)
+        merged_counts = ws.output_counts if want_pairs else ws.merged_counts
+        incomplete = ws.shard_flags.amax(dim=0).bool() | (merged_counts < wanted)
         ws.failure_flags.copy_(incomplete)
     return ws.output_ids
 
