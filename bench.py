@@ -13,11 +13,13 @@ then costs the slowest rank's time ("strong" scaling).  For the short-Q workload
 c3s the key range is sharded instead, and the step includes the NCCL all-gather of
 the per-rank Top-2048 candidates and the merge.
 
-Rank 0 prints ONE JSON line.  `value` is microseconds per call with inputs resident
-in HBM (CUDA events, summed over the K timed steps, max over ranks); `e2e` is the
-same call through the public API from pinned host buffers with the host->device
-copies of all inputs and the device->host copy of the ids inside the timed region;
-`roofline` is the fused kernel alone against the dense-FP8 tensor-core peak;
+Rank 0 prints ONE JSON line.  `value` is microseconds per call of the public callable
+`fused_index_topk` with inputs resident in HBM (CUDA events around every call, summed
+over the K timed steps, max over ranks; the callable replays one CUDA graph from its
+second call on); `e2e` is the host-buffer entry (`HostPipeline`) from pinned host
+tensors to pinned host ids, with the host->device copies of all inputs and the
+device->host copy of the ids inside the timed region; `roofline` is the fused
+kernel alone (timed in a pass of its own) against the dense-FP8 tensor-core peak;
 `cpu_baseline` is the CPU restatement of the reference path (dense fp32 scores +
 torch.topk) on a bounded row sample.  `--impl reference` times only that CPU path.
 """
@@ -277,7 +279,35 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_calls(count: int):
+        """The step as a user makes it (the public callable, which replays one CUDA graph from its
+        second call on), then the fused launch alone, timed in a pass of its own for the roofline."""
+
+        from fusedindextopk_b200 import fused_index_topk
+
+        total_ms, fused_ms = 0.0, 0.0
+        events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(count)]
+        for ev in events:
+            flush.fill_(1)
+            ev[0].record()
+            fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end, workspace=ws)
+            ev[1].record()
+        torch.cuda.synchronize()
+        total_ms = sum(ev[0].elapsed_time(ev[1]) for ev in events)
+        for ev in events:
+            flush.fill_(1)
+            operator.run_sample_thresholds(ws, *tensors)
+            ev[0].record()
+            operator.run_fused_topk(ws, *tensors)
+            ev[1].record()
+            operator.run_repair(ws, *tensors)
+        torch.cuda.synchronize()
+        fused_ms = sum(ev[0].elapsed_time(ev[1]) for ev in events)
+        return total_ms, fused_ms
+
     def timed_steps(count: int):
+        if not key_mode:
+            return timed_calls(count)
         total_ms, fused_ms = 0.0, 0.0
         events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(count)]
         for ev in events:

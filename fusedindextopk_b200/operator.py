@@ -339,13 +339,20 @@ def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end) -> An
 _WORKSPACES: dict[tuple, Workspace] = {}
 
 
+_OPERATOR_GRAPHS: dict[tuple, Any] = {}
+_OPERATOR_SEEN: set[tuple] = set()
+
+
 def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *, workspace: Workspace | None = None,
-                     seed: int = 0) -> Any:
+                     seed: int = 0, use_graph: bool = True) -> Any:
     """Exact unordered Top-K key ids per query row, int32 ``[Q, K]``, ``-1`` padded.
 
     ``kv_pair`` is ``(kv, kv_scales)``.  Without ``workspace`` one is cached per
     (Q, N, device, seed); the returned tensor is that workspace's output buffer
-    and is overwritten by the next call with the same key.
+    and is overwritten by the next call with the same key.  From the second call with the
+    same tensors (same storage) and workspace on, the launches of the call are replayed as one
+    CUDA graph: a long context has dozens of small repair launches whose host-side cost
+    would otherwise exceed the kernels' time on calls with few query rows.
     """
 
     kv, kv_scales = kv_pair
@@ -358,7 +365,37 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
             workspace = make_workspace(rows, keys, q.device, seed=seed)
             _WORKSPACES[key] = workspace
     _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
-    return run_operator(workspace, q, kv, kv_scales, weights, k_start, k_end)
+    tensors = (q, kv, kv_scales, weights, k_start, k_end)
+    import torch
+
+    if use_graph and not torch.cuda.is_current_stream_capturing():
+        key = (id(workspace), *(int(tensor.data_ptr()) for tensor in tensors))
+        graph = _OPERATOR_GRAPHS.get(key)
+        if graph is None and key in _OPERATOR_SEEN and len(_OPERATOR_GRAPHS) < 16:
+            graph = _capture_operator(workspace, tensors)
+            if graph is not None:
+                _OPERATOR_GRAPHS[key] = graph
+        _OPERATOR_SEEN.add(key)
+        if graph is not None:
+            graph.replay()
+            return workspace.output_ids
+    return run_operator(workspace, *tensors)
+
+
+def _capture_operator(workspace: Workspace, tensors) -> Any:
+    """One operator call as a CUDA graph, or None when the capture fails (the caller launches directly)."""
+
+    import torch
+
+    graph = torch.cuda.CUDAGraph()
+    try:
+        torch.cuda.synchronize(workspace.device)
+        with torch.cuda.graph(graph):
+            run_operator(workspace, *tensors)
+        return graph
+    except Exception:   # noqa: BLE001 - any capture problem falls back to direct launches
+        torch.cuda.synchronize(workspace.device)
+        return None
 
 
 # --------------------------------------------------------------------------- host buffers
