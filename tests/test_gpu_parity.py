@@ -227,6 +227,28 @@ def test_key_shards_inside_one_gpu_give_the_unsharded_sets(device, rows, keys, s
     assert operator.auto_key_shards(2, 8192, 148) == 2
 
 
+def test_public_callable_replays_a_graph_with_the_same_result(device):
+    """From its second call with the same tensors on the callable replays one CUDA graph."""
+
+    from fusedindextopk_b200 import fused_index_topk
+
+    host = make_workload_inputs("c3s", query_tokens=16, context_tokens=40000)   # key shards + 3 repair chunks
+    gpu = inputs_to(host, device)
+    args = (gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end)
+    want = fused_index_topk(*args, use_graph=False).sort(dim=-1).values.clone()
+    before = len(operator._OPERATOR_GRAPHS)
+    for _ in range(3):
+        got = fused_index_topk(*args)
+        torch.cuda.synchronize()
+        assert torch.equal(got.sort(dim=-1).values, want)
+    assert len(operator._OPERATOR_GRAPHS) == before + 1
+    # new contents in the same storage are picked up by the replay
+    gpu.weights.neg_()
+    flipped = fused_index_topk(*args, use_graph=False).sort(dim=-1).values.clone()
+    assert not torch.equal(flipped, want)
+    assert torch.equal(fused_index_topk(*args).sort(dim=-1).values, flipped)
+
+
 def test_host_pipeline_matches_the_device_call(device):
     """Pinned host tensors through the chunked three-stream pipeline give the device call's sets."""
 
