@@ -101,6 +101,9 @@ class Workspace:
     block_stride: int = 1
     num_blocks: int = 0
     buffers: dict = field(default_factory=dict)
+    # CUDA graphs of whole operator calls, keyed by the input tensors' addresses (they die with the workspace)
+    graphs: dict = field(default_factory=dict)
+    seen_inputs: set = field(default_factory=set)
 
     def __getattr__(self, name: str) -> Any:
         buffers = self.__dict__.get("buffers", {})
@@ -339,10 +342,6 @@ def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end) -> An
 _WORKSPACES: dict[tuple, Workspace] = {}
 
 
-_OPERATOR_GRAPHS: dict[tuple, Any] = {}
-_OPERATOR_SEEN: set[tuple] = set()
-
-
 def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *, workspace: Workspace | None = None,
                      seed: int = 0, use_graph: bool = True) -> Any:
     """Exact unordered Top-K key ids per query row, int32 ``[Q, K]``, ``-1`` padded.
@@ -369,13 +368,14 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
     import torch
 
     if use_graph and not torch.cuda.is_current_stream_capturing():
-        key = (id(workspace), *(int(tensor.data_ptr()) for tensor in tensors))
-        graph = _OPERATOR_GRAPHS.get(key)
-        if graph is None and key in _OPERATOR_SEEN and len(_OPERATOR_GRAPHS) < 16:
+        key = tuple(int(tensor.data_ptr()) for tensor in tensors)
+        graph = workspace.graphs.get(key)
+        if graph is None and key in workspace.seen_inputs and len(workspace.graphs) < 4:
             graph = _capture_operator(workspace, tensors)
             if graph is not None:
-                _OPERATOR_GRAPHS[key] = graph
-        _OPERATOR_SEEN.add(key)
+                workspace.graphs[key] = graph
+        if len(workspace.seen_inputs) < 64:
+            workspace.seen_inputs.add(key)
         if graph is not None:
             graph.replay()
             return workspace.output_ids
