@@ -176,6 +176,90 @@ def cpu_reference_time(host, sample_rows: int, threads: int) -> dict:
     }
 
 
+def hbm_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured copy bandwidth (MEASURED_PEAKS.json), of measured"
+    return 6650.0, "6.65 TB/s fallback, of fallback"
+
+
+def bench_quantize(args) -> None:
+    """`--stage quantize`: the step before the operator, bf16 queries and keys -> e4m3 on one GPU."""
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantisation has no CPU path")
+    from fusedindextopk_b200 import quantize
+    from fusedindextopk_b200.inputs import WORKLOADS
+
+    workload = WORKLOADS[args.workload]
+    rows, keys = args.rows or workload.query_tokens, args.keys or workload.context_tokens
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    generator = torch.Generator(device=device).manual_seed(0)
+    q_source = torch.randn((rows, 64, 128), device=device, dtype=torch.bfloat16, generator=generator)
+    kv_source = torch.randn((keys, 128), device=device, dtype=torch.bfloat16, generator=generator)
+    weights = torch.randn((rows, 64), device=device, generator=generator)
+    q = torch.empty((rows, 64, 128), device=device, dtype=torch.float8_e4m3fn)
+    kv = torch.empty((keys, 128), device=device, dtype=torch.float8_e4m3fn)
+    kv_scales = torch.empty((keys,), device=device)
+    folded = torch.empty_like(weights)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+
+    def step() -> None:
+        quantize.quantize_rows(q_source, fold=weights, out=q, out_folded=folded, want_scales=False)
+        quantize.quantize_rows(kv_source, out=kv, out_scales=kv_scales)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.wait_first_sample()
+    torch.cuda.synchronize()
+    begin = sampler.mark()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        step()
+        stop.record()
+        stop.synchronize()
+        total_ms += start.elapsed_time(stop)
+    # the query launch alone, for the roofline of the kernel
+    kernel_ms = 0.0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        quantize.quantize_rows(q_source, fold=weights, out=q, out_folded=folded, want_scales=False)
+        stop.record()
+        stop.synchronize()
+        kernel_ms += start.elapsed_time(stop)
+    torch.cuda.synchronize()
+    clocks = sampler.stop(begin, sampler.mark())
+    microseconds = total_ms * 1e3 / args.steps
+    kernel_microseconds = kernel_ms * 1e3 / args.steps
+    # bf16 in, e4m3 out; per query row the weight read and the folded weight written
+    algorithmic_bytes = rows * 64 * (256 + 128 + 8)
+    peak, peak_note = hbm_peak_gbs()
+    achieved = algorithmic_bytes / (kernel_microseconds * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "quantize_inputs_us_per_call", "value": microseconds, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": microseconds / 1e3,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload} activations: Q={rows}x64x128 and N={keys}x128 bf16 -> e4m3 + scales "
+                               "(query scales folded into the weights)",
+                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written before every timed step (L2 flush)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_note, "algorithmic_bytes": algorithmic_bytes,
+                     "kernel": "itk_quantize_rows_kernel<bf16>, the query launch",
+                     "kernel_us": kernel_microseconds},
+        "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -190,7 +274,12 @@ def main() -> None:
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--e2e-chunk-units", type=int, default=1,
                         help="row chunk of the host-buffer pipeline, in multiples of 148 work units (592 rows)")
+    parser.add_argument("--stage", default="operator", choices=["operator", "quantize"],
+                        help="operator: the headline path; quantize: the bf16 -> e4m3 input step before it (1 GPU)")
     args = parser.parse_args()
+    if args.stage == "quantize":
+        bench_quantize(args)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

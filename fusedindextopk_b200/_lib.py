@@ -32,7 +32,7 @@ EXPORTED_SYMBOLS = (
     "itk_version", "itk_last_error", "itk_init", "itk_resource_report", "itk_workspace_bytes",
     "itk_gather_sampled_kv", "itk_sample_thresholds", "itk_fused_topk", "itk_update_chunk_ranges",
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
-    "itk_merge_candidate_lists", "itk_fused_topk_static",
+    "itk_merge_candidate_lists", "itk_fused_topk_static", "itk_quantize_rows_e4m3",
 )
 
 
@@ -95,6 +95,7 @@ def load_library() -> ctypes.CDLL:
     library.itk_merge_candidate_lists.argtypes = (
         [POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     )
+    library.itk_quantize_rows_e4m3.argtypes = [c_void_p, c_int] + [c_void_p] * 4 + [c_longlong, c_void_p]
     for name in EXPORTED_SYMBOLS:
         function = getattr(library, name)
         if name not in ("itk_version", "itk_last_error"):

@@ -9,6 +9,7 @@
 #include <mutex>
 #include <string>
 
+#include "itk_quantize.cuh"
 #include "itk_select.cuh"
 
 namespace {
@@ -220,6 +221,27 @@ int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t*
         static_cast<const uint8_t*>(kv), kv_scales, sample_ids, static_cast<uint8_t*>(sampled_kv), sampled_scales,
         samples);
     return launch_check("itk_gather_kernel");
+}
+
+int itk_quantize_rows_e4m3(const void* source, int source_dtype, const float* fold, float* folded, void* values,
+                           float* scales, long long rows, itk_stream_t stream) {
+    static_assert(kQuantDim == ITK_HEAD_DIM, "rows are one index head wide");
+    ITK_REQUIRE(source && values, "source and values must not be null");
+    ITK_REQUIRE(source_dtype == ITK_SOURCE_F32 || source_dtype == ITK_SOURCE_BF16,
+                "source_dtype must be ITK_SOURCE_F32 or ITK_SOURCE_BF16");
+    ITK_REQUIRE((fold == nullptr) == (folded == nullptr), "fold and folded go together");
+    ITK_REQUIRE(scales || folded, "nothing would receive the row scales");
+    ITK_REQUIRE(rows > 0 && rows <= (1ll << 31) * kQuantRowsPerBlock / 2, "rows out of range");
+    ITK_REQUIRE(aligned16(source) && aligned16(values), "source and values must be 16-byte aligned");
+    const unsigned blocks = static_cast<unsigned>((rows + kQuantRowsPerBlock - 1) / kQuantRowsPerBlock);
+    if (source_dtype == ITK_SOURCE_F32) {
+        itk_quantize_rows_kernel<float><<<blocks, kQuantThreads, 0, stream>>>(
+            static_cast<const float*>(source), fold, folded, static_cast<uint8_t*>(values), scales, rows);
+    } else {
+        itk_quantize_rows_kernel<__nv_bfloat16><<<blocks, kQuantThreads, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(source), fold, folded, static_cast<uint8_t*>(values), scales, rows);
+    }
+    return launch_check("itk_quantize_rows_kernel");
 }
 
 int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,

@@ -182,6 +182,22 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
+/* Row-wise e4m3 quantisation of operator inputs on the device: the step before the
+ * operator.  For each of `rows` rows of ITK_HEAD_DIM elements
+ *   scale = max(amax(|x|), 1e-4) / 448 (fp32), value = e4m3(x / scale) with IEEE fp32
+ *   division and round-to-nearest-even,
+ * the arithmetic of quantize_contiguous_index_kv (src/fused_index_topk/inputs.py:76-90),
+ * which the reference runs in torch; results are bit-identical to it for finite inputs.
+ * source_dtype: ITK_SOURCE_F32 or ITK_SOURCE_BF16.  `values` gets [rows,128] e4m3 bytes.
+ * `scales` ([rows] fp32) may be null when a fold is requested.  With fold and folded set
+ * (both [rows] fp32, may alias) folded[r] = fold[r] * scale[r]: quantised queries
+ * ([Q*64,128] rows) carry their scale in the head weights, because the operator has no
+ * query-scale argument (src/fused_index_topk/contract.py:152-185). */
+#define ITK_SOURCE_F32 0
+#define ITK_SOURCE_BF16 1
+int itk_quantize_rows_e4m3(const void* source, int source_dtype, const float* fold, float* folded, void* values,
+                           float* scales, long long rows, itk_stream_t stream);
+
 /* The fused kernel for callers that must not allocate device memory.
  *
  * Some hosts of this operator cannot call cudaMalloc at the point where they run it:

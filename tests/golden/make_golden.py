@@ -7,8 +7,8 @@ Run where the reference checkout is available (it is not on the GPU box):
 The reference's CUDA kernels and its DeepGEMM scorer cannot run without their
 GPU and third-party dependency, but its pure-Python host layer imports on a
 CPU.  This script calls that layer (sample schedule, guarded rank, sample
-positions, RNG stream seeds, the standard input recipe, the output-contract
-validator and the cutoff-tie oracle) and records inputs and outputs as small
+positions, RNG stream seeds, the standard input recipe, the row-wise key
+quantisation, the output-contract validator and the cutoff-tie oracle) and records inputs and outputs as small
 fixtures; the tests replay them against this package's own implementations.
 """
 
@@ -36,7 +36,11 @@ def main(reference_root: str) -> None:
         compare_topk_indices,
         validate_topk_indices,
     )
-    from fused_index_topk.inputs import input_stream_seeds, make_prefill_inputs
+    from fused_index_topk.inputs import (
+        input_stream_seeds,
+        make_prefill_inputs,
+        quantize_contiguous_index_kv,
+    )
     from fused_index_topk.kernel.plugin import (
         _SAMPLING_SEED_XOR,
         _TARGET_CANDIDATES,
@@ -172,6 +176,33 @@ def main(reference_root: str) -> None:
             message = str(error)
         contract["violations"].append({"label": label, "data": data, "message": message})
     golden["output_contract"] = contract
+
+    # 6. row-wise e4m3 quantisation of the index keys (fp32 and bf16 sources, edge rows)
+    quantize = []
+    for label, dtype, seed in (("float32", torch.float32, 11), ("bfloat16", torch.bfloat16, 12)):
+        generator = torch.Generator().manual_seed(seed)
+        source = torch.randn((20, 128), generator=generator) * torch.exp(
+            2.0 * torch.randn((20, 1), generator=generator)
+        )
+        source[0] = 0.0                                   # amax floor 1e-4
+        source[1] = source[1] * 1e-7                      # below the floor: codes near zero
+        source[2] = source[2] * 1e6
+        source[3, ::2] = -0.0
+        source[4] = 0.0
+        source[4, 0] = 448.0                              # scale exactly 1: ties land on code midpoints
+        source[4, 1:9] = torch.tensor([17.0, 19.0, -21.0, 2.0 ** -10, 3 * 2.0 ** -10, -416.0 - 16.0, 0.0107421875, 1.0625])
+        source = source.to(dtype).contiguous()
+        values, scales = quantize_contiguous_index_kv(source)
+        quantize.append(
+            {
+                "dtype": label,
+                "rows": int(source.shape[0]),
+                "source_hex": source.view(torch.uint8).numpy().tobytes().hex(),
+                "values_hex": values.view(torch.uint8).numpy().tobytes().hex(),
+                "scales_hex": scales.view(torch.uint8).numpy().tobytes().hex(),
+            }
+        )
+    golden["quantize_index_kv"] = quantize
 
     target = Path(__file__).resolve().parent / "reference_golden.json"
     target.write_text(json.dumps(golden, indent=1, sort_keys=True) + "\n")
