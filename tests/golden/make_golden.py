@@ -8,7 +8,8 @@ The reference's CUDA kernels and its DeepGEMM scorer cannot run without their
 GPU and third-party dependency, but its pure-Python host layer imports on a
 CPU.  This script calls that layer (sample schedule, guarded rank, sample
 positions, RNG stream seeds, the standard input recipe, the row-wise key
-quantisation, the output-contract validator and the cutoff-tie oracle) and records inputs and outputs as small
+quantisation, the replay file format and manifest checks, the output-contract
+validator and the cutoff-tie oracle) and records inputs and outputs as small
 fixtures; the tests replay them against this package's own implementations.
 """
 
@@ -203,6 +204,64 @@ def main(reference_root: str) -> None:
             }
         )
     golden["quantize_index_kv"] = quantize
+
+    # 7. replay format: bytes of a saved fixture and manifest validation verdicts
+    import copy
+    import tempfile
+
+    from fused_index_topk.replay import save_replay_tensors, validate_replay_manifest
+
+    case = PrefillCase("golden-q6-n96", 6, 96, top_k=96, seed=0)
+    made = make_prefill_inputs(case, device="cpu", fixture_id="A")
+    with tempfile.TemporaryDirectory() as scratch:
+        saved = save_replay_tensors(
+            Path(scratch) / "item.safetensors",
+            {name: getattr(made, name) for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")},
+            # one key only: the writer's metadata map has no fixed order across processes
+            metadata={"case_id": case.case_id},
+        )
+    shape = {"query_tokens": 6, "context_tokens": 96, "top_k": 96, "indexer_heads": 64, "head_dim": 128}
+    good = {
+        "schema_version": 1, "dataset_id": "golden", "frozen": True,
+        "items": [
+            {"item_id": f"{split}-{fixture}", "split": split, "case_id": "golden-q6-n96", "fixture_id": fixture,
+             "path": f"{split}/{fixture}.safetensors", "sha256": "0" * 64, "case": shape}
+            for split in ("tuning", "test_normal", "test_hard") for fixture in ("A", "B")
+        ],
+    }
+
+    def verdict(manifest):
+        try:
+            return {"summary": validate_replay_manifest(manifest)}
+        except ValueError as error:
+            return {"error": str(error)}
+
+    def broken(edit):
+        manifest = copy.deepcopy(good)
+        edit(manifest)
+        return manifest
+
+    manifests = {
+        "good": good,
+        "schema": broken(lambda m: m.update(schema_version=2)),
+        "not_frozen": broken(lambda m: m.update(frozen=False)),
+        "no_dataset": broken(lambda m: m.update(dataset_id="")),
+        "no_items": broken(lambda m: m.update(items=[])),
+        "duplicate_item": broken(lambda m: m["items"][1].update(item_id=m["items"][0]["item_id"])),
+        "bad_split": broken(lambda m: m["items"][0].update(split="train")),
+        "bad_fixture": broken(lambda m: m["items"][0].update(fixture_id="C")),
+        "duplicate_key": broken(lambda m: m["items"][1].update(fixture_id="A")),
+        "absolute_path": broken(lambda m: m["items"][0].update(path="/etc/passwd")),
+        "parent_path": broken(lambda m: m["items"][0].update(path="../x.safetensors")),
+        "bad_sha": broken(lambda m: m["items"][0].update(sha256="xyz")),
+        "bad_shape": broken(lambda m: m["items"][0]["case"].update(top_k=0)),
+        "missing_split": broken(lambda m: m.update(items=[i for i in m["items"] if i["split"] != "test_hard"])),
+    }
+    golden["replay"] = {
+        "saved_bytes": saved["bytes"],
+        "saved_sha256": saved["sha256"],
+        "manifests": {name: {"manifest": value, "verdict": verdict(value)} for name, value in manifests.items()},
+    }
 
     target = Path(__file__).resolve().parent / "reference_golden.json"
     target.write_text(json.dumps(golden, indent=1, sort_keys=True) + "\n")
