@@ -104,12 +104,12 @@ class FusedIndexTopK:
             "operator_sources": _source_fingerprint(),
             "options": self.options,
             "normal_candidate_gmem_bytes": 0,
-            "spill_capacity_per_segment": _lib.SPILL_U64_PER_ROW // 8,
+            "spill_capacity_per_segment": _lib.SPILL_U64_PER_ROW // 4,
             "spill_workspace_bytes_per_row": _lib.SPILL_U64_PER_ROW * 8,
             "spill_index_bits": 32,
             "candidate_index_bits": 16,
             "index_encoding": "segment-relative-lossless",
-            "candidate_segments": 8,
+            "candidate_segments": 4,
             "max_context": sampling.MAX_CONTEXT,
             "block_q": self.block_q,
             "timed_repair": True,
@@ -231,7 +231,7 @@ class FusedIndexTopK:
                 "sample_guard_sigmas": self.sample_guard_sigmas,
                 "sampling_granularity": "individual-random-token",
                 "dense_logits_materialized": diag is not None,
-                "candidate_segments": 8,
+                "candidate_segments": 4,
                 "device_failure_flags": True,
                 "timed_failure_repair": True,
                 "repair_dispatch": "device-mask-no-host-sync",
