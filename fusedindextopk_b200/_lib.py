@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "itk_gather_sampled_kv", "itk_sample_thresholds", "itk_fused_topk", "itk_update_chunk_ranges",
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
     "itk_merge_candidate_lists", "itk_fused_topk_static", "itk_quantize_rows_e4m3",
+    "itk_gather_sampled_kv_paged", "itk_repair_produce_paged",
 )
 
 
@@ -58,6 +59,7 @@ class FusedArgs(ctypes.Structure):
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
         ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
         ("force_compute", c_int), ("max_ctas", c_int), ("thresholds_per_row", c_int),
+        ("tile_table", c_void_p), ("physical_keys", c_int),
     ]
 
 
@@ -95,6 +97,8 @@ def load_library() -> ctypes.CDLL:
     library.itk_merge_candidate_lists.argtypes = (
         [POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     )
+    library.itk_gather_sampled_kv_paged.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p]
+    library.itk_repair_produce_paged.argtypes = [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_int, c_void_p, c_void_p]
     library.itk_quantize_rows_e4m3.argtypes = [c_void_p, c_int] + [c_void_p] * 4 + [c_longlong, c_void_p]
     for name in EXPORTED_SYMBOLS:
         function = getattr(library, name)

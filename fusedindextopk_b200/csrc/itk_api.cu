@@ -108,6 +108,8 @@ int init_current_device(int* device_out) {
         ITK_CUDA(raise_smem(itk_fused_kernel<kModeSample, false>, kFusedSmemBytes));
         ITK_CUDA(raise_smem(itk_fused_kernel<kModeSample, true>, kFusedSmemBytes));
         ITK_CUDA(raise_smem(itk_fused_kernel<kModeRepair, false>, kFusedSmemBytes));
+        ITK_CUDA(raise_smem(itk_fused_kernel<kModeTopK, false, true>, kFusedSmemBytes));
+        ITK_CUDA(raise_smem(itk_fused_kernel<kModeRepair, false, true>, kFusedSmemBytes));
         ITK_CUDA(raise_smem(itk_pair_topk_kernel, kPairSmemBytes));
         g_sm_count[device] = properties.multiProcessorCount;
         g_initialised[device] = true;
@@ -132,11 +134,18 @@ int fused_grid(int device, long long units, int max_ctas) {
 template <int MODE>
 int launch_fused(const FusedParams& params, bool diagnostic, int grid, cudaStream_t stream) {
     if (diagnostic) {
+        if (params.tile_table != nullptr) return fail(ITK_ERR_UNSUPPORTED, "paged keys have no diagnostic build");
         if (MODE == kModeRepair) return fail(ITK_ERR_UNSUPPORTED, "the repair producer has no diagnostic build");
         if (MODE == kModeTopK)
             itk_fused_kernel<kModeTopK, true><<<grid, kThreads, kFusedSmemBytes, stream>>>(params);
         else
             itk_fused_kernel<kModeSample, true><<<grid, kThreads, kFusedSmemBytes, stream>>>(params);
+    } else if (params.tile_table != nullptr) {
+        if (MODE == kModeSample) return fail(ITK_ERR_UNSUPPORTED, "the sample prepass reads gathered keys, not pages");
+        if (MODE == kModeTopK)
+            itk_fused_kernel<kModeTopK, false, true><<<grid, kThreads, kFusedSmemBytes, stream>>>(params);
+        else
+            itk_fused_kernel<kModeRepair, false, true><<<grid, kThreads, kFusedSmemBytes, stream>>>(params);
     } else {
         itk_fused_kernel<MODE, false><<<grid, kThreads, kFusedSmemBytes, stream>>>(params);
     }
@@ -211,16 +220,25 @@ int itk_workspace_bytes(int rows, int keys, int shards, itk_workspace_sizes* siz
     return ITK_OK;
 }
 
-int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t* sample_ids, void* sampled_kv,
-                          float* sampled_scales, int keys, int samples, itk_stream_t stream) {
+int itk_gather_sampled_kv_paged(const void* kv, const float* kv_scales, const int32_t* sample_ids,
+                                const int32_t* tile_table, void* sampled_kv, float* sampled_scales, int keys,
+                                int physical_keys, int samples, itk_stream_t stream) {
     ITK_REQUIRE(kv && kv_scales && sample_ids && sampled_kv && sampled_scales, "gather pointers must not be null");
     ITK_REQUIRE(keys > 0 && samples > 0 && samples <= keys, "need 0 < samples <= keys");
+    ITK_REQUIRE(tile_table == nullptr || (physical_keys >= kTileKeys && physical_keys % kTileKeys == 0),
+                "physical_keys must be a positive multiple of 128");
     ITK_REQUIRE(aligned16(kv) && aligned16(sampled_kv), "kv and sampled_kv must be 16-byte aligned");
     const int work = samples * 8;
     itk_gather_kernel<<<(work + 255) / 256, 256, 0, stream>>>(
-        static_cast<const uint8_t*>(kv), kv_scales, sample_ids, static_cast<uint8_t*>(sampled_kv), sampled_scales,
-        samples);
+        static_cast<const uint8_t*>(kv), kv_scales, sample_ids, tile_table, static_cast<uint8_t*>(sampled_kv),
+        sampled_scales, samples);
     return launch_check("itk_gather_kernel");
+}
+
+int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t* sample_ids, void* sampled_kv,
+                          float* sampled_scales, int keys, int samples, itk_stream_t stream) {
+    return itk_gather_sampled_kv_paged(kv, kv_scales, sample_ids, nullptr, sampled_kv, sampled_scales, keys, 0, samples,
+                                       stream);
 }
 
 int itk_quantize_rows_e4m3(const void* source, int source_dtype, const float* fold, float* folded, void* values,
@@ -315,8 +333,13 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     if (rc != ITK_OK) return rc;
     FusedParams params{};
     if ((rc = make_row_map(&params.map_q, a.q, static_cast<long long>(a.rows) * kHeads, kUmmaN)) != ITK_OK) return rc;
-    if ((rc = make_row_map(&params.map_kv, a.kv, a.keys, kTileKeys)) != ITK_OK) return rc;
+    if (a.tile_table != nullptr)
+        ITK_REQUIRE(a.physical_keys >= kTileKeys && a.physical_keys % kTileKeys == 0,
+                    "physical_keys must be a positive multiple of 128");
+    if ((rc = make_row_map(&params.map_kv, a.kv, a.tile_table != nullptr ? a.physical_keys : a.keys, kTileKeys)) != ITK_OK)
+        return rc;
     params.kv_scales = a.kv_scales;
+    params.tile_table = a.tile_table;
     params.weights = a.weights;
     params.k_start = a.k_start;
     params.k_end = a.k_end;
@@ -364,6 +387,18 @@ int itk_repair_produce(const void* q, const void* kv, const float* kv_scales, co
                        const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
                        uint64_t* repair_pairs, int rows, int keys, int chunk_lo, int chunk_hi, int block_begin,
                        int block_stride, int num_blocks, int* status, itk_stream_t stream) {
+    return itk_repair_produce_paged(q, kv, kv_scales, weights, k_start, k_end, failure_flags, repair_pairs, rows, keys,
+                                    chunk_lo, chunk_hi, block_begin, block_stride, num_blocks, nullptr, 0, status,
+                                    stream);
+}
+
+int itk_repair_produce_paged(const void* q, const void* kv, const float* kv_scales, const float* weights,
+                             const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
+                             uint64_t* repair_pairs, int rows, int keys, int chunk_lo, int chunk_hi, int block_begin,
+                             int block_stride, int num_blocks, const int32_t* tile_table, int physical_keys,
+                             int* status, itk_stream_t stream) {
+    ITK_REQUIRE(tile_table == nullptr || (physical_keys >= kTileKeys && physical_keys % kTileKeys == 0),
+                "physical_keys must be a positive multiple of 128");
     ITK_REQUIRE(q && kv && kv_scales && weights && k_start && k_end && failure_flags && repair_pairs && status,
                 "repair producer pointers must not be null");
     ITK_REQUIRE(rows > 0 && keys > 0 && keys <= ITK_MAX_KEYS, "need rows > 0 and 0 < keys <= %d", ITK_MAX_KEYS);
@@ -381,8 +416,9 @@ int itk_repair_produce(const void* q, const void* kv, const float* kv_scales, co
     if (rc != ITK_OK) return rc;
     FusedParams params{};
     if ((rc = make_row_map(&params.map_q, q, static_cast<long long>(rows) * kHeads, kUmmaN)) != ITK_OK) return rc;
-    if ((rc = make_row_map(&params.map_kv, kv, keys, kTileKeys)) != ITK_OK) return rc;
+    if ((rc = make_row_map(&params.map_kv, kv, tile_table != nullptr ? physical_keys : keys, kTileKeys)) != ITK_OK) return rc;
     params.kv_scales = kv_scales;
+    params.tile_table = tile_table;
     params.weights = weights;
     params.k_start = k_start;
     params.k_end = k_end;

@@ -113,8 +113,9 @@ constexpr int kTraceSm = 24, kTraceNsBegin = 25, kTraceNsEnd = 26;
 
 struct FusedParams {
     CUtensorMap map_q;    // [rows*64, 128] bytes, box 256 x 128, 128-byte swizzle
-    CUtensorMap map_kv;   // [keys, 128] bytes, box 128 x 128, 128-byte swizzle
-    const float* kv_scales;     // [keys]
+    CUtensorMap map_kv;   // [keys, 128] bytes (PAGED: the physical pool), box 128 x 128, 128-byte swizzle
+    const float* kv_scales;     // [keys] (PAGED: [physical keys])
+    const int32_t* tile_table;  // PAGED builds: physical 128-key tile of every logical tile, [ceil(keys/128)]
     const float* weights;       // [rows, 64]
     const int32_t* k_start;     // [rows]
     const int32_t* k_end;       // [rows]
@@ -870,7 +871,7 @@ __device__ __forceinline__ bool warp_tile_wait(uint64_t* bar, uint32_t parity, v
     return ok;
 }
 
-template <int MODE, bool DIAG>
+template <int MODE, bool DIAG, bool PAGED = false>
 __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_constant__ FusedParams p) {
     extern __shared__ uint8_t smem_raw[];
     // Align by pointer arithmetic on the shared array (not through an integer cast) so that the
@@ -962,7 +963,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     mbar_arrive(&sh.kv_full[stage]);
 #else
                     mbar_arrive_expect_tx(&sh.kv_full[stage], kKvBytes);
-                    tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0, t * kTileKeys);
+                    tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0,
+                                (PAGED ? __ldg(p.tile_table + t) : t) * kTileKeys);
 #endif
                     ITK_BEAT(100 + kv_iter);
                 }
@@ -1141,7 +1143,9 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             const auto per_key = [&](int t, float& scale, int& range_key) {
                 const int key = t * kTileKeys + quarter * 32 + own_lane;
                 const bool key_ok = key < p.keys;
-                scale = key_ok ? __ldg(p.kv_scales + key) : 0.0f;
+                // a paged key keeps its logical position (ids, ranges); only its storage moves
+                const int stored = PAGED ? __ldg(p.tile_table + t) * kTileKeys + quarter * 32 + own_lane : key;
+                scale = key_ok ? __ldg(p.kv_scales + stored) : 0.0f;
                 if (MODE == kModeSample) range_key = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
             };
             // ReLU is applied in place on the fragment registers, which are consecutive pairs

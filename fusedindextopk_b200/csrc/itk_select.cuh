@@ -20,14 +20,16 @@ constexpr int kMaxPairSources = 8;
 // ------------------------------------------------------------------ gather
 
 // sampled_kv[s,:] = kv[ids[s],:] (128 bytes as 8 x 16 B), sampled_scales[s] = kv_scales[ids[s]].
+// With a tile table, key position k is stored at row tile_table[k / 128] * 128 + k % 128.
 __global__ void itk_gather_kernel(const uint8_t* __restrict__ kv, const float* __restrict__ kv_scales,
-                                  const int32_t* __restrict__ sample_ids, uint8_t* __restrict__ sampled_kv,
-                                  float* __restrict__ sampled_scales, int samples) {
+                                  const int32_t* __restrict__ sample_ids, const int32_t* __restrict__ tile_table,
+                                  uint8_t* __restrict__ sampled_kv, float* __restrict__ sampled_scales, int samples) {
     const int work = blockIdx.x * blockDim.x + threadIdx.x;
     if (work >= samples * 8) return;
     const int sample = work >> 3;
     const int part = work & 7;
-    const long long source = sample_ids[sample];
+    long long source = sample_ids[sample];
+    if (tile_table != nullptr) source = static_cast<long long>(tile_table[source >> 7]) * 128 + (source & 127);
     reinterpret_cast<uint4*>(sampled_kv)[work] = reinterpret_cast<const uint4*>(kv + source * kHeadDim)[part];
     if (part == 0) sampled_scales[sample] = kv_scales[source];
 }

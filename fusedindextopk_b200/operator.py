@@ -207,7 +207,7 @@ def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
 
 
 def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None,
-                          trace=None) -> Any:
+                          trace=None, tile_table=None) -> Any:
     """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph."""
 
     import torch
@@ -218,9 +218,9 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
     library = load_library()
     stream = current_stream(torch, ws.device)
     plan = ws.plan
-    check(library.itk_gather_sampled_kv(
-        ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
-        ws.keys, plan.sample_elements, stream,
+    check(library.itk_gather_sampled_kv_paged(
+        ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(tile_table), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
+        ws.keys, int(kv.shape[0]), plan.sample_elements, stream,
     ))
     check(library.itk_sample_thresholds(
         ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
@@ -233,8 +233,12 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
 
 def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, thresholds=None,
                    diag_logits=None, trace=None, debug_skip: int = 0, force_compute: bool = False, max_ctas: int = 0,
-                   key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False) -> Any:
-    """Stage ``fused_topk``: one launch of the persistent fused kernel."""
+                   key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
+    """Stage ``fused_topk``: one launch of the persistent fused kernel.
+
+    With ``tile_table`` (int32, one physical 128-key tile per logical tile) ``kv`` and ``kv_scales`` are
+    the physical pool of a paged key cache.
+    """
 
     import torch
 
@@ -260,6 +264,8 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.block_begin, args.block_stride, args.num_blocks = ws.block_begin, ws.block_stride, ws.num_blocks
     args.force_compute = 1 if force_compute else 0
     args.max_ctas = max_ctas
+    args.tile_table = ptr(tile_table)
+    args.physical_keys = int(kv.shape[0]) if tile_table is not None else 0
     sharded = "shard_pairs" in ws.buffers and diag_logits is None
     if sharded:
         # every (query block, key shard) is a work unit; the shards share the row's threshold and
@@ -290,7 +296,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
 
 
 def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
-               key_hi: int | None = None, want_pairs: bool = False) -> Any:
+               key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
     """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags."""
 
     import torch
@@ -306,10 +312,10 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
         chunk_hi = min(ws.keys, chunk_lo + _lib.REPAIR_CHUNK)
         if chunk_hi <= key_lo or chunk_lo >= key_hi:
             continue
-        check(library.itk_repair_produce(
+        check(library.itk_repair_produce_paged(
             ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
             ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
-            ws.num_blocks, ptr(ws.status), stream,
+            ws.num_blocks, ptr(tile_table), int(kv.shape[0]) if tile_table is not None else 0, ptr(ws.status), stream,
         ))
         check(library.itk_chunk_local_topk(
             ptr(ws.repair_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
@@ -329,13 +335,13 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
     return ws.output_ids
 
 
-def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end) -> Any:
+def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, tile_table=None) -> Any:
     """Sampling + fused kernel + repair on the current stream; returns ``ws.output_ids``."""
 
-    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end)
-    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end)
+    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
+    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
     if "repair_pairs" in ws.buffers:
-        run_repair(ws, q, kv, kv_scales, weights, k_start, k_end)
+        run_repair(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
     return ws.output_ids
 
 

@@ -1,0 +1,134 @@
+"""Index keys in a paged cache.
+
+Serving stacks keep keys in fixed-size pages handed out by an allocator, so a
+sequence's keys are not contiguous.  The reference supports contiguous keys only
+(``src/fused_index_topk/inputs.py:31-32``).  Here the pool is
+``kv_pool [pages, page_size, 128]`` e4m3 with ``scale_pool [pages, page_size]``
+fp32, and ``block_table`` (int32) lists the pages of the logical key sequence in
+order.  ``page_size`` must be a multiple of 128, the kernel's key tile: the TMA
+producer, the epilogue's scale load and the sample gather then only swap the
+tile's row offset (``tile_table[t] * 128``), and everything a caller sees (ids,
+``[k_start, k_end)``, the number of keys) stays in logical positions.
+
+Together with ``batched.varlen_ranges`` one block table serves a whole batch: the
+logical key space is the concatenation of the sequences, each starting on a page
+boundary.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+from . import _lib
+from .operator import _WORKSPACES, Workspace, _require, make_workspace, run_operator
+
+TILE_KEYS = 128
+
+
+def expand_block_table(block_table: Any, page_size: int) -> Any:
+    """int32 ``[pages_used]`` pages -> int32 ``[pages_used * page_size / 128]`` physical 128-key tiles."""
+
+    import torch
+
+    _require(page_size >= TILE_KEYS and page_size % TILE_KEYS == 0, "page_size must be a positive multiple of 128")
+    _require(block_table.dtype == torch.int32 and block_table.dim() == 1, "block_table must be int32 [pages]")
+    per_page = page_size // TILE_KEYS
+    within = torch.arange(per_page, device=block_table.device, dtype=torch.int32)
+    return (block_table.unsqueeze(1) * per_page + within.unsqueeze(0)).reshape(-1).contiguous()
+
+
+_TILE_TABLES: dict[tuple, Any] = {}
+
+
+def _checked_tile_table(block_table: Any, page_size: int, pages: int) -> Any:
+    """Range-checked expansion, remembered while the table's storage and version stay the same.
+
+    The range check reads the table back to the host (one synchronisation); a serving loop that
+    reuses a block table for many calls pays it once.
+    """
+
+    key = (int(block_table.data_ptr()), int(block_table._version), int(block_table.numel()), page_size, pages,
+           str(block_table.device))
+    cached = _TILE_TABLES.get(key)
+    if cached is None:
+        _require(int(block_table.min()) >= 0 and int(block_table.max()) < pages,
+                 "block_table names a page outside the pool")
+        cached = expand_block_table(block_table, page_size)
+        if len(_TILE_TABLES) >= 64:
+            _TILE_TABLES.clear()
+        _TILE_TABLES[key] = cached
+    return cached
+
+
+def scatter_to_pages(kv: Any, kv_scales: Any, page_size: int, *, pool_pages: int | None = None,
+                     generator: Any = None) -> tuple[Any, Any, Any]:
+    """Place contiguous keys into randomly chosen pages of a fresh pool.
+
+    Returns ``(kv_pool [P, page_size, 128], scale_pool [P, page_size], block_table int32)``; unused
+    pool rows are filled with a byte pattern and NaN scales so that a wrong page shows up in results.
+    For tests and for callers migrating a contiguous cache.
+    """
+
+    import torch
+
+    keys = int(kv.shape[0])
+    used = (keys + page_size - 1) // page_size
+    pool_pages = max(used, pool_pages or used + 3)
+    order = torch.randperm(pool_pages, generator=generator)[:used].to(torch.int32)
+    kv_pool = torch.full((pool_pages * page_size, _lib.HEAD_DIM), 0x3C, dtype=torch.uint8, device=kv.device)
+    scale_pool = torch.full((pool_pages * page_size,), float("nan"), dtype=torch.float32, device=kv.device)
+    rows = torch.arange(keys, device=kv.device)
+    target = order.to(kv.device).long()[rows // page_size] * page_size + rows % page_size
+    kv_pool[target] = kv.view(torch.uint8)
+    scale_pool[target] = kv_scales
+    return (kv_pool.view(torch.float8_e4m3fn).view(pool_pages, page_size, _lib.HEAD_DIM),
+            scale_pool.view(pool_pages, page_size), order.to(kv.device))
+
+
+def fused_index_topk_paged(q: Any, kv_pool_pair: tuple[Any, Any], block_table: Any, keys: int, weights: Any,
+                           k_start: Any, k_end: Any, top_k: int = _lib.TOP_K, *, workspace: Workspace | None = None,
+                           seed: int = 0) -> Any:
+    """Exact Top-K ids (logical key positions) with the keys read through a block table.
+
+    ``kv_pool_pair = (kv_pool [P, page_size, 128] e4m3, scale_pool [P, page_size] fp32)``;
+    ``block_table`` int32 ``[ceil(keys / page_size)]`` on the same device; ``keys`` is the logical
+    number of keys.  Returns int32 ``[Q, K]`` like ``fused_index_topk``.
+    """
+
+    import torch
+
+    kv_pool, scale_pool = kv_pool_pair
+    _require(top_k == _lib.TOP_K, f"top_k must be {_lib.TOP_K}")
+    _require(q.is_cuda, "q must be a CUDA tensor (there is no CPU path)")
+    _require(kv_pool.dim() == 3 and kv_pool.shape[2] == _lib.HEAD_DIM, "kv_pool must have shape [P, page_size, 128]")
+    pages, page_size = int(kv_pool.shape[0]), int(kv_pool.shape[1])
+    _require(page_size % TILE_KEYS == 0, "page_size must be a positive multiple of 128")
+    _require(tuple(scale_pool.shape) == (pages, page_size) and scale_pool.dtype == torch.float32,
+             "scale_pool must be float32 [P, page_size]")
+    _require(q.dtype == torch.float8_e4m3fn and kv_pool.dtype == torch.float8_e4m3fn, "q and kv_pool must be float8_e4m3fn")
+    _require(q.dim() == 3 and q.shape[1] == _lib.HEADS and q.shape[2] == _lib.HEAD_DIM, "q must have shape [Q, 64, 128]")
+    rows = int(q.shape[0])
+    _require(rows > 0 and 0 < keys <= _lib.MAX_KEYS, f"need Q > 0 and 0 < keys <= {_lib.MAX_KEYS}")
+    _require(weights.dtype == torch.float32 and tuple(weights.shape) == (rows, _lib.HEADS), "weights must be float32 [Q, 64]")
+    _require(k_start.dtype == torch.int32 and k_end.dtype == torch.int32 and tuple(k_start.shape) == (rows,)
+             and tuple(k_end.shape) == (rows,), "k_start and k_end must be int32 [Q]")
+    for name, tensor in (("q", q), ("kv_pool", kv_pool), ("scale_pool", scale_pool), ("weights", weights),
+                         ("k_start", k_start), ("k_end", k_end), ("block_table", block_table)):
+        _require(tensor.is_contiguous(), f"{name} must be contiguous")
+        _require(tensor.device == q.device, f"{name} must live on the same device as q")
+    _require(int(block_table.numel()) * page_size >= keys, "block_table does not cover the keys")
+    tile_table = _checked_tile_table(block_table, page_size, pages)
+
+    if workspace is None:
+        key = (rows, keys, str(q.device), int(seed))
+        workspace = _WORKSPACES.get(key)
+        if workspace is None:
+            workspace = make_workspace(rows, keys, q.device, seed=seed)
+            _WORKSPACES[key] = workspace
+    _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
+    flat_kv = kv_pool.view(pages * page_size, _lib.HEAD_DIM)
+    flat_scales = scale_pool.view(pages * page_size)
+    return run_operator(workspace, q, flat_kv, flat_scales, weights, k_start, k_end, tile_table=tile_table)
+
+
+__all__ = ["expand_block_table", "fused_index_topk_paged", "scatter_to_pages"]

@@ -135,6 +135,11 @@ typedef struct itk_fused_args {
     int thresholds_per_row;     /* with shards > 1: thresholds has [Q] entries (one per row, shared by its
                                  * shards) and a shard that finds fewer than 2048 candidates returns them
                                  * all instead of failing; the merge decides whether the row is complete */
+    const int32_t* tile_table;  /* paged keys (null = contiguous): physical 128-key tile of each logical
+                                 * tile, [ceil(keys/128)], every entry in [0, physical_keys/128).  kv and
+                                 * kv_scales then are the physical pool ([physical_keys,128], [physical_keys]);
+                                 * ids, ranges and `keys` stay logical.  Not offered with diag_logits. */
+    int physical_keys;          /* rows of the pool, a multiple of 128 (ignored without tile_table) */
 } itk_fused_args;
 int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream);
 
@@ -181,6 +186,19 @@ int itk_finalize_repair(const uint64_t* accumulator_pairs, const int32_t* accumu
 int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts,
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
+
+/* Paged forms of itk_gather_sampled_kv and itk_repair_produce: the keys live in a pool of
+ * 128-key physical tiles addressed through tile_table as in itk_fused_args.  The reference
+ * has no paged layout (src/fused_index_topk/inputs.py:31-32 rejects it); these exist for
+ * serving stacks that keep the index keys in a paged cache. */
+int itk_gather_sampled_kv_paged(const void* kv, const float* kv_scales, const int32_t* sample_ids,
+                                const int32_t* tile_table, void* sampled_kv, float* sampled_scales, int keys,
+                                int physical_keys, int samples, itk_stream_t stream);
+int itk_repair_produce_paged(const void* q, const void* kv, const float* kv_scales, const float* weights,
+                             const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
+                             uint64_t* repair_pairs, int rows, int keys, int chunk_lo, int chunk_hi, int block_begin,
+                             int block_stride, int num_blocks, const int32_t* tile_table, int physical_keys,
+                             int* status, itk_stream_t stream);
 
 /* Row-wise e4m3 quantisation of operator inputs on the device: the step before the
  * operator.  For each of `rows` rows of ITK_HEAD_DIM elements
