@@ -508,7 +508,17 @@ int itk_finalize_repair(const uint64_t* accumulator_pairs, const int32_t* accumu
 int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts,
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream) {
+    return itk_merge_shard_lists(source_pairs, source_counts, sources, out_ids, out_pairs, out_counts, rows, nullptr,
+                                 nullptr, nullptr, nullptr, 0, 0, stream);
+}
+
+int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
+                          int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
+                          const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
+                          const int32_t* k_end, int key_lo, int key_hi, itk_stream_t stream) {
     ITK_REQUIRE(source_pairs && source_counts, "source tables must not be null");
+    ITK_REQUIRE(failure_flags == nullptr || (shard_flags && k_start && k_end && key_hi > key_lo && key_lo >= 0),
+                "a row verdict needs shard_flags, k_start, k_end and 0 <= key_lo < key_hi");
     ITK_REQUIRE(sources >= 1 && sources <= kMaxPairSources, "need 1 <= sources <= %d", kMaxPairSources);
     ITK_REQUIRE(out_ids != nullptr || out_pairs != nullptr, "need out_ids or out_pairs");
     ITK_REQUIRE(rows > 0, "need rows > 0");
@@ -526,6 +536,12 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
     params.out_ids = out_ids;
     params.out_pairs = out_pairs;
     params.out_counts = out_counts;
+    params.verdict_flags = failure_flags;
+    params.shard_flags = shard_flags;
+    params.k_start = k_start;
+    params.k_end = k_end;
+    params.key_lo = key_lo;
+    params.key_hi = key_hi;
     itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (lists)");
 }

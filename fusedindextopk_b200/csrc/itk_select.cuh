@@ -76,7 +76,23 @@ struct PairTopKParams {
     int32_t* out_ids;               // null or [rows, 2048]
     int32_t* out_counts;            // null or [rows]
     uint8_t* clear_flags;           // null, or flag reset to 0 for rows that produced a full result
+    // Merge of the key shards of one launch: verdict_flags[row] (null = off) becomes 1 when a shard of
+    // the row overflowed (shard_flags [sources, rows]) or the union holds fewer than
+    // min(2048, keys of the row inside [key_lo, key_hi)) pairs, else 0.
+    uint8_t* verdict_flags;
+    const uint8_t* shard_flags;
+    const int32_t* k_start;
+    const int32_t* k_end;
+    int key_lo, key_hi;
 };
+
+__device__ __forceinline__ void write_shard_verdict(const PairTopKParams& p, int row, int produced) {
+    if (p.verdict_flags == nullptr) return;
+    int failed = 0;
+    for (int s = 0; s < p.num_sources; ++s) failed |= p.shard_flags[static_cast<long long>(s) * p.rows + row];
+    const int wanted = min(max(min(p.k_end[row], p.key_hi) - max(p.k_start[row], p.key_lo), 0), kTopK);
+    p.verdict_flags[row] = (failed != 0 || produced < wanted) ? 1 : 0;
+}
 
 struct PairShared {
     int hist[256];
@@ -157,6 +173,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
             if (tx == 0) {
                 if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(error);
                 if (p.out_counts != nullptr) p.out_counts[row] = 0;
+                write_shard_verdict(p, row, 0);
             }
             continue;
         }
@@ -172,6 +189,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
             if (tx == 0) {
                 if (p.out_counts != nullptr) p.out_counts[row] = count;
                 if (p.clear_flags != nullptr && count == kTopK) p.clear_flags[row] = 0;
+                write_shard_verdict(p, row, count);
             }
             continue;
         }
@@ -247,6 +265,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
                 if (p.out_counts != nullptr) p.out_counts[row] = kTopK;
                 if (p.clear_flags != nullptr) p.clear_flags[row] = 0;
             }
+            write_shard_verdict(p, row, consistent ? kTopK : 0);
         }
     }
 }

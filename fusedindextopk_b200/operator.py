@@ -282,16 +282,12 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         shards = args.shards
         pair_table = _lib.pointer_table([ws.shard_pairs[s] for s in range(shards)])
         count_table = _lib.pointer_table([ws.shard_counts[s] for s in range(shards)])
-        check(library.itk_merge_candidate_lists(
+        # the merge also decides which rows are complete: no shard overflowed and the union holds
+        # min(2048, valid keys) candidates; the others go to the repair graph
+        check(library.itk_merge_shard_lists(
             pair_table, count_table, shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
-            ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows, stream))
-        # a row is complete when no shard overflowed and the union holds min(2048, valid keys) candidates
-        lo = k_start.clamp(min=key_lo)
-        hi = k_end.clamp(max=args.key_hi)
-        wanted = (hi - lo).clamp(min=0, max=TOP_K)
-        merged_counts = ws.output_counts if want_pairs else ws.merged_counts
-        incomplete = ws.shard_flags.amax(dim=0).bool() | (merged_counts < wanted)
-        ws.failure_flags.copy_(incomplete)
+            ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows,
+            ptr(ws.shard_flags), ptr(ws.failure_flags), ptr(k_start), ptr(k_end), key_lo, args.key_hi, stream))
     return ws.output_ids
 
 

@@ -187,6 +187,17 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
+/* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1,
+ * thresholds_per_row), which also decides per row whether the result is complete:
+ * failure_flags[row] = 1 when any shard of the row reported an overflow
+ * (shard_flags [sources, rows], the launch's failure_flags) or the union holds fewer than
+ * min(2048, number of keys of the row inside [key_lo, key_hi)) pairs, else 0.  Such rows
+ * go to the repair graph.  No counterpart in the reference (one unit per query block there). */
+int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
+                          int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
+                          const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
+                          const int32_t* k_end, int key_lo, int key_hi, itk_stream_t stream);
+
 /* Paged forms of itk_gather_sampled_kv and itk_repair_produce: the keys live in a pool of
  * 128-key physical tiles addressed through tile_table as in itk_fused_args.  The reference
  * has no paged layout (src/fused_index_topk/inputs.py:31-32 rejects it); these exist for
