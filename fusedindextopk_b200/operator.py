@@ -79,7 +79,9 @@ def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigma
     if context_tokens <= target:
         empty = torch.zeros(0, dtype=torch.int32, device=device)
         return SamplePlan(context_tokens, 0, 0, target, empty, False)
-    elements = sampling.production_sample_elements(context_tokens)
+    # Beyond the reference's longest context (163840 keys) its schedule would ask for more samples than
+    # the prepass kernel keeps per row (2048); the guarded rank is valid for any sample size, so clamp.
+    elements = min(sampling.production_sample_elements(context_tokens), TOP_K)
     rank = sampling.guarded_sample_rank(
         elements, context_tokens, target_candidates=target, guard_sigmas=guard_sigmas
     )

@@ -83,3 +83,26 @@ def test_random_ranges_and_shapes_are_exact(device, seed):
         plain.check_status()
         _assert_exact(first, logits, host.k_start, host.k_end, keys)
         _assert_exact(again, logits, host.k_start, host.k_end, keys)
+
+
+def test_largest_key_count_the_library_accepts(device):
+    """262144 keys (the 16-bit segment-relative candidate id limit), beyond the reference's 163840."""
+
+    from fusedindextopk_b200 import _lib
+
+    rows, keys = 6, _lib.MAX_KEYS
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=12)
+    gpu = inputs_to(host, device)
+    tensors = (gpu.q, gpu.kv, gpu.kv_scales, gpu.weights, gpu.k_start, gpu.k_end)
+    ids = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end).clone()
+    plain = operator.make_workspace(rows, keys, device, key_shards=1)
+    assert plain.plan.sample_elements == 2048
+    operator.run_sample_thresholds(plain, *tensors)
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(plain, *tensors, diag_logits=logits, force_compute=True)
+    torch.cuda.synchronize()
+    plain.check_status()
+    _assert_exact(ids, logits, host.k_start, host.k_end, keys)
+    with pytest.raises(ValueError):
+        too_many = torch.empty((keys + 128, 128), dtype=torch.float8_e4m3fn, device=device)
+        fused_index_topk(gpu.q, (too_many, torch.ones(keys + 128, device=device)), gpu.weights, gpu.k_start, gpu.k_end)
