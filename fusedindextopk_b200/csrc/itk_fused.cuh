@@ -597,15 +597,20 @@ __device__ __forceinline__ void emit_row(RowSelect& rs, const RowView& v, int la
         if (out_pairs != nullptr) out_pairs[at] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
     };
     // One candidate per lane (score 0: none); `key()` is only evaluated for the candidates that are written.
+    // No divergent branch on the common path: a lane that writes nothing aims past the end, and the
+    // tie tickets (about one per row) sit behind a warp-uniform test.
     const auto place = [&](uint32_t score, auto&& key) {
         const bool is_greater = score > cutoff;
         const unsigned ballot = __ballot_sync(0xffffffffu, is_greater);
-        if (is_greater) {
-            write(position + __popc(ballot & below), score, key());
-        } else if (score == cutoff && cutoff != 0u) {
-            const int ticket = atomicAdd(&rs.tickets, 1);
-            if (ticket < equal_needed) write(greater_total + ticket, score, key());
+        const bool tie = score == cutoff && cutoff != 0u;
+        int at = is_greater ? position + __popc(ballot & below) : kTopK;
+        if (__any_sync(0xffffffffu, tie)) {
+            if (tie) {
+                const int ticket = atomicAdd(&rs.tickets, 1);
+                if (ticket < equal_needed) at = greater_total + ticket;
+            }
         }
+        write(at, score, key());
         position += __popc(ballot);
     };
     {
