@@ -368,14 +368,21 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
             workspace = make_workspace(rows, keys, q.device, seed=seed)
             _WORKSPACES[key] = workspace
     _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
-    tensors = (q, kv, kv_scales, weights, k_start, k_end)
+    return replay_or_run(workspace, (q, kv, kv_scales, weights, k_start, k_end), use_graph=use_graph)
+
+
+def replay_or_run(workspace: Workspace, tensors, *, tile_table=None, use_graph: bool = True) -> Any:
+    """One operator call: a graph replay from the second call with the same tensor addresses on."""
+
     import torch
 
     if use_graph and not torch.cuda.is_current_stream_capturing():
         key = tuple(int(tensor.data_ptr()) for tensor in tensors)
+        if tile_table is not None:
+            key += (int(tile_table.data_ptr()),)
         graph = workspace.graphs.get(key)
         if graph is None and key in workspace.seen_inputs and len(workspace.graphs) < 4:
-            graph = _capture_operator(workspace, tensors)
+            graph = _capture_operator(workspace, tensors, tile_table)
             if graph is not None:
                 workspace.graphs[key] = graph
         if len(workspace.seen_inputs) < 64:
@@ -383,10 +390,10 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
         if graph is not None:
             graph.replay()
             return workspace.output_ids
-    return run_operator(workspace, *tensors)
+    return run_operator(workspace, *tensors, tile_table=tile_table)
 
 
-def _capture_operator(workspace: Workspace, tensors) -> Any:
+def _capture_operator(workspace: Workspace, tensors, tile_table=None) -> Any:
     """One operator call as a CUDA graph, or None when the capture fails (the caller launches directly)."""
 
     import torch
@@ -395,7 +402,7 @@ def _capture_operator(workspace: Workspace, tensors) -> Any:
     try:
         torch.cuda.synchronize(workspace.device)
         with torch.cuda.graph(graph):
-            run_operator(workspace, *tensors)
+            run_operator(workspace, *tensors, tile_table=tile_table)
         return graph
     except Exception:   # noqa: BLE001 - any capture problem falls back to direct launches
         torch.cuda.synchronize(workspace.device)

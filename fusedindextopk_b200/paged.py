@@ -20,7 +20,7 @@ from __future__ import annotations
 from typing import Any
 
 from . import _lib
-from .operator import _WORKSPACES, Workspace, _require, make_workspace, run_operator
+from .operator import _WORKSPACES, Workspace, _require, make_workspace, replay_or_run
 
 TILE_KEYS = 128
 
@@ -87,12 +87,13 @@ def scatter_to_pages(kv: Any, kv_scales: Any, page_size: int, *, pool_pages: int
 
 def fused_index_topk_paged(q: Any, kv_pool_pair: tuple[Any, Any], block_table: Any, keys: int, weights: Any,
                            k_start: Any, k_end: Any, top_k: int = _lib.TOP_K, *, workspace: Workspace | None = None,
-                           seed: int = 0) -> Any:
+                           seed: int = 0, use_graph: bool = True) -> Any:
     """Exact Top-K ids (logical key positions) with the keys read through a block table.
 
     ``kv_pool_pair = (kv_pool [P, page_size, 128] e4m3, scale_pool [P, page_size] fp32)``;
     ``block_table`` int32 ``[ceil(keys / page_size)]`` on the same device; ``keys`` is the logical
-    number of keys.  Returns int32 ``[Q, K]`` like ``fused_index_topk``.
+    number of keys.  Returns int32 ``[Q, K]`` like ``fused_index_topk`` (the workspace's output buffer; from the
+    second call with the same tensors and block table on, one CUDA-graph replay).
     """
 
     import torch
@@ -128,7 +129,8 @@ def fused_index_topk_paged(q: Any, kv_pool_pair: tuple[Any, Any], block_table: A
     _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
     flat_kv = kv_pool.view(pages * page_size, _lib.HEAD_DIM)
     flat_scales = scale_pool.view(pages * page_size)
-    return run_operator(workspace, q, flat_kv, flat_scales, weights, k_start, k_end, tile_table=tile_table)
+    return replay_or_run(workspace, (q, flat_kv, flat_scales, weights, k_start, k_end), tile_table=tile_table,
+                         use_graph=use_graph)
 
 
 __all__ = ["expand_block_table", "fused_index_topk_paged", "scatter_to_pages"]

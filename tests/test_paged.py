@@ -123,6 +123,29 @@ def test_paged_batch_through_one_block_table(device):
 
 
 @pytest.mark.gpu
+def test_repeated_paged_calls_replay_a_graph_and_follow_a_changed_table(device):
+    from fusedindextopk_b200 import fused_index_topk
+
+    host = make_workload_inputs("c1", query_tokens=48, context_tokens=8192, seed=3)
+    q, kv, scales = host.q.to(device), host.kv.to(device), host.kv_scales.to(device)
+    weights, k_start, k_end = host.weights.to(device), host.k_start.to(device), host.k_end.to(device)
+    want = fused_index_topk(q, (kv, scales), weights, k_start, k_end).clone().sort(dim=-1).values
+    pool, scale_pool, block_table = paged.scatter_to_pages(kv, scales, 256, generator=torch.Generator().manual_seed(8))
+    results = [paged.fused_index_topk_paged(q, (pool, scale_pool), block_table, 8192, weights, k_start, k_end).clone()
+               for _ in range(4)]
+    for got in results:
+        assert torch.equal(got.sort(dim=-1).values, want)
+    # move two pages inside the pool and update the table in place: the next call must follow
+    a, b = int(block_table[0]), int(block_table[1])
+    raw = pool.view(torch.uint8)
+    raw[[a, b]] = raw[[b, a]]
+    scale_pool[[a, b]] = scale_pool[[b, a]]
+    block_table[0], block_table[1] = b, a
+    again = paged.fused_index_topk_paged(q, (pool, scale_pool), block_table, 8192, weights, k_start, k_end).clone()
+    assert torch.equal(again.sort(dim=-1).values, want)
+
+
+@pytest.mark.gpu
 def test_paged_argument_errors(device):
     host = make_workload_inputs("c1", query_tokens=8, context_tokens=2048, seed=1)
     q, kv, scales = host.q.to(device), host.kv.to(device), host.kv_scales.to(device)
