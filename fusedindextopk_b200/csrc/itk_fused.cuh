@@ -304,6 +304,15 @@ __device__ __forceinline__ void row_sync(RowBarrier& rb) {
     ++rb.phase;
 }
 
+// The same barrier for warps that expect to wait long (one warp of the row works alone): a failed
+// probe parks the warp instead of competing with the working warp for issue slots.
+__device__ __forceinline__ void row_sync_parked(RowBarrier& rb) {
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);
+    if (!mbar_wait<500>(rb.bar, rb.phase & 1u, rb.abort_flag)) *rb.abort_flag = 1;
+    ++rb.phase;
+}
+
 __device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
     return static_cast<int>(((packed >> 5) << 7) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
 }
@@ -739,16 +748,77 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     if (!(overflow || total < wanted) && total > kTopK) lap(rb, 6);
 }
 
-// Threshold of one row = rank-th largest valid sampled score (kModeSample): the radix selection over
-// the row's candidates by the row's four warps (a single warp walking the candidates once per score
-// bit took twice as long; it was four fifths of the sampling launch).  Called by the 128 threads of
-// the row after the barrier that publishes the counts.
-__device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
+// The rank-th largest (1-based) of at most 32 * SLOTS ordered score words spread over the four
+// segments of a row, by ONE warp: every lane keeps SLOTS values in registers and the answer is
+// fixed bit by bit from the top, counting the live values that have the bit set (one warp reduction per bit).
+// No shared-memory histogram and no barrier between the row's warps.
+template <int SLOTS>
+__device__ __forceinline__ uint32_t ballot_rank_select(const uint32_t* row_scores, const int (&counts)[kSegments],
+                                                       int total, int rank, int lane) {
+    static_assert(kSegments == 4, "the segment lookup below is written for four segments");
+    const int b1 = counts[0], b2 = b1 + counts[1], b3 = b2 + counts[2];
+    // a value that can no longer be the answer is set to 0, which has no bit to count
+    uint32_t value[SLOTS];
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+        const int index = lane + 32 * i;
+        const bool valid = index < total;
+        const int segment = (index >= b1) + (index >= b2) + (index >= b3);
+        const int base = segment == 0 ? 0 : segment == 1 ? b1 : segment == 2 ? b2 : b3;
+        value[i] = valid ? row_scores[segment * kSegCap + (index - base)] : 0u;
+    }
+    // Bits above the highest one in which two values differ are common to all of them; below, every
+    // bit about halves the live set, and once a single value is left it is the answer.
+    uint32_t any_bits = 0, all_bits = 0xffffffffu;
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+        any_bits |= value[i];
+        all_bits &= lane + 32 * i < total ? value[i] : 0xffffffffu;
+    }
+    any_bits = __reduce_or_sync(0xffffffffu, any_bits);
+    all_bits = __reduce_and_sync(0xffffffffu, all_bits);
+    const uint32_t differing = any_bits ^ all_bits;
+    if (differing == 0u) return all_bits;                      // all values are equal
+    const int top = 31 - __clz(static_cast<int>(differing));
+    uint32_t prefix = top == 31 ? 0u : all_bits & ~((2u << top) - 1u);
+    int alive = total;
+#pragma unroll 1
+    for (int bit = top; bit >= 0 && alive > 1; --bit) {
+        const uint32_t probe = 1u << bit;
+        int mine = 0;
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i) mine += static_cast<int>((value[i] >> bit) & 1u);
+        const int with_bit = __reduce_add_sync(0xffffffffu, mine);
+        const bool take = rank <= with_bit;   // the answer has this bit set
+        if (take) prefix |= probe;
+        else rank -= with_bit;
+        alive = take ? with_bit : alive - with_bit;
+        // keep the values that agree with the answer on this bit (zeros stay zero either way)
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i) value[i] = ((value[i] & probe) != 0) == take ? value[i] : 0u;
+    }
+    if (alive == 1) {
+        // the one value left (everything else is zero by now)
+        uint32_t last = 0;
+#pragma unroll
+        for (int i = 0; i < SLOTS; ++i) last = max(last, value[i]);
+        return __reduce_max_sync(0xffffffffu, last);
+    }
+    return prefix;
+}
+
+// Threshold of one row = rank-th largest valid sampled score (kModeSample).  Up to 512 samples are
+// selected by one warp from registers (ballot_rank_select; row r by its warp of lane quarter r, the
+// other three warps park at the row barrier); more samples go through the radix rounds of the row's
+// four warps.  Called by the 128 threads of the row after the barrier that publishes the counts;
+// returns whether the one-warp path was taken.
+__device__ __forceinline__ bool sample_threshold_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
                                                      bool has_tiles, RowBarrier& rb, int tid) {
     const int row = u.row0 + r;
     const int start = __ldg(p.k_start + row);
     const int end = __ldg(p.k_end + row);
     float result = __int_as_float(0xff800000);
+    bool solo = false;   // the row's first warp selected alone; the others only wait for it
     if (has_tiles && end - start > p.target_candidates) {
         const int segment = tid >> 5;
         int total = 0;
@@ -758,7 +828,18 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
             total += sh.counts[r][s];
             overflow = overflow || sh.counts[r][s] > kSegCap;
         }
-        if (!overflow && total >= p.sample_rank) {   // the same decision in all 128 threads
+        if (!overflow && total >= p.sample_rank && total <= 512) {
+            // row r is selected by its warp of lane quarter r: the four working warps of a unit then sit on
+            // four different schedulers
+            solo = true;
+            if (segment == (r & 3)) {
+                const int counts[kSegments] = {sh.counts[r][0], sh.counts[r][1], sh.counts[r][2], sh.counts[r][3]};
+                const uint32_t cutoff = total <= 256
+                    ? ballot_rank_select<8>(sh.cand_scores[r], counts, total, p.sample_rank, tid & 31)
+                    : ballot_rank_select<16>(sh.cand_scores[r], counts, total, p.sample_rank, tid & 31);
+                result = ordered_to_float(cutoff);
+            }
+        } else if (!overflow && total >= p.sample_rank) {   // the same decision in all 128 threads
             RowView view;
             view.segment = segment;
             view.scores = sh.cand_scores[r] + segment * kSegCap;
@@ -772,7 +853,8 @@ __device__ __forceinline__ void sample_threshold_row(FusedShared& sh, const Fuse
             result = ordered_to_float(cutoff);
         }
     }
-    if (tid == 0) p.thresholds_out[row] = result;
+    if (solo ? tid == (r & 3) * 32 : tid == 0) p.thresholds_out[row] = result;
+    return solo;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -1091,16 +1173,20 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         RowBarrier rb{&sh.row_bar[own_r], 0u, abort_flag, DIAG ? laps : nullptr, 0};
         const auto finish_row = [&](const Unit& u, bool has_tiles) {
             const long long begin = DIAG ? clock64() : 0;
+            bool solo = false;
             if (own_r < u.nrows) {
                 if (MODE == kModeTopK) {
 #if ITK_EXPERIMENT < 6
                     if (!(DIAG && (p.debug_skip & 1))) select_topk_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
 #endif
                 } else if (MODE == kModeSample) {
-                    sample_threshold_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
+                    solo = sample_threshold_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
                 }
             }
-            if (MODE == kModeSample) row_sync(rb);   // the row's buffers may be written again
+            if (MODE == kModeSample) {   // the row's buffers may be written again
+                if (solo && quarter != (own_r & 3)) row_sync_parked(rb);
+                else row_sync(rb);
+            }
             if (DIAG) select_cycles += clock64() - begin;
         };
         for (int iter = 0; ok; ++iter) {
