@@ -78,9 +78,14 @@ def test_library_loads_and_reports_resources(device):
     assert int(report["sm_count"]) >= 100
 
 
-@pytest.mark.parametrize("rows,keys", [(8, 8192), (5, 8192), (1, 9000)])
-def test_sampled_scores_and_thresholds(device, rows, keys):
-    host = make_workload_inputs("c0", query_tokens=rows, context_tokens=keys)
+@pytest.mark.parametrize(
+    "workload,rows,keys",
+    [("c0", 8, 8192), ("c0", 5, 8192), ("c0", 1, 9000),      # 512 samples: one-warp selection, 16 values per lane
+     ("c1", 16, 16384), ("c4", 9, 16384),                   # 256 samples: 8 values per lane; c4 ties everywhere
+     ("c4", 8, 8192), ("c2", 4, 40000), ("c3", 3, 163840)],   # ties with 512; 1024 and 2048 samples: radix rounds
+)
+def test_sampled_scores_and_thresholds(device, workload, rows, keys):
+    host = make_workload_inputs(workload, query_tokens=rows, context_tokens=keys)
     gpu = inputs_to(host, device)
     ws = operator.make_workspace(rows, keys, device)
     plan = ws.plan
