@@ -638,10 +638,33 @@ __device__ __forceinline__ void emit_row(RowSelect& rs, const RowView& v, int la
                 score[k] = live ? scores[i] : 0u;
                 id[k] = live ? ids[i] : 0u;
             }
+            // The four ballots first, then the positions, then the stores: the votes of one group do not
+            // wait for each other's stores, and the tie test costs one vote per group (dead lanes carry
+            // score 0, which is neither greater than nor tied with a cutoff).
+            unsigned ballot[4];
+            bool tie = false;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                if (base + 32 * k < in_smem) place(score[k], [&]() { return decode_key(id[k], segment); });
+                ballot[k] = __ballot_sync(0xffffffffu, score[k] > cutoff);
+                tie = tie || (score[k] == cutoff && cutoff != 0u);
             }
+            int at[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                at[k] = score[k] > cutoff ? position + __popc(ballot[k] & below) : kTopK;
+                position += __popc(ballot[k]);
+            }
+            if (__any_sync(0xffffffffu, tie)) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (score[k] == cutoff && cutoff != 0u) {
+                        const int ticket = atomicAdd(&rs.tickets, 1);
+                        if (ticket < equal_needed) at[k] = greater_total + ticket;
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) write(at[k], score[k], decode_key(id[k], segment));
         }
     }
 #pragma unroll 1
@@ -1308,16 +1331,17 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const int position = count + __popc(ballot & ((1u << lane) - 1u));
                 count += __popc(ballot);
                 const uint32_t score_bits = ordered_bits(score);
-                if (MODE == kModeTopK && active) {
+                // The three shared-memory writes are predicated instructions, not branches (an inactive lane
+                // computes an address it never uses).
+                if (MODE == kModeTopK) {
                     // one more candidate in its bin of the row's score histogram (16-bit counters)
                     const uint32_t bin = __float_as_uint(ordered_to_float(score_bits) - threshold) >> 23;
-                    red_shared_add_u32(hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
+                    red_shared_add_u32_if(active, hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
                 }
-                if (active && position < kSegCap) {
-                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), score_bits);
-                    // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
-                    st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
-                }
+                const bool keep = active && position < kSegCap;
+                st_shared_u32_if(keep, score_slots + 4u * static_cast<uint32_t>(position), score_bits);
+                // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
+                st_shared_u16_if(keep, id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
                 if (MODE == kModeTopK && count > kSegCap) {
                     // warp-uniform and rare: the segment is full, later candidates go to the global spill
                     if (active && position >= kSegCap && position < kSegCap + kSpillSegCap) {
