@@ -1331,17 +1331,16 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const int position = count + __popc(ballot & ((1u << lane) - 1u));
                 count += __popc(ballot);
                 const uint32_t score_bits = ordered_bits(score);
-                // The three shared-memory writes are predicated instructions, not branches (an inactive lane
-                // computes an address it never uses).
-                if (MODE == kModeTopK) {
+                if (MODE == kModeTopK && active) {
                     // one more candidate in its bin of the row's score histogram (16-bit counters)
                     const uint32_t bin = __float_as_uint(ordered_to_float(score_bits) - threshold) >> 23;
-                    red_shared_add_u32_if(active, hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
+                    red_shared_add_u32(hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
                 }
-                const bool keep = active && position < kSegCap;
-                st_shared_u32_if(keep, score_slots + 4u * static_cast<uint32_t>(position), score_bits);
-                // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
-                st_shared_u16_if(keep, id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
+                if (active && position < kSegCap) {
+                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), score_bits);
+                    // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
+                    st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
+                }
                 if (MODE == kModeTopK && count > kSegCap) {
                     // warp-uniform and rare: the segment is full, later candidates go to the global spill
                     if (active && position >= kSegCap && position < kSegCap + kSpillSegCap) {

@@ -132,23 +132,6 @@ __device__ __forceinline__ void red_shared_add_u32(uint32_t address, uint32_t va
     asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
 }
 
-// The same three with the condition as an instruction predicate: a store or add under a C++ `if`
-// costs a divergent branch around the asm statement, which a hot loop pays per iteration.
-__device__ __forceinline__ void st_shared_u32_if(bool condition, uint32_t address, uint32_t value) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %0, 0;\n\t@p st.shared.u32 [%1], %2;\n\t}"
-                 ::"r"(static_cast<uint32_t>(condition)), "r"(address), "r"(value) : "memory");
-}
-
-__device__ __forceinline__ void st_shared_u16_if(bool condition, uint32_t address, uint32_t value) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %0, 0;\n\t@p st.shared.u16 [%1], %2;\n\t}"
-                 ::"r"(static_cast<uint32_t>(condition)), "r"(address), "h"(static_cast<uint16_t>(value)) : "memory");
-}
-
-__device__ __forceinline__ void red_shared_add_u32_if(bool condition, uint32_t address, uint32_t value) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %0, 0;\n\t@p red.shared.add.u32 [%1], %2;\n\t}"
-                 ::"r"(static_cast<uint32_t>(condition)), "r"(address), "r"(value) : "memory");
-}
-
 // ------------------------------------------------------------------ TMA
 
 // Tiled 2-D load of one box into this CTA's shared memory; completion is
