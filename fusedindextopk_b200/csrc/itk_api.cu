@@ -438,6 +438,52 @@ int itk_repair_produce_paged(const void* q, const void* kv, const float* kv_scal
     return launch_fused<kModeRepair>(params, false, fused_grid(device, num_blocks, 0), stream);
 }
 
+int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales, const float* weights,
+                           const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
+                           uint64_t* repair_pairs, int rows, int keys, int block_begin, int block_stride,
+                           int num_blocks, const int32_t* tile_table, int physical_keys, int* status,
+                           itk_stream_t stream) {
+    ITK_REQUIRE(q && kv && kv_scales && weights && k_start && k_end && failure_flags && repair_pairs && status,
+                "repair producer pointers must not be null");
+    ITK_REQUIRE(rows > 0 && keys > 0 && keys <= ITK_MAX_KEYS, "need rows > 0 and 0 < keys <= %d", ITK_MAX_KEYS);
+    ITK_REQUIRE(tile_table == nullptr || (physical_keys >= kTileKeys && physical_keys % kTileKeys == 0),
+                "physical_keys must be a positive multiple of 128");
+    const int total_blocks = (rows + kBlockQ - 1) / kBlockQ;
+    ITK_REQUIRE(block_stride >= 1 && block_begin >= 0 && num_blocks >= 0 &&
+                    (num_blocks == 0 || block_begin + static_cast<long long>(num_blocks - 1) * block_stride < total_blocks),
+                "owned query blocks must lie inside the %d blocks of the problem", total_blocks);
+    ITK_REQUIRE(aligned16(q) && aligned16(kv) && aligned16(weights), "q, kv, weights must be 16-byte aligned");
+    if (num_blocks == 0) return ITK_OK;
+    int device = 0;
+    int rc = init_current_device(&device);
+    if (rc != ITK_OK) return rc;
+    const int chunks = (keys + kRepairChunk - 1) / kRepairChunk;
+    FusedParams params{};
+    if ((rc = make_row_map(&params.map_q, q, static_cast<long long>(rows) * kHeads, kUmmaN)) != ITK_OK) return rc;
+    if ((rc = make_row_map(&params.map_kv, kv, tile_table != nullptr ? physical_keys : keys, kTileKeys)) != ITK_OK) return rc;
+    params.kv_scales = kv_scales;
+    params.tile_table = tile_table;
+    params.weights = weights;
+    params.k_start = k_start;
+    params.k_end = k_end;
+    params.failure_flags = const_cast<uint8_t*>(failure_flags);
+    params.repair_pairs = repair_pairs;
+    params.status = status;
+    params.rows = rows;
+    params.keys = keys;
+    params.key_lo = 0;
+    params.key_hi = keys;
+    params.shard_keys = kRepairChunk;
+    params.shards = chunks;          // one work unit per (query block, chunk)
+    params.flags_per_row = 1;
+    params.block_begin = block_begin;
+    params.block_stride = block_stride;
+    params.num_blocks = num_blocks;
+    params.top_k_min_valid = kTopK;
+    return launch_fused<kModeRepair>(params, false, fused_grid(device, static_cast<long long>(num_blocks) * chunks, 0),
+                                     stream);
+}
+
 int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_start, const int32_t* chunk_end,
                          const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
                          uint8_t* repair_error_flags, int rows, int first_chunk, itk_stream_t stream) {

@@ -147,6 +147,8 @@ struct FusedParams {
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
     int row_thresholds;         // 1: thresholds are per row (shared by the row's shards); a shard that finds
                                 // fewer than 2048 candidates returns them all instead of failing
+    int flags_per_row;          // kModeRepair with shards > 1: failure_flags has [rows] entries (one launch over
+                                // all repair chunks of every flagged row), repair_pairs stays [shards*rows, 16384]
 };
 
 // Per-row scratch of the selection.
@@ -248,7 +250,7 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
             if (MODE == kModeTopK) {
                 needed = e - s > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
             } else {
-                needed = e > s && p.failure_flags[static_cast<long long>(u.shard) * p.rows + row] != 0;
+                needed = e > s && p.failure_flags[(p.flags_per_row ? 0ll : static_cast<long long>(u.shard) * p.rows) + row] != 0;
             }
         }
         if (needed) {
@@ -929,7 +931,7 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
                 if (valid > kTopK) state.threshold = __ldg(p.thresholds + (p.row_thresholds ? row : state.slot));
                 state.on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
             } else {
-                state.on = p.failure_flags[state.slot] != 0;
+                state.on = p.failure_flags[p.flags_per_row ? row : state.slot] != 0;
             }
         }
     }
@@ -999,7 +1001,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         // The usual case is that the fast path flagged no row: find that out with one parallel scan
         // of the flags before any barrier, TMEM or descriptor is set up.
         int any = 0;
-        const int flags = p.shards * p.rows;
+        const int flags = (p.flags_per_row ? 1 : p.shards) * p.rows;
         for (int i = static_cast<int>(threadIdx.x); i < flags; i += kThreads) any |= p.failure_flags[i];
         if (__syncthreads_or(any) == 0) return;
     }

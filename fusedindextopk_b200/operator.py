@@ -70,6 +70,9 @@ class SamplePlan:
     enabled: bool            # False: every row has few enough keys, thresholds are -inf
 
 
+REPAIR_ALL_CHUNKS_BYTES_LIMIT = 16 << 30
+
+
 def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigmas: float = 2.0) -> SamplePlan:
     """Sample size, guarded rank and sample positions (``kernel/plugin.py:187-201``)."""
 
@@ -168,8 +171,14 @@ def make_workspace(
         buffers["output_counts"] = torch.zeros(rows, device=device, dtype=i32)
     if repair:
         chunks = sizes.repair_chunks
+        # One buffer per chunk lets a single launch rescan all chunks of the flagged rows on different SMs
+        # (a flagged row of a 160 K context otherwise keeps one SM busy for a whole pass over the context);
+        # 512 MiB per chunk at 4096 rows, which a 180 GB device affords.  Very large problems keep the
+        # one-chunk buffer and the chunk-by-chunk launches.
+        all_chunks_bytes = chunks * rows * _lib.REPAIR_CHUNK * 8
+        parallel_chunks = chunks > 1 and all_chunks_bytes <= REPAIR_ALL_CHUNKS_BYTES_LIMIT
         buffers.update(
-            repair_pairs=empty((rows, _lib.REPAIR_CHUNK), i64),
+            repair_pairs=empty((chunks, rows, _lib.REPAIR_CHUNK) if parallel_chunks else (rows, _lib.REPAIR_CHUNK), i64),
             local_pairs=empty((rows, TOP_K), i64),
             local_counts=torch.zeros(rows, device=device, dtype=i32),
             accumulator_pairs=empty((rows, TOP_K), i64),
@@ -305,18 +314,29 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
     check(library.itk_update_chunk_ranges(
         ptr(k_start), ptr(k_end), ptr(ws.chunk_starts), ptr(ws.chunk_ends), ws.rows, ws.keys, stream
     ))
+    physical_keys = int(kv.shape[0]) if tile_table is not None else 0
+    all_chunks = ws.repair_pairs.dim() == 3 and key_lo == 0 and key_hi == ws.keys
+    if all_chunks:
+        check(library.itk_repair_produce_all(
+            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
+            ptr(ws.repair_pairs), ws.rows, ws.keys, ws.block_begin, ws.block_stride, ws.num_blocks,
+            ptr(tile_table), physical_keys, ptr(ws.status), stream,
+        ))
     first = True
     for chunk_index, chunk_lo in enumerate(range(0, ws.keys, _lib.REPAIR_CHUNK)):
         chunk_hi = min(ws.keys, chunk_lo + _lib.REPAIR_CHUNK)
         if chunk_hi <= key_lo or chunk_lo >= key_hi:
             continue
-        check(library.itk_repair_produce_paged(
-            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
-            ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
-            ws.num_blocks, ptr(tile_table), int(kv.shape[0]) if tile_table is not None else 0, ptr(ws.status), stream,
-        ))
+        chunk_pairs = ws.repair_pairs[chunk_index] if all_chunks else (
+            ws.repair_pairs[0] if ws.repair_pairs.dim() == 3 else ws.repair_pairs)
+        if not all_chunks:
+            check(library.itk_repair_produce_paged(
+                ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
+                ptr(chunk_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
+                ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
+            ))
         check(library.itk_chunk_local_topk(
-            ptr(ws.repair_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
+            ptr(chunk_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
             ptr(ws.failure_flags), ptr(ws.local_pairs), ptr(ws.local_counts), ptr(ws.repair_error_flags),
             ws.rows, 1 if first else 0, stream,
         ))

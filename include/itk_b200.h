@@ -187,6 +187,19 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
+/* itk_repair_produce for every 16384-key chunk of the context in ONE launch: the work units are
+ * (query block, chunk), so the chunks of a flagged row are rescanned by different SMs at the same
+ * time instead of one after the other (a single flagged row of a 160 K context otherwise costs a
+ * whole pass of one SM over the context).  repair_pairs is [chunks, Q, 16384]; chunk c of row r is
+ * repair_pairs[(c*Q + r)*16384 ...], in the layout itk_chunk_local_topk reads.  tile_table /
+ * physical_keys as in itk_fused_args (null / 0 for contiguous keys).  The reference launches its
+ * repair producer once per chunk (src/fused_index_topk/kernel/plugin.py:333-377). */
+int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales, const float* weights,
+                           const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
+                           uint64_t* repair_pairs, int rows, int keys, int block_begin, int block_stride,
+                           int num_blocks, const int32_t* tile_table, int physical_keys, int* status,
+                           itk_stream_t stream);
+
 /* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1,
  * thresholds_per_row), which also decides per row whether the result is complete:
  * failure_flags[row] = 1 when any shard of the row reported an overflow

@@ -140,6 +140,27 @@ def test_forced_spill_and_forced_repair(device, threshold):
     score_threshold_check(indices, logits.cpu(), case)
 
 
+@pytest.mark.parametrize("rows,keys", [(10, 40000), (6, 70001)])
+def test_forced_repair_over_several_chunks_in_one_producer_launch(device, rows, keys, monkeypatch):
+    """+inf thresholds starve every row; the repair rescans 3 / 5 chunks per row.  The workspace that holds
+    all chunks (one producer launch) and the one-chunk workspace (a launch per chunk) must agree."""
+
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=keys)
+    case = PrefillCase("forced-chunks", rows, keys, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=math.inf)
+    assert ws.repair_pairs.dim() == 3 and ws.repair_pairs.shape[0] == (keys + 16383) // 16384
+    assert int(fast_flags.sum()) == rows
+    assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+    monkeypatch.setattr(operator, "REPAIR_ALL_CHUNKS_BYTES_LIMIT", 0)
+    ws_one, _, _ = _run_with_diagnostics(host, device, thresholds=math.inf)
+    assert ws_one.repair_pairs.dim() == 2
+    assert int(ws_one.failure_flags.sum()) == 0
+    assert torch.equal(ws_one.output_ids.sort(dim=-1).values, ws.output_ids.sort(dim=-1).values)
+
+
 def test_spill_path_without_overflow(device):
     """N = 8192 with threshold -inf: 2048 candidates per segment, 1280 in shared memory and 768 spilled;
     all distances to the threshold are infinite, so the selection takes its radix fallback."""
