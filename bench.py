@@ -360,7 +360,12 @@ def main() -> None:
     merged_ids = torch.empty((rows, 2048), dtype=torch.int32, device=device) if key_mode else None
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     chunks = (keys + 16383) // 16384
-    launches_per_step = ((2 if ws.plan.enabled else 0) + 1 + 1 + 3 * chunks + 1 + (1 if key_mode else 0)
+    if ws.repair_pairs.dim() == 3:
+        # all chunks of the flagged rows in one producer launch, one local Top-K launch, merges of up to 8 lists
+        repair_launches = 1 + 1 + 1 + (1 if chunks <= 8 else 1 + math.ceil((chunks - 8) / 7)) + 1
+    else:
+        repair_launches = 1 + 3 * chunks + 1
+    launches_per_step = ((2 if ws.plan.enabled else 0) + 1 + repair_launches + (1 if key_mode else 0)
                          + (1 if "shard_pairs" in ws.buffers else 0))   # the merge of intra-GPU key shards
 
     def barrier() -> None:

@@ -34,7 +34,7 @@ EXPORTED_SYMBOLS = (
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
     "itk_merge_candidate_lists", "itk_fused_topk_static", "itk_quantize_rows_e4m3",
     "itk_gather_sampled_kv_paged", "itk_repair_produce_paged", "itk_merge_shard_lists",
-    "itk_repair_produce_all",
+    "itk_repair_produce_all", "itk_chunk_local_topk_all", "itk_merge_local_lists",
 )
 
 
@@ -103,6 +103,8 @@ def load_library() -> ctypes.CDLL:
         + [c_void_p] * 4 + [c_int, c_int, c_void_p]
     )
     library.itk_repair_produce_all.argtypes = [c_void_p] * 8 + [c_int] * 5 + [c_void_p, c_int, c_void_p, c_void_p]
+    library.itk_chunk_local_topk_all.argtypes = [c_void_p] * 7 + [c_int, c_int, c_void_p]
+    library.itk_merge_local_lists.argtypes = [c_void_p, c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_void_p]
     library.itk_gather_sampled_kv_paged.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p]
     library.itk_repair_produce_paged.argtypes = [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_int, c_void_p, c_void_p]
     library.itk_quantize_rows_e4m3.argtypes = [c_void_p, c_int] + [c_void_p] * 4 + [c_longlong, c_void_p]

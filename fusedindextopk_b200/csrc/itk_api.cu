@@ -512,6 +512,75 @@ int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_star
     return launch_check("itk_pair_topk_kernel (chunk)");
 }
 
+int itk_chunk_local_topk_all(const uint64_t* repair_pairs, const int32_t* chunk_starts, const int32_t* chunk_ends,
+                             const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
+                             uint8_t* repair_error_flags, int rows, int chunks, itk_stream_t stream) {
+    ITK_REQUIRE(repair_pairs && chunk_starts && chunk_ends && failure_flags && local_pairs && local_counts &&
+                    repair_error_flags,
+                "chunk top-k pointers must not be null");
+    ITK_REQUIRE(rows > 0 && chunks > 0 && static_cast<long long>(rows) * chunks <= 0x7fffffffll,
+                "need rows > 0, chunks > 0 and rows * chunks below 2^31");
+    int device = 0;
+    const int rc = init_current_device(&device);
+    if (rc != ITK_OK) return rc;
+    // the chunks of a row run at the same time, so the error flags are cleared here, not by a first chunk
+    ITK_CUDA(cudaMemsetAsync(repair_error_flags, 0, static_cast<size_t>(rows), stream));
+    PairTopKParams params{};
+    params.sources[0] = PairSource{repair_pairs, nullptr};
+    params.num_sources = 1;
+    params.capacity = kRepairChunk;
+    params.rows = rows * chunks;
+    params.row_period = rows;
+    params.row_mask = failure_flags;
+    params.error_flags = repair_error_flags;
+    params.expect_start = chunk_starts;
+    params.expect_end = chunk_ends;
+    params.error_count_mismatch = ITK_REPAIR_ERR_COUNT;
+    params.error_selection = ITK_REPAIR_ERR_LOCAL_SELECT;
+    params.out_pairs = local_pairs;
+    params.out_counts = local_counts;
+    itk_pair_topk_kernel<<<pair_grid(device, rows * chunks), kPairThreads, kPairSmemBytes, stream>>>(params);
+    return launch_check("itk_pair_topk_kernel (all chunks)");
+}
+
+int itk_merge_local_lists(const uint64_t* local_pairs, const int32_t* local_counts, int chunks,
+                          uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint8_t* failure_flags,
+                          uint8_t* repair_error_flags, int rows, itk_stream_t stream) {
+    ITK_REQUIRE(local_pairs && local_counts && accumulator_pairs && accumulator_counts && failure_flags &&
+                    repair_error_flags,
+                "merge pointers must not be null");
+    ITK_REQUIRE(rows > 0 && chunks > 0, "need rows > 0 and chunks > 0");
+    int device = 0;
+    const int rc = init_current_device(&device);
+    if (rc != ITK_OK) return rc;
+    // up to eight lists per launch: the first launch takes eight chunks, every further one the
+    // accumulator and seven more
+    int next = 0;
+    while (next < chunks) {
+        PairTopKParams params{};
+        int used = 0;
+        if (next > 0) params.sources[used++] = PairSource{accumulator_pairs, accumulator_counts};
+        while (used < kMaxPairSources && next < chunks) {
+            params.sources[used++] = PairSource{local_pairs + static_cast<size_t>(next) * rows * kTopK,
+                                                local_counts + static_cast<size_t>(next) * rows};
+            ++next;
+        }
+        params.num_sources = used;
+        params.capacity = kTopK;
+        params.rows = rows;
+        params.row_mask = failure_flags;
+        params.error_flags = repair_error_flags;
+        params.error_count_mismatch = ITK_REPAIR_ERR_MERGE_SELECT;
+        params.error_selection = ITK_REPAIR_ERR_MERGE_SELECT;
+        params.out_pairs = accumulator_pairs;
+        params.out_counts = accumulator_counts;
+        itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
+        const int launched = launch_check("itk_pair_topk_kernel (merge of chunk lists)");
+        if (launched != ITK_OK) return launched;
+    }
+    return ITK_OK;
+}
+
 int itk_merge_topk_pairs(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* local_pairs,
                          const int32_t* local_counts, const uint8_t* failure_flags, uint8_t* repair_error_flags,
                          int rows, int first_chunk, itk_stream_t stream) {

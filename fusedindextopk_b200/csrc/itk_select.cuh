@@ -64,6 +64,8 @@ struct PairTopKParams {
     int first_source;               // sources below this index are ignored (empty accumulator)
     int capacity;                   // entries per row of every source
     int rows;
+    int row_period;                 // > 0: `rows` counts (chunk, row) pairs, chunk-major; row_mask and error_flags
+                                    // are indexed by row % row_period (one entry per query row)
     const uint8_t* row_mask;        // null, or only rows with row_mask[row] != 0 are processed
     uint8_t* error_flags;           // null, or per-row error code; rows with a nonzero code are skipped
     int clear_errors;               // reset error_flags[row] of processed rows first
@@ -121,18 +123,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
         int any = 0;
         for (int row = static_cast<int>(blockIdx.x) + tx * static_cast<int>(gridDim.x); row < p.rows;
              row += kPairThreads * static_cast<int>(gridDim.x))
-            any |= p.row_mask[row];
+            any |= p.row_mask[p.row_period > 0 ? row % p.row_period : row];
         if (__syncthreads_or(any) == 0) return;
     }
 
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
         __syncthreads();
+        const int flag_row = p.row_period > 0 ? row % p.row_period : row;
         if (tx == 0) {
             int skip = 0;
-            if (p.row_mask != nullptr && p.row_mask[row] == 0) skip = 1;
+            if (p.row_mask != nullptr && p.row_mask[flag_row] == 0) skip = 1;
             if (!skip && p.error_flags != nullptr) {
-                if (p.clear_errors) p.error_flags[row] = 0;
-                else if (p.error_flags[row] != 0) skip = 1;
+                if (p.clear_errors) p.error_flags[flag_row] = 0;
+                else if (p.error_flags[flag_row] != 0) skip = 1;
             }
             sh.skip = skip;
             sh.count = 0;
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
             error = p.error_count_mismatch;
         if (error != 0) {
             if (tx == 0) {
-                if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(error);
+                if (p.error_flags != nullptr) p.error_flags[flag_row] = static_cast<uint8_t>(error);
                 if (p.out_counts != nullptr) p.out_counts[row] = 0;
                 write_shard_verdict(p, row, 0);
             }
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
         if (tx == 0) {
             const bool consistent = equal_needed > 0 && sh.gcount == greater_total && sh.ecount >= equal_needed;
             if (!consistent) {
-                if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(p.error_selection);
+                if (p.error_flags != nullptr) p.error_flags[flag_row] = static_cast<uint8_t>(p.error_selection);
                 if (p.out_counts != nullptr) p.out_counts[row] = 0;
             } else {
                 if (p.out_counts != nullptr) p.out_counts[row] = kTopK;

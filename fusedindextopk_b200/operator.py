@@ -179,8 +179,8 @@ def make_workspace(
         parallel_chunks = chunks > 1 and all_chunks_bytes <= REPAIR_ALL_CHUNKS_BYTES_LIMIT
         buffers.update(
             repair_pairs=empty((chunks, rows, _lib.REPAIR_CHUNK) if parallel_chunks else (rows, _lib.REPAIR_CHUNK), i64),
-            local_pairs=empty((rows, TOP_K), i64),
-            local_counts=torch.zeros(rows, device=device, dtype=i32),
+            local_pairs=empty((chunks, rows, TOP_K) if parallel_chunks else (rows, TOP_K), i64),
+            local_counts=torch.zeros((chunks, rows) if parallel_chunks else (rows,), device=device, dtype=i32),
             accumulator_pairs=empty((rows, TOP_K), i64),
             accumulator_counts=torch.zeros(rows, device=device, dtype=i32),
             repair_error_flags=torch.zeros(rows, device=device, dtype=u8),
@@ -322,26 +322,35 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
             ptr(ws.repair_pairs), ws.rows, ws.keys, ws.block_begin, ws.block_stride, ws.num_blocks,
             ptr(tile_table), physical_keys, ptr(ws.status), stream,
         ))
+        chunks = int(ws.repair_pairs.shape[0])
+        check(library.itk_chunk_local_topk_all(
+            ptr(ws.repair_pairs), ptr(ws.chunk_starts), ptr(ws.chunk_ends), ptr(ws.failure_flags),
+            ptr(ws.local_pairs), ptr(ws.local_counts), ptr(ws.repair_error_flags), ws.rows, chunks, stream,
+        ))
+        check(library.itk_merge_local_lists(
+            ptr(ws.local_pairs), ptr(ws.local_counts), chunks, ptr(ws.accumulator_pairs),
+            ptr(ws.accumulator_counts), ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, stream,
+        ))
     first = True
     for chunk_index, chunk_lo in enumerate(range(0, ws.keys, _lib.REPAIR_CHUNK)):
         chunk_hi = min(ws.keys, chunk_lo + _lib.REPAIR_CHUNK)
-        if chunk_hi <= key_lo or chunk_lo >= key_hi:
+        if all_chunks or chunk_hi <= key_lo or chunk_lo >= key_hi:
             continue
-        chunk_pairs = ws.repair_pairs[chunk_index] if all_chunks else (
-            ws.repair_pairs[0] if ws.repair_pairs.dim() == 3 else ws.repair_pairs)
-        if not all_chunks:
-            check(library.itk_repair_produce_paged(
-                ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
-                ptr(chunk_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
-                ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
-            ))
+        chunk_pairs = ws.repair_pairs[0] if ws.repair_pairs.dim() == 3 else ws.repair_pairs
+        local_pairs = ws.local_pairs[0] if ws.local_pairs.dim() == 3 else ws.local_pairs
+        local_counts = ws.local_counts[0] if ws.local_counts.dim() == 2 else ws.local_counts
+        check(library.itk_repair_produce_paged(
+            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
+            ptr(chunk_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
+            ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
+        ))
         check(library.itk_chunk_local_topk(
             ptr(chunk_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
-            ptr(ws.failure_flags), ptr(ws.local_pairs), ptr(ws.local_counts), ptr(ws.repair_error_flags),
+            ptr(ws.failure_flags), ptr(local_pairs), ptr(local_counts), ptr(ws.repair_error_flags),
             ws.rows, 1 if first else 0, stream,
         ))
         check(library.itk_merge_topk_pairs(
-            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.local_pairs), ptr(ws.local_counts),
+            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(local_pairs), ptr(local_counts),
             ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, 1 if first else 0, stream,
         ))
         first = False

@@ -200,6 +200,18 @@ int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales
                            int num_blocks, const int32_t* tile_table, int physical_keys, int* status,
                            itk_stream_t stream);
 
+/* The chunk-local Top-2048 of every (chunk, flagged row) in one launch, and the merge of a row's chunk
+ * lists in ceil((chunks-1)/7) launches of up to eight lists: the companions of itk_repair_produce_all.
+ * repair_pairs [chunks,Q,16384], chunk_starts / chunk_ends [chunks,Q] (itk_update_chunk_ranges),
+ * local_pairs [chunks,Q,2048], local_counts [chunks,Q]; repair_error_flags [Q] is cleared first.
+ * Same selection and error codes as itk_chunk_local_topk / itk_merge_topk_pairs. */
+int itk_chunk_local_topk_all(const uint64_t* repair_pairs, const int32_t* chunk_starts, const int32_t* chunk_ends,
+                             const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
+                             uint8_t* repair_error_flags, int rows, int chunks, itk_stream_t stream);
+int itk_merge_local_lists(const uint64_t* local_pairs, const int32_t* local_counts, int chunks,
+                          uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint8_t* failure_flags,
+                          uint8_t* repair_error_flags, int rows, itk_stream_t stream);
+
 /* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1,
  * thresholds_per_row), which also decides per row whether the result is complete:
  * failure_flags[row] = 1 when any shard of the row reported an overflow

@@ -140,9 +140,9 @@ def test_forced_spill_and_forced_repair(device, threshold):
     score_threshold_check(indices, logits.cpu(), case)
 
 
-@pytest.mark.parametrize("rows,keys", [(10, 40000), (6, 70001)])
+@pytest.mark.parametrize("rows,keys", [(10, 40000), (6, 70001), (4, 150000)])   # 3, 5 and 10 chunks (two merge launches)
 def test_forced_repair_over_several_chunks_in_one_producer_launch(device, rows, keys, monkeypatch):
-    """+inf thresholds starve every row; the repair rescans 3 / 5 chunks per row.  The workspace that holds
+    """+inf thresholds starve every row; the repair rescans every chunk of every row.  The workspace that holds
     all chunks (one producer launch) and the one-chunk workspace (a launch per chunk) must agree."""
 
     host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=keys)
