@@ -56,7 +56,8 @@ class FusedArgs(ctypes.Structure):
         ("k_start", c_void_p), ("k_end", c_void_p), ("thresholds", c_void_p),
         ("out_ids", c_void_p), ("out_pairs", c_void_p), ("out_counts", c_void_p),
         ("failure_flags", c_void_p), ("spill", c_void_p), ("diag_logits", c_void_p),
-        ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p), ("debug_skip", c_int),
+        ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p),
+        ("wait_limit_ns", ctypes.c_ulonglong), ("withhold_loads", c_int),
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
         ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
         ("force_compute", c_int), ("max_ctas", c_int), ("thresholds_per_row", c_int),

@@ -304,6 +304,7 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
     params.sample_rank = sample_rank;
     params.target_candidates = target_candidates;
     params.top_k_min_valid = kTopK;
+    params.wait_limit_ns = kWaitLimitNs;
     return launch_fused<kModeSample>(params, diag_logits != nullptr || trace != nullptr,
                                      fused_grid(device, params.num_blocks, 0), stream);
 }
@@ -352,7 +353,8 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.diag_logits = a.diag_logits;
     params.diag_stride = a.diag_stride;
     params.trace = a.trace;
-    params.debug_skip = a.debug_skip;
+    params.wait_limit_ns = a.wait_limit_ns != 0 ? a.wait_limit_ns : kWaitLimitNs;
+    params.withhold_q_loads = a.withhold_loads;
     params.status = a.status;
     params.rows = a.rows;
     params.keys = a.keys;
@@ -435,6 +437,7 @@ int itk_repair_produce_paged(const void* q, const void* kv, const float* kv_scal
     params.block_stride = block_stride;
     params.num_blocks = num_blocks;
     params.top_k_min_valid = kTopK;
+    params.wait_limit_ns = kWaitLimitNs;
     return launch_fused<kModeRepair>(params, false, fused_grid(device, num_blocks, 0), stream);
 }
 
@@ -480,6 +483,7 @@ int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales
     params.block_stride = block_stride;
     params.num_blocks = num_blocks;
     params.top_k_min_valid = kTopK;
+    params.wait_limit_ns = kWaitLimitNs;
     return launch_fused<kModeRepair>(params, false, fused_grid(device, static_cast<long long>(num_blocks) * chunks, 0),
                                      stream);
 }

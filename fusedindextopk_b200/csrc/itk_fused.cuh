@@ -24,10 +24,9 @@
 //   kModeRepair  for rows flagged as failed, write every (score, key) of one
 //                16 K-key chunk to global memory for the exact repair reducers.
 //
-// Warp roles (640 threads): warp 0 TMA producer, warp 1 UMMA issuer and TMEM
-// owner, warps 2-3 idle, warps 4-19 epilogue and selection.  All hand-offs are
-// mbarriers with bounded waits; a wait that expires sets bit 0 of *status and
-// the CTA drains.
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 UMMA issuer and TMEM
+// owner, warps 2-17 epilogue and selection.  All hand-offs are mbarriers with
+// bounded waits; a wait that expires sets bit 0 of *status and the CTA drains.
 //
 // Counterparts in the reference (sm_90a, WGMMA): the persistent kernel
 // kernel/csrc/include/fused_index_topk/long_fused_topk.cuh:64-672 and its
@@ -38,28 +37,13 @@
 
 #include "itk_ptx.cuh"
 
-// Build-time experiment switch for timing studies (0 in every shipped build):
-//   1 = epilogue only drains TMEM and hands the buffer back, 2 = drain + head reduction, no filtering,
-//   6 = everything but the per-row Top-K selection, 7 = additionally no filter / compaction.
-#ifndef ITK_EXPERIMENT
-#define ITK_EXPERIMENT 0
-#endif
-
-// Heartbeat builds (-DITK_HEARTBEAT, diagnostic kernels only): lane 0 of every warp records the last
-// point it reached in trace[32 + warp], so that a host thread can read a stuck kernel's state from
-// mapped host memory.
-#ifdef ITK_HEARTBEAT
-#define ITK_BEAT(code)                                                                                        \
-    do {                                                                                                      \
-        if (DIAG && p.trace != nullptr && lane == 0)                                                          \
-            *reinterpret_cast<volatile long long*>(p.trace + static_cast<long long>(blockIdx.x) * kTraceFields + \
-                                                   32 + warp) = (code);                                        \
-    } while (0)
-#else
-#define ITK_BEAT(code) do { } while (0)
-#endif
-
+#include <cstddef>
 #include <type_traits>
+
+// Development switch (timing studies): which unit computes the ReLUs of the epilogue.
+#ifndef ITK_DEV_RELU
+#define ITK_DEV_RELU 2
+#endif
 
 namespace itk {
 
@@ -74,22 +58,22 @@ constexpr int kTmemColumns = kAccBuffers * kUmmaN;  // 512 = all of TMEM
 constexpr int kTopK = 2048;
 
 constexpr int kSegments = 4;                   // one per TMEM lane quarter: segment = (key >> 5) & 3
-constexpr int kSegCap = 1280;                  // shared-memory candidates per (row, segment)
-constexpr int kRowCap = kSegments * kSegCap;   // 5120
+constexpr int kSegCap = 1248;                  // shared-memory candidates per (row, segment)
+constexpr int kRowCap = kSegments * kSegCap;   // 4992
 constexpr int kSpillSegCap = 1408;             // global spill entries per (row, segment)
 constexpr int kSpillRow = kSegments * kSpillSegCap;  // 5632 u64 per row
 constexpr int kRepairChunk = 16384;
 
-// Warp 0: TMA producer; warp 1: UMMA issuer; warps 2-3: idle (they complete the first warpgroup);
-// warps 4-19: epilogue and per-row selection.  65536 / 640 rounded down to the allocation unit of 8
-// gives every thread 96 registers.
-constexpr int kThreads = 640;
-constexpr int kEpilogueWarp0 = 4;
+// Warp 0: TMA producer; warp 1: UMMA issuer; warps 2-17: epilogue and per-row selection (a warp may
+// only read the TMEM lane quarter warp % 4, so sixteen consecutive warps cover every quarter four
+// times: once per query row of the unit).  65536 / 576 rounded down to the allocation unit of 8
+// gives every thread 112 registers, of which the five warps of a scheduler can use 96.
+constexpr int kThreads = 576;
+constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueThreads = 512;
 constexpr int kEpilogueWarps = kEpilogueThreads / 32;
 constexpr int kScoreBins = 256;
 constexpr int kBinListCap = 64;     // scores of the histogram bin that holds the cutoff; more: radix fallback
-constexpr int kRankDirect = 48;    // lists up to this size are ranked without a second histogram level
 
 constexpr uint32_t kQBytes = kUmmaN * kHeadDim;       // 32768
 constexpr uint32_t kKvBytes = kTileKeys * kHeadDim;   // 16384
@@ -99,13 +83,10 @@ constexpr int kModeSample = 1;
 constexpr int kModeRepair = 2;
 
 constexpr int kStatusWaitExpired = 1;
+constexpr int kStatusBadSharedBase = 2;   // the dynamic shared memory does not start on a 1 KB boundary
 
 // Per-CTA phase trace of diagnostic builds (clock64 cycles unless noted).
-#ifdef ITK_HEARTBEAT
-constexpr int kTraceFields = 64;
-#else
 constexpr int kTraceFields = 32;
-#endif
 constexpr int kTraceMmaTotal = 0, kTraceMmaWaitAcc = 1, kTraceMmaWaitKv = 2, kTraceMmaWaitQ = 3, kTraceMmaTiles = 4;
 constexpr int kTraceTmaTotal = 8, kTraceTmaWaitKv = 9, kTraceTmaWaitQ = 10;
 constexpr int kTraceEpiTotal = 12, kTraceEpiWaitAcc = 13, kTraceEpiSelect = 14, kTraceEpiWaitW = 15;  // +4 for query row 1
@@ -131,8 +112,10 @@ struct FusedParams {
     float* diag_logits;         // [rows, diag_stride] dense scores, diagnostic builds only
     long long diag_stride;
     long long* trace;           // [grid, kTraceFields] per-CTA cycle counters, diagnostic builds only
-    int debug_skip;             // diagnostic builds only: 1 no selection, 2 no compaction, 4 no head reduction
     int* status;                // device status word, bits are or-ed in
+    unsigned long long wait_limit_ns;  // wall-clock limit of every wait inside the kernel
+    int withhold_q_loads;       // diagnostic builds only: the producer issues no load at all, so that the
+                                // first wait for the query tile runs into wait_limit_ns (tests of the expiry path)
     int rows;                   // Q
     int keys;                   // N (or S in kModeSample)
     int key_lo;                 // first key of shard 0 (multiple of 128)
@@ -154,7 +137,8 @@ struct FusedParams {
 // Per-row scratch of the selection.
 struct RowSelect {
     int hist[256];                      // second-level histogram / digit histogram of the radix fallback
-    uint32_t bin_scores[kBinListCap];   // the scores of the histogram bin that holds the cutoff
+    uint32_t bin_scores[kBinListCap];   // the candidates of the histogram bin that holds the cutoff
+    int32_t bin_keys[kBinListCap];
     int position;     // next free output position of the row
     int bin_count;
     int tickets;
@@ -165,13 +149,15 @@ struct RowSelect {
 };
 
 struct __align__(16) FusedShared {
+    // Histogram of a row's candidates over the binary exponent of their distance to the row
+    // threshold (first pass of the selection).
+    uint32_t row_hist[kBlockQ][kScoreBins];
     float weights[2][kBlockQ * kHeads];
     uint32_t cand_scores[kBlockQ][kRowCap];
     uint16_t cand_ids[kBlockQ][kRowCap];
-    int counts[kBlockQ][kSegments];
-    // Score histogram of every row's candidates, filled by the epilogue as it finds them:
-    // kScoreBins bins of the distance to the row threshold, two 16-bit counters per word.
-    uint32_t row_hist[kBlockQ][kScoreBins / 2];
+    int counts[kBlockQ][kSegments];         // candidates of every (row, segment) in shared memory
+    int spill_counts[kBlockQ][kSegments];   // candidates that went (or would have gone) to the segment's spill
+    uint32_t scale_part[kBlockQ][kSegments];   // sampled median distance to the threshold, per segment
     RowSelect select[kBlockQ];
     uint32_t tmem_base;
     int abort;
@@ -186,21 +172,27 @@ struct __align__(16) FusedShared {
 };
 
 constexpr size_t kSmemTileBytes = kQBytes + kKvStages * kKvBytes;
-constexpr size_t kFusedSmemBytes = 1024 + kSmemTileBytes + sizeof(FusedShared);
+constexpr size_t kFusedSmemBytes = kSmemTileBytes + sizeof(FusedShared);
+static_assert(kSmemTileBytes % 1024 == 0, "FusedShared must start on a 1 KB boundary");
 static_assert(kFusedSmemBytes <= 232448, "fused kernel exceeds the 227 KB shared-memory limit");
 static_assert(kSegCap % 32 == 0 && kSpillSegCap % 32 == 0, "segment capacities are warp multiples");
 
+// What a bounded wait needs besides the barrier: the CTA's abort flag and the time limit.
+struct WaitCtl {
+    volatile int* abort_flag;
+    uint64_t limit_ns;
+};
+
 // mbar_wait that adds the cycles it took to `cycles` in diagnostic builds.
 template <bool DIAG, uint32_t PARK_NS = kWaitParkNs>
-__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                           long long& cycles) {
+__device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, long long& cycles) {
     if (DIAG) {
         const long long begin = clock64();
-        const bool ok = mbar_wait<PARK_NS>(bar, parity, abort_flag);
+        const bool ok = mbar_wait<PARK_NS>(bar, parity, ctl.abort_flag, ctl.limit_ns);
         cycles += clock64() - begin;
         return ok;
     }
-    return mbar_wait<PARK_NS>(bar, parity, abort_flag);
+    return mbar_wait<PARK_NS>(bar, parity, ctl.abort_flag, ctl.limit_ns);
 }
 
 // ------------------------------------------------------------------ work units
@@ -268,8 +260,6 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
     return true;
 }
 
-// ------------------------------------------------------------------ selection helpers
-
 // ------------------------------------------------------------------ per-row selection
 
 // The four epilogue warps that score one query row (one per TMEM lane quarter) also select its
@@ -285,7 +275,7 @@ constexpr int kRowThreads = 128;
 struct RowBarrier {
     uint64_t* bar;
     uint32_t phase;
-    volatile int* abort_flag;
+    WaitCtl ctl;
     long long* lap;        // diagnostic builds: cycle counters of the selection steps (else null)
     long long lap_start;
 };
@@ -302,7 +292,7 @@ __device__ __forceinline__ void lap(RowBarrier& rb, int index) {
 __device__ __forceinline__ void row_sync(RowBarrier& rb) {
     __syncwarp();
     if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);   // one arrival per warp
-    if (!mbar_wait<kHotWait>(rb.bar, rb.phase & 1u, rb.abort_flag)) *rb.abort_flag = 1;
+    if (!mbar_wait<kHotWait>(rb.bar, rb.phase & 1u, rb.ctl.abort_flag, rb.ctl.limit_ns)) *rb.ctl.abort_flag = 1;
     ++rb.phase;
 }
 
@@ -311,17 +301,8 @@ __device__ __forceinline__ void row_sync(RowBarrier& rb) {
 __device__ __forceinline__ void row_sync_parked(RowBarrier& rb) {
     __syncwarp();
     if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);
-    if (!mbar_wait<500>(rb.bar, rb.phase & 1u, rb.abort_flag)) *rb.abort_flag = 1;
+    if (!mbar_wait<500>(rb.bar, rb.phase & 1u, rb.ctl.abort_flag, rb.ctl.limit_ns)) *rb.ctl.abort_flag = 1;
     ++rb.phase;
-}
-
-__device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
-    return static_cast<int>(((packed >> 5) << 7) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
-}
-
-__device__ __forceinline__ uint16_t encode_key(int key) {
-    const uint32_t k = static_cast<uint32_t>(key);
-    return static_cast<uint16_t>(((k >> 7) << 5) | (k & 31u));
 }
 
 // Warp-aggregated slot reservation: every lane calls, active lanes get distinct slots.
@@ -335,48 +316,59 @@ __device__ __forceinline__ int warp_reserve(int* counter, bool active, int lane)
     return active ? base + __popc(mask & ((1u << lane) - 1u)) : -1;
 }
 
+__device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
+    return static_cast<int>(((packed >> 5) << 7) | (static_cast<uint32_t>(segment) << 5) | (packed & 31u));
+}
+
 // The view a warp has of the candidates it owns during the selection: the segment it filled itself
-// (its TMEM lane quarter) and that segment's spill region in global memory.
+// (its TMEM lane quarter) and that segment's spill region in global memory.  Lane l owns the
+// entries j * 32 + l, j < lane_entries, of the segment: in the Top-K mode every thread of the
+// epilogue appends to its own list (no warp vote per tile), in the sample mode the segment is
+// filled densely and lane l simply has ceil((count - l) / 32) entries.
+//
+// Score words in shared memory are the float itself in the Top-K mode (RAW = true in the functions
+// below: the selection works on distances to the row threshold) and its ordered integer image in the
+// sample mode; the spill always holds (ordered score << 32 | key).
 struct RowView {
     const uint32_t* scores;        // [kSegCap] of the warp's segment
     const uint16_t* ids;           // [kSegCap]
     const uint64_t* spill;         // [kSpillSegCap] of the warp's segment
-    int in_smem;                   // candidates of the segment in shared memory
-    int in_spill;                  // ... and in the spill region
+    int lane_entries;              // entries of the calling lane in shared memory
+    int max_entries;               // largest lane_entries of the warp
+    int in_spill;                  // entries in the spill region
     int segment;
 };
 
-// Histogram bin of a candidate: the binary exponent of its distance to the row threshold (in value,
-// not in bit patterns: scores may straddle zero).  One bin per octave covers every float, so the
-// histogram needs no knowledge of the scale of the scores; the octave that holds the Top-K cutoff is
-// resolved by a second histogram over the next eight bits of the distance.
-__device__ __forceinline__ uint32_t distance_bits(uint32_t score_bits, float threshold) {
-    return __float_as_uint(ordered_to_float(score_bits) - threshold);   // >= +0 for every candidate
+// The float `steps` representable values above (below, for negative steps) x.
+__device__ __forceinline__ float neighbour_float(float x, int steps) {
+    return ordered_to_float(ordered_bits(x) + static_cast<uint32_t>(steps));
 }
 
-// visit(score) for every candidate of the calling lane (candidate i of the segment belongs to lane
-// i % 32).  The passes of a selection run once per unit, far apart in time, so their instructions
-// come from a cold instruction cache: they are kept as short rolled loops over shared memory rather
-// than unrolled passes over a register cache, which took several times longer.
-// Four candidates are loaded before the first is visited: a visit may contain a shared-memory atomic,
-// above which the compiler cannot move the next load, and a lone warp cannot hide a load per step.
-// Missing candidates are passed as the score 0, which is below every real score (finite scores map
-// to ordered bits above 0x00800000) and whose distance to a threshold is a NaN pattern that belongs
-// to no bin, so a visit needs no liveness test.
-template <typename Visit>
+template <bool RAW>
+__device__ __forceinline__ uint32_t word_to_ordered(uint32_t word) {
+    return RAW ? ordered_bits(__uint_as_float(word)) : word;
+}
+
+template <bool RAW>
+__device__ __forceinline__ float word_to_value(uint32_t word) {
+    return RAW ? __uint_as_float(word) : ordered_to_float(word);
+}
+
+// visit(ordered score) for every candidate of the calling lane: its list in shared memory, four
+// entries at a time so that the loads of a group are in flight together, then its share of the spill
+// region.  A visit may use shared-memory atomics but no warp-collective operation.
+template <bool RAW, typename Visit>
 __device__ __forceinline__ void for_scores(const RowView& v, int lane, Visit&& visit) {
-    const uint32_t* scores = v.scores;
-    const int in_smem = v.in_smem;
+    const uint32_t* scores = v.scores + lane;
+    const int mine = v.lane_entries;
 #pragma unroll 1
-    for (int i = lane; i < in_smem; i += 128) {
-        const uint32_t s0 = scores[i];
-        const uint32_t s1 = i + 32 < in_smem ? scores[i + 32] : 0u;
-        const uint32_t s2 = i + 64 < in_smem ? scores[i + 64] : 0u;
-        const uint32_t s3 = i + 96 < in_smem ? scores[i + 96] : 0u;
-        visit(s0);
-        visit(s1);
-        visit(s2);
-        visit(s3);
+    for (int j = 0; j < mine; j += 4) {
+        uint32_t s[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s[k] = j + k < mine ? scores[(j + k) * 32] : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (j + k < mine) visit(word_to_ordered<RAW>(s[k]));
     }
 #pragma unroll 1
     for (int e = lane; e < v.in_spill; e += 32) visit(static_cast<uint32_t>(v.spill[e] >> 32));
@@ -412,122 +404,235 @@ __device__ __forceinline__ bool find_rank(const int (&counts)[8], int lane, int 
     return found;
 }
 
-// Warp-wide result of find_rank: every lane gets the values of the lane that found the entry.
+// Warp-wide result of find_rank: every lane gets the values of the lane that found the entry
+// (entry -1 when no lane found it: the histogram holds fewer than `rank` candidates).
 __device__ __forceinline__ void share_rank(bool found, int& entry, int& above, int& inside) {
     const unsigned who = __ballot_sync(0xffffffffu, found);
-    const int source = __ffs(who) - 1;
-    entry = __shfl_sync(0xffffffffu, entry, source);
+    const int source = who != 0u ? __ffs(who) - 1 : 0;
+    entry = __shfl_sync(0xffffffffu, who != 0u ? entry : -1, source);
     above = __shfl_sync(0xffffffffu, above, source);
     inside = __shfl_sync(0xffffffffu, inside, source);
 }
 
-// Selection from the histogram that the epilogue filled while it found the candidates.  The octave
-// (of the distance to the threshold) that holds the rank-th largest score is read off that histogram;
-// the candidates of that octave are histogrammed again by the next eight bits of the distance; the
-// handful of scores in the sub-bin that holds the cutoff are gathered and ranked against one another.
-// The small steps (reading a histogram, ranking the list) are done by every warp redundantly, which
-// costs a few dozen instructions and saves a barrier and a broadcast each.  Returns false (outputs
-// untouched) when the last list holds more than kBinListCap scores (many equal or nearly equal
-// scores); the caller then falls back to the radix selection.  Called by the 128 threads of a row
-// after the barrier that publishes the row's counts; rs.hist and rs.bin_count are zero on entry;
-// needs rank_in <= number of candidates.
-__device__ __forceinline__ bool bin_select(RowSelect& rs, const RowView& v, const uint32_t* row_hist, float threshold,
-                                           RowBarrier& rb, int tid, int rank_in, uint32_t& cutoff,
-                                           int& equal_needed) {
+// One pass of a warp over its candidates that writes the selected ones.  classify(word) (the score
+// word as stored in shared memory; spill entries are passed converted to the same form) returns 2
+// for a candidate that is selected, 1 for one that is handed to on_listed(ordered score, key), 0
+// otherwise.  Selected candidates get consecutive output positions from rs.position: four entries
+// per lane are classified at a time, one shared-memory atomic per such group reserves the positions,
+// the position inside the group comes from warp votes, so the stores of a warp instruction fall into
+// a few sectors (every lane keeping its own run of positions made each store touch 32 sectors, which
+// took several times longer).
+template <bool RAW, typename Classify, typename Listed>
+__device__ __forceinline__ void emit_pass(RowSelect& rs, const RowView& v, int lane, int32_t* out_ids,
+                                          uint64_t* out_pairs, Classify&& classify, Listed&& on_listed) {
+    const unsigned below = (1u << lane) - 1u;
+    const auto write = [&](int at, uint32_t word, int key) {
+        at = min(at, kTopK - 1);
+        if (out_ids != nullptr) out_ids[at] = key;
+        if (out_pairs != nullptr)
+            out_pairs[at] = (static_cast<uint64_t>(word_to_ordered<RAW>(word)) << 32) | static_cast<uint32_t>(key);
+    };
+    const uint32_t* scores = v.scores + lane;
+    const uint16_t* ids = v.ids + lane;
+    const int mine = v.lane_entries, segment = v.segment;
+#pragma unroll 1
+    for (int j = 0; j < v.max_entries; j += 4) {
+        uint32_t word[4], id[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const bool live = j + k < mine;
+            word[k] = live ? scores[(j + k) * 32] : 0u;
+            id[k] = live ? ids[(j + k) * 32] : 0u;
+        }
+        int kind[4];
+        unsigned ballot[4];
+        int group = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            kind[k] = j + k < mine ? classify(word[k]) : 0;
+            ballot[k] = __ballot_sync(0xffffffffu, kind[k] == 2);
+            group += __popc(ballot[k]);
+        }
+        int position = 0;
+        if (lane == 0 && group > 0) position = atomicAdd(&rs.position, group);
+        position = __shfl_sync(0xffffffffu, position, 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int key = decode_key(id[k], segment);
+            if (kind[k] == 2) write(position + __popc(ballot[k] & below), word[k], key);
+            else if (kind[k] == 1) on_listed(word_to_ordered<RAW>(word[k]), key);
+            position += __popc(ballot[k]);
+        }
+    }
+#pragma unroll 1
+    for (int base = 0; base < v.in_spill; base += 32) {
+        const int e = base + lane;
+        const bool live = e < v.in_spill;
+        const uint64_t pair = live ? v.spill[e] : 0ull;
+        const uint32_t ordered = static_cast<uint32_t>(pair >> 32);
+        const uint32_t word = RAW ? __float_as_uint(ordered_to_float(ordered)) : ordered;
+        const int key = static_cast<int>(static_cast<uint32_t>(pair));
+        const int kind = live ? classify(word) : 0;
+        const unsigned ballot = __ballot_sync(0xffffffffu, kind == 2);
+        int position = 0;
+        if (lane == 0 && ballot != 0u) position = atomicAdd(&rs.position, __popc(ballot));
+        position = __shfl_sync(0xffffffffu, position, 0);
+        if (kind == 2) write(position + __popc(ballot & below), word, key);
+        else if (kind == 1) on_listed(ordered, key);
+    }
+}
+
+// Median (upper median) of the calling warp's valid values, one per lane, as a warp-uniform result;
+// 0 when fewer than four lanes hold a valid value.  Values are compared as unsigned integers.
+__device__ __forceinline__ uint32_t warp_median(uint32_t value, bool valid, int lane) {
+    const unsigned who = __ballot_sync(0xffffffffu, valid);
+    const int live = __popc(who);
+    int below = 0;   // valid values that sort before this lane's (ties: the lower lane first)
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+        const uint32_t other = __shfl_sync(0xffffffffu, value, k);
+        const bool counts = ((who >> k) & 1u) != 0u && (other < value || (other == value && k < lane));
+        below += counts ? 1 : 0;
+    }
+    const unsigned median_lane = __ballot_sync(0xffffffffu, valid && below == live / 2);
+    const uint32_t median = __shfl_sync(0xffffffffu, value, median_lane != 0u ? __ffs(median_lane) - 1 : 0);
+    return live >= 4 ? median : 0u;
+}
+
+// Exact Top-2048 of a row whose candidates lie above a finite threshold (Top-K mode: the score words
+// are floats).  `width` is a robust scale of the candidates' distances to the threshold (four times
+// the median of a sample of them): 256 equal bins over [0, width) resolve the lower, densely
+// populated part of the distances, where the 2048th largest score lies, to a couple of dozen
+// candidates per bin; the few large distances beyond (all of them selected anyway) share the last bin.
+//   1. histogram of the bins (one pass of every warp over its own candidates); the bin that holds
+//      the 2048th largest score is read off it, by every warp redundantly;
+//   2. the bin's two edges are turned into score values (exactly: the edge is moved until the bin
+//      arithmetic agrees), so that the second pass classifies a candidate with two comparisons: above
+//      the bin it goes to the output, inside the bin onto a list;
+//   3. one warp ranks the list and writes its largest entries to the remaining positions (ties: the
+//      first ones of the list).
+// Returns false, with nothing written, when the list would hold more than kBinListCap scores (many
+// equal or nearly equal scores, or a scale that does not fit the row); the caller then falls back to
+// the radix selection.  Called by the 128 threads of a row after the barrier that publishes the
+// row's counts; row_hist, rs.bin_count and rs.position are zero on entry.
+__device__ __forceinline__ bool binned_select(RowSelect& rs, const RowView& v, uint32_t* row_hist, float threshold,
+                                              float width, RowBarrier& rb, int tid, int32_t* out_ids,
+                                              uint64_t* out_pairs) {
     const int lane = tid & 31;
-    int octave_entry, above, in_list;
+    const float bins_per_unit = static_cast<float>(kScoreBins) / width;
+    const auto bin_of = [&](float score) -> int {
+        return __float2int_rz(fminf((score - threshold) * bins_per_unit, static_cast<float>(kScoreBins - 1)));
+    };
+    {
+        const uint32_t* scores = v.scores + lane;
+        const int mine = v.lane_entries;
+#pragma unroll 1
+        for (int j = 0; j < mine; j += 4) {
+            float s[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s[k] = j + k < mine ? __uint_as_float(scores[(j + k) * 32]) : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (j + k < mine) atomicAdd(&row_hist[bin_of(s[k])], 1u);
+        }
+#pragma unroll 1
+        for (int e = lane; e < v.in_spill; e += 32)
+            atomicAdd(&row_hist[bin_of(ordered_to_float(static_cast<uint32_t>(v.spill[e] >> 32)))], 1u);
+    }
+    lap(rb, 1);
+    row_sync(rb);
+    int cutoff_bin, above, in_list;
     {
         int counts[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t word = row_hist[lane * 4 + j];
-            counts[2 * j] = static_cast<int>(word & 0xffffu);
-            counts[2 * j + 1] = static_cast<int>(word >> 16);
-        }
-        const bool found = find_rank(counts, lane, rank_in, octave_entry, above, in_list);
-        share_rank(found, octave_entry, above, in_list);
+        for (int j = 0; j < 8; ++j) counts[j] = static_cast<int>(row_hist[lane * 8 + j]);
+        const bool found = find_rank(counts, lane, kTopK, cutoff_bin, above, in_list);
+        share_rank(found, cutoff_bin, above, in_list);
     }
-    lap(rb, 1);
-    const uint32_t octave = static_cast<uint32_t>(octave_entry);
-    int sub_bin = -1;            // -1: the whole octave is the list
-    // octave 255 (infinite distances: the threshold is -inf) holds no usable order; the radix
-    // selection sorts such rows out
-    if (octave >= 255u) return false;
-    if (in_list > kRankDirect) {
-        // second level: the next eight bits of the distance inside the octave
-        for_scores(v, lane, [&](uint32_t score) {
-            const uint32_t d = distance_bits(score, threshold);
-            if (d >> 23 == octave) atomicAdd(&rs.hist[(d >> 15) & 255u], 1);
-        });
-        lap(rb, 8);
-        row_sync(rb);
-        lap(rb, 9);
-        int counts[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) counts[j] = rs.hist[lane * 8 + j];
-        int above2 = 0;
-        const bool found = find_rank(counts, lane, rank_in - above, sub_bin, above2, in_list);
-        share_rank(found, sub_bin, above2, in_list);
-        above += above2;
-        lap(rb, 2);
-    }
-    if (in_list > kBinListCap) return false;
-    const int need = rank_in - above;       // how many of the list's scores belong to the top rank_in
-    // gather the list: the candidates whose distance starts with (octave) or (octave, sub-bin)
-    const int list_shift = sub_bin < 0 ? 23 : 15;
-    const uint32_t list_prefix = sub_bin < 0 ? octave : (octave << 8 | static_cast<uint32_t>(sub_bin));
-    for_scores(v, lane, [&](uint32_t score) {
-        if (distance_bits(score, threshold) >> list_shift == list_prefix) {
-            const int at = atomicAdd(&rs.bin_count, 1);
-            if (at < kBinListCap) rs.bin_scores[at] = score;
-        }
-    });
-    lap(rb, 10);
-    row_sync(rb);
-    lap(rb, 3);
-    // The need-th largest of the list: the score with fewer than `need` scores above it and at least
-    // `need` scores above or equal to it.  Every warp ranks the whole list (two entries per lane).
-    uint32_t found_cutoff = 0u;
-    int found_equal = 0;
-    bool found = false;
+    if (cutoff_bin < 0 || in_list > kBinListCap) return false;
+    // Smallest score of bin `b`: start from the arithmetic edge and move by single floats until
+    // bin_of puts the value into bin >= b and its predecessor below; bin_of is monotone in the score.
+    const auto lower_edge = [&](int b) -> float {
+        if (b <= 0) return threshold;   // every candidate is at or above the threshold
+        float edge = threshold + static_cast<float>(b) / bins_per_unit;
 #pragma unroll 1
-    for (int k = 0; k < kBinListCap / 32; ++k) {
-        const int i = lane + 32 * k;
-        const uint32_t mine = i < in_list ? rs.bin_scores[i] : 0u;
-        int greater = 0, equal = 0;
-#pragma unroll 4
-        for (int j = 0; j < in_list; ++j) {
-            const uint32_t other = rs.bin_scores[j];
-            greater += other > mine ? 1 : 0;
-            equal += other == mine ? 1 : 0;
+        for (int step = 0; step < 64 && bin_of(edge) < b; ++step) edge = neighbour_float(edge, 1);
+#pragma unroll 1
+        for (int step = 0; step < 64; ++step) {
+            const float lower = neighbour_float(edge, -1);
+            if (bin_of(lower) < b) break;
+            edge = lower;
         }
-        if (i < in_list && greater < need && need <= greater + equal) {
-            found = true;
-            found_cutoff = mine;
-            found_equal = need - greater;
+        return edge;
+    };
+    const float list_from = lower_edge(cutoff_bin);
+    const float take_from = cutoff_bin >= kScoreBins - 1 ? __int_as_float(0x7f800000) : lower_edge(cutoff_bin + 1);
+    // the edges must agree with the histogram, else the counts would not add up: check them
+    if (bin_of(list_from) != cutoff_bin || (cutoff_bin < kScoreBins - 1 && bin_of(take_from) != cutoff_bin + 1)) return false;
+    if (cutoff_bin > 0 && bin_of(neighbour_float(list_from, -1)) >= cutoff_bin) return false;
+    if (cutoff_bin < kScoreBins - 1 && bin_of(neighbour_float(take_from, -1)) > cutoff_bin) return false;
+    lap(rb, 2);
+    emit_pass<true>(rs, v, lane, out_ids, out_pairs,
+                    [&](uint32_t word) {
+                        const float score = __uint_as_float(word);
+                        return score >= take_from ? 2 : (score >= list_from ? 1 : 0);
+                    },
+                    [&](uint32_t ordered, int key) {
+                        const int at = atomicAdd(&rs.bin_count, 1);
+                        if (at < kBinListCap) {
+                            rs.bin_scores[at] = ordered;
+                            rs.bin_keys[at] = key;
+                        }
+                    });
+    lap(rb, 3);
+    row_sync(rb);
+    // The list's `need` largest scores complete the row: an entry is taken when fewer than `need`
+    // entries are above it, counting equal scores that come earlier in the list as above.
+    if (tid < 32) {
+        const int need = kTopK - above;
+        in_list = min(in_list, kBinListCap);
+#pragma unroll 1
+        for (int k = 0; k < kBinListCap / 32; ++k) {
+            const int i = lane + 32 * k;
+            const uint32_t mine = i < in_list ? rs.bin_scores[i] : 0u;
+            int before = 0;
+#pragma unroll 4
+            for (int j = 0; j < in_list; ++j) {
+                const uint32_t other = rs.bin_scores[j];
+                before += (other > mine || (other == mine && j < i)) ? 1 : 0;
+            }
+            if (i < in_list && before < need) {
+                const int key = rs.bin_keys[i];
+                if (out_ids != nullptr) out_ids[above + before] = key;
+                if (out_pairs != nullptr) out_pairs[above + before] = (static_cast<uint64_t>(mine) << 32) | static_cast<uint32_t>(key);
+            }
         }
     }
-    const unsigned who = __ballot_sync(0xffffffffu, found);
-    const int source = __ffs(who) - 1;
-    cutoff = __shfl_sync(0xffffffffu, found_cutoff, source);
-    equal_needed = __shfl_sync(0xffffffffu, found_equal, source);
     lap(rb, 4);
     return true;
 }
 
 // Radix selection over the ordered score bits of one row, up to 8 bits per round: the fallback for
-// rows whose cutoff bin is too full (many equal or nearly equal scores).  On return `cutoff` is the
-// rank-th largest score and `equal_needed` the number of candidates equal to it that belong to the
-// top `rank_in`.  The leading bits that all candidates share are found first and skipped.
+// rows whose cutoff bin is too full (many equal or nearly equal scores), and the selection of the
+// sample mode beyond 512 samples.  On return `cutoff` is the rank-th largest score and
+// `equal_needed` the number of candidates equal to it that belong to the top `rank_in`.  The leading
+// bits that all candidates share are found first and skipped.
+template <bool RAW>
 __device__ __forceinline__ void radix_select(RowSelect& rs, const RowView& v, RowBarrier& rb, int tid, int rank_in,
                                              uint32_t& cutoff, int& equal_needed) {
     const int lane = tid & 31;
-    if (tid == 0) rs.differing = 0u;
-    if (lane == 0 && v.in_smem > 0) rs.reference = v.scores[0];   // any candidate of the row (the row has at least
-    row_sync(rb);                                                  // rank_in >= 1 candidates, so some segment has one)
+    if (tid == 0) {
+        rs.differing = 0u;
+        rs.reference = 0u;
+    }
+    row_sync(rb);
+    // any candidate of the row serves as the reference (the row has at least rank_in >= 1 candidates)
+    if (lane == 0 && v.lane_entries > 0) atomicMax(&rs.reference, word_to_ordered<RAW>(v.scores[0]));
+    if (lane == 0 && v.lane_entries == 0 && v.in_spill > 0) atomicMax(&rs.reference, static_cast<uint32_t>(v.spill[0] >> 32));
+    row_sync(rb);
     const uint32_t reference = rs.reference;
     uint32_t differing = 0u;
-    for_scores(v, lane, [&](uint32_t score) { differing |= score ^ reference; });
+    for_scores<RAW>(v, lane, [&](uint32_t score) { differing |= score ^ reference; });
     differing = __reduce_or_sync(0xffffffffu, differing);
     if (lane == 0 && differing != 0u) atomicOr(&rs.differing, differing);
     row_sync(rb);
@@ -544,7 +649,7 @@ __device__ __forceinline__ void radix_select(RowSelect& rs, const RowView& v, Ro
         const uint32_t digit_mask = (1u << width) - 1u;
         for (int bin = tid; bin < 256; bin += kRowThreads) rs.hist[bin] = 0;
         row_sync(rb);
-        for_scores(v, lane, [&](uint32_t score) {
+        for_scores<RAW>(v, lane, [&](uint32_t score) {
             if ((score & mask) == prefix) atomicAdd(&rs.hist[(score >> shift) & digit_mask], 1);
         });
         row_sync(rb);
@@ -584,104 +689,34 @@ __device__ __forceinline__ void radix_select(RowSelect& rs, const RowView& v, Ro
     equal_needed = rank;
 }
 
-// Writes the selected candidates of one row: everything above `cutoff`, then `equal_needed` of the
-// candidates equal to it (any of them); cutoff 0 takes every candidate.  Every warp counts its
-// candidates above the cutoff, reserves that many output positions with one atomic add and fills
-// them in ballot order, 32 candidates at a time, so that the stores of a warp instruction fall into
-// a few sectors.  The few candidates equal to the cutoff draw tickets for the positions behind.
-// rs.position and rs.tickets must be 0 on entry (a row barrier before the call publishes that).
+// Writes the selected candidates of one row when the cutoff (an ordered score) is known: everything
+// above `cutoff`, then `equal_needed` of the candidates equal to it (any of them); cutoff 0 takes
+// every candidate.  greater_total = number of candidates above the cutoff (their positions come
+// first).  rs.position and rs.tickets must be 0 on entry (a row barrier before the call publishes that).
+template <bool RAW>
 __device__ __forceinline__ void emit_row(RowSelect& rs, const RowView& v, int lane, uint32_t cutoff, int equal_needed,
-                                         int greater_total, int32_t* out_ids, uint64_t* out_pairs,
-                                         RowBarrier* timer = nullptr) {
-    int greater = 0;
-    for_scores(v, lane, [&](uint32_t score) { greater += score > cutoff ? 1 : 0; });
-    greater = __reduce_add_sync(0xffffffffu, greater);
-    if (timer != nullptr) lap(*timer, 12);
-    int position = 0;
-    if (lane == 0 && greater > 0) position = atomicAdd(&rs.position, greater);
-    position = __shfl_sync(0xffffffffu, position, 0);
-    if (timer != nullptr) lap(*timer, 13);
-    const unsigned below = (1u << lane) - 1u;
-    const auto write = [&](int at, uint32_t score, int key) {
-        if (at >= kTopK) return;
-        if (out_ids != nullptr) out_ids[at] = key;
-        if (out_pairs != nullptr) out_pairs[at] = (static_cast<uint64_t>(score) << 32) | static_cast<uint32_t>(key);
-    };
-    // One candidate per lane (score 0: none); `key()` is only evaluated for the candidates that are written.
-    // No divergent branch on the common path: a lane that writes nothing aims past the end, and the
-    // tie tickets (about one per row) sit behind a warp-uniform test.
-    const auto place = [&](uint32_t score, auto&& key) {
-        const bool is_greater = score > cutoff;
-        const unsigned ballot = __ballot_sync(0xffffffffu, is_greater);
-        const bool tie = score == cutoff && cutoff != 0u;
-        int at = is_greater ? position + __popc(ballot & below) : kTopK;
-        if (__any_sync(0xffffffffu, tie)) {
-            if (tie) {
-                const int ticket = atomicAdd(&rs.tickets, 1);
-                if (ticket < equal_needed) at = greater_total + ticket;
-            }
-        }
-        write(at, score, key());
-        position += __popc(ballot);
-    };
-    {
-        // four candidates (score and id) are loaded before the first is placed, see for_scores
-        const uint32_t* scores = v.scores;
-        const uint16_t* ids = v.ids;
-        const int in_smem = v.in_smem, segment = v.segment;
-#pragma unroll 1
-        for (int base = 0; base < in_smem; base += 128) {
-            uint32_t score[4];
-            uint32_t id[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int i = base + 32 * k + lane;
-                const bool live = i < in_smem;
-                score[k] = live ? scores[i] : 0u;
-                id[k] = live ? ids[i] : 0u;
-            }
-            // The four ballots first, then the positions, then the stores: the votes of one group do not
-            // wait for each other's stores, and the tie test costs one vote per group (dead lanes carry
-            // score 0, which is neither greater than nor tied with a cutoff).
-            unsigned ballot[4];
-            bool tie = false;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                ballot[k] = __ballot_sync(0xffffffffu, score[k] > cutoff);
-                tie = tie || (score[k] == cutoff && cutoff != 0u);
-            }
-            int at[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                at[k] = score[k] > cutoff ? position + __popc(ballot[k] & below) : kTopK;
-                position += __popc(ballot[k]);
-            }
-            if (__any_sync(0xffffffffu, tie)) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (score[k] == cutoff && cutoff != 0u) {
-                        const int ticket = atomicAdd(&rs.tickets, 1);
-                        if (ticket < equal_needed) at[k] = greater_total + ticket;
-                    }
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) write(at[k], score[k], decode_key(id[k], segment));
-        }
-    }
-#pragma unroll 1
-    for (int base = 0; base < v.in_spill; base += 32) {
-        const int e = base + lane;
-        const uint64_t pair = e < v.in_spill ? v.spill[e] : 0ull;
-        place(static_cast<uint32_t>(pair >> 32), [&]() { return static_cast<int>(static_cast<uint32_t>(pair)); });
-    }
+                                         int greater_total, int32_t* out_ids, uint64_t* out_pairs) {
+    emit_pass<RAW>(rs, v, lane, out_ids, out_pairs,
+                   [&](uint32_t word) {
+                       const uint32_t score = word_to_ordered<RAW>(word);
+                       return score > cutoff ? 2 : (score == cutoff && cutoff != 0u ? 1 : 0);
+                   },
+                   [&](uint32_t ordered, int key) {
+                       const int ticket = atomicAdd(&rs.tickets, 1);
+                       if (ticket < equal_needed) {
+                           const int at = min(greater_total + ticket, kTopK - 1);
+                           if (out_ids != nullptr) out_ids[at] = key;
+                           if (out_pairs != nullptr) out_pairs[at] = (static_cast<uint64_t>(ordered) << 32) | static_cast<uint32_t>(key);
+                       }
+                   });
 }
 
 // Exact Top-2048 of one row from its candidates.  Called by the 128 threads of row r after the
-// row's four segment counts are in shared memory and the row barrier has been passed; returns with
-// the row barrier passed again (the candidate buffers and the histogram may be reused).
+// row's four segment totals are in shared memory and the row barrier has been passed (lane_entries:
+// the calling lane's own number of entries in its segment); returns with the row barrier passed
+// again (the candidate buffers and the histograms may be reused).
 __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
-                                                bool has_tiles, RowBarrier& rb, int tid) {
+                                                bool has_tiles, RowBarrier& rb, int tid, int lane_entries) {
     const int row = u.row0 + r;
     const long long row_slot = static_cast<long long>(u.shard) * p.rows + row;
     const int start = max(__ldg(p.k_start + row), u.key_lo);
@@ -715,20 +750,41 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     RowSelect& rs = sh.select[r];
     const int lane = tid & 31;
     const int segment = tid >> 5;
-    int total = 0;
-    bool overflow = false;
-#pragma unroll
-    for (int s = 0; s < kSegments; ++s) {
-        total += sh.counts[r][s];
-        overflow = overflow || sh.counts[r][s] > kSegCap + kSpillSegCap;
-    }
+    const float threshold =
+        valid > kTopK ? __ldg(p.thresholds + (p.row_thresholds ? row : row_slot)) : __int_as_float(0xff800000);
     RowView view;
     view.segment = segment;
     view.scores = sh.cand_scores[r] + segment * kSegCap;
     view.ids = sh.cand_ids[r] + segment * kSegCap;
     view.spill = p.spill + row_slot * kSpillRow + segment * kSpillSegCap;
-    view.in_smem = min(sh.counts[r][segment], kSegCap);
-    view.in_spill = min(max(sh.counts[r][segment] - kSegCap, 0), kSpillSegCap);
+    view.lane_entries = lane_entries;
+    view.max_entries = __reduce_max_sync(0xffffffffu, lane_entries);
+    // Every warp publishes the number of candidates in its segment and the median distance to the
+    // threshold of a sample of them (the first entry of every lane); one barrier, after which all
+    // four warps of the row know the totals and agree on a scale for the selection's bins.
+    {
+        // sample: the last entry of every lane (the first ones are the lowest key positions, where
+        // attention sinks sit)
+        const uint32_t sample = lane_entries > 0
+            ? __float_as_uint(__uint_as_float(view.scores[(lane_entries - 1) * 32 + lane]) - threshold) : 0u;
+        const uint32_t median = warp_median(sample, lane_entries > 0 && sample < 0x7f800000u, lane);
+        const int in_segment = __reduce_add_sync(0xffffffffu, lane_entries);
+        if (lane == 0) {
+            sh.counts[r][segment] = in_segment;
+            sh.scale_part[r][segment] = median;
+        }
+    }
+    row_sync(rb);
+    int total = 0;
+    bool overflow = false;
+    uint32_t scale_bits = 0u;
+#pragma unroll
+    for (int s = 0; s < kSegments; ++s) {
+        total += sh.counts[r][s] + min(sh.spill_counts[r][s], kSpillSegCap);
+        overflow = overflow || sh.spill_counts[r][s] > kSpillSegCap;
+        scale_bits = max(scale_bits, sh.scale_part[r][s]);
+    }
+    view.in_spill = min(sh.spill_counts[r][segment], kSpillSegCap);
     const int wanted = min(valid, kTopK);
     uint32_t* row_hist = sh.row_hist[r];
     if (overflow || (total < wanted && !p.row_thresholds)) {
@@ -742,35 +798,40 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     } else {
         if (rb.lap != nullptr) rb.lap_start = clock64();
         if (total <= kTopK) {
-            // only reachable when valid <= 2048 (threshold forced to -inf): take everything
-            emit_row(rs, view, lane, 0u, 0, 0, out_ids, out_pairs);
+            // only reachable when valid <= 2048 or a shard came up short: take everything
+            emit_row<true>(rs, view, lane, 0u, 0, 0, out_ids, out_pairs);
             fill_empty(total);
         } else {
-            uint32_t cutoff;
-            int equal_needed;
-            const float threshold =
-                valid > kTopK ? __ldg(p.thresholds + (p.row_thresholds ? row : row_slot)) : __int_as_float(0xff800000);
-            if (!bin_select(rs, view, row_hist, threshold, rb, tid, kTopK, cutoff, equal_needed))
-                radix_select(rs, view, rb, tid, kTopK, cutoff, equal_needed);
-            emit_row(rs, view, lane, cutoff, equal_needed, kTopK - equal_needed, out_ids, out_pairs, &rb);
-            lap(rb, 11);
+            // bins of the selection: 256 over [0, 4 x the largest of the four sampled medians)
+            const float width = 4.0f * __uint_as_float(scale_bits);
+            const bool usable = scale_bits != 0u && width < 3.0e38f;
+            if (!usable || !binned_select(rs, view, row_hist, threshold, width, rb, tid, out_ids, out_pairs)) {
+                uint32_t cutoff;
+                int equal_needed;
+                radix_select<true>(rs, view, rb, tid, kTopK, cutoff, equal_needed);
+                emit_row<true>(rs, view, lane, cutoff, equal_needed, kTopK - equal_needed, out_ids, out_pairs);
+            }
+            lap(rb, 5);
         }
         if (tid == 0) {
             p.failure_flags[row_slot] = 0;
             if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
         }
     }
-    for (int i = tid; i < kScoreBins / 2; i += kRowThreads) row_hist[i] = 0u;   // for the next unit
-    row_sync(rb);
-    // the selection's scratch is clean again for the row's next selection, whose first barrier
+    row_sync(rb);   // every warp is done with the candidates, the histograms and the list
+    // leave the selection's scratch clean for the row's next selection, whose first barrier
     // (the one that publishes the counts) orders these stores before any use
-    for (int i = tid; i < 256; i += kRowThreads) rs.hist[i] = 0;
+    for (int i = tid; i < kScoreBins; i += kRowThreads) {
+        row_hist[i] = 0u;
+        rs.hist[i] = 0;
+    }
+    if (tid < kSegments) sh.spill_counts[r][tid] = 0;
     if (tid == 0) {
         rs.position = 0;
         rs.tickets = 0;
         rs.bin_count = 0;
     }
-    if (!(overflow || total < wanted) && total > kTopK) lap(rb, 6);
+    lap(rb, 6);
 }
 
 // The rank-th largest (1-based) of at most 32 * SLOTS ordered score words spread over the four
@@ -870,11 +931,13 @@ __device__ __forceinline__ bool sample_threshold_row(FusedShared& sh, const Fuse
             view.scores = sh.cand_scores[r] + segment * kSegCap;
             view.ids = sh.cand_ids[r] + segment * kSegCap;
             view.spill = nullptr;
-            view.in_smem = sh.counts[r][segment];
+            // the dense segment as per-lane lists: lane l owns the entries l, l + 32, ...
+            view.lane_entries = max(sh.counts[r][segment] - (tid & 31) + 31, 0) >> 5;
+            view.max_entries = (sh.counts[r][segment] + 31) >> 5;
             view.in_spill = 0;
             uint32_t cutoff;
             int equal_needed;
-            radix_select(sh.select[r], view, rb, tid, p.sample_rank, cutoff, equal_needed);
+            radix_select<false>(sh.select[r], view, rb, tid, p.sample_rank, cutoff, equal_needed);
             result = ordered_to_float(cutoff);
         }
     }
@@ -882,25 +945,118 @@ __device__ __forceinline__ bool sample_threshold_row(FusedShared& sh, const Fuse
     return solo;
 }
 
-// ------------------------------------------------------------------ the kernel
+// ------------------------------------------------------------------ epilogue arithmetic
 
-__device__ __forceinline__ uint64_t pack_pair(float lo, float hi) {
-    uint64_t packed;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(lo), "f"(hi));
-    return packed;
+// ReLU of two neighbouring accumulator columns and their packed multiply-add with the two head
+// weights.  A ReLU is either max(x, 0) on the integer/compare pipe (which issues it at half rate) or
+// fma.rn.sat(x, 2^-25, 0) on the FMA pipe: |x| <= 128 * 448^2 < 2^25, so the saturating multiply
+// by 2^-25 is exact for x > 0, clamps x <= 0 (and NaN) to +0 and never reaches the upper clamp; the
+// weights of such a column pair are pre-multiplied by 2^25 (exact for |w| < 2^103), so that every
+// product, and with it every partial sum, is bit-identical to the max form.  Splitting the ReLUs
+// over both pipes balances them.  The two accumulator registers are neighbours of an even/odd
+// register pair already (they come out of one tcgen05.ld), so packing them costs no move; both
+// ReLUs of a pair use the same form (mixed pairs made the assembler insert a register move each).
+template <bool SAT, bool FIRST>
+__device__ __forceinline__ void relu_fma(uint32_t& x0, uint32_t& x1, uint64_t wpair, uint64_t& acc) {
+    float& f0 = *reinterpret_cast<float*>(&x0);
+    float& f1 = *reinterpret_cast<float*>(&x1);
+#define ITK_RELU_MAX(r) "max.f32 " r ", " r ", 0f00000000;\n\t"
+#define ITK_RELU_SAT(r) "fma.rn.sat.f32 " r ", " r ", 0f33000000, 0f00000000;\n\t"
+#define ITK_RELU_BODY(OP)                                                                                \
+    if (FIRST) {                                                                                         \
+        asm("{\n\t.reg .b64 t;\n\t" OP("%0") OP("%1") "mov.b64 t, {%0, %1};\n\tmul.rn.f32x2 %2, t, %3;\n\t}" \
+            : "+f"(f0), "+f"(f1), "=l"(acc)                                                              \
+            : "l"(wpair));                                                                               \
+    } else {                                                                                             \
+        asm("{\n\t.reg .b64 t;\n\t" OP("%0") OP("%1") "mov.b64 t, {%0, %1};\n\tfma.rn.f32x2 %2, t, %3, %2;\n\t}" \
+            : "+f"(f0), "+f"(f1), "+l"(acc)                                                              \
+            : "l"(wpair));                                                                               \
+    }
+    if (SAT) {
+        ITK_RELU_BODY(ITK_RELU_SAT)
+    } else {
+        ITK_RELU_BODY(ITK_RELU_MAX)
+    }
+#undef ITK_RELU_BODY
+#undef ITK_RELU_SAT
+#undef ITK_RELU_MAX
 }
 
-__device__ __forceinline__ void unpack_pair(uint64_t packed, float& lo, float& hi) {
+// Which column pairs (n = 0..7 of a thread's 16 heads) take their ReLUs on the FMA pipe.
+__host__ __device__ constexpr bool relu_sat(int n) {
+    return ITK_DEV_RELU == 2 || (ITK_DEV_RELU == 5 && (n & 1)) || (ITK_DEV_RELU == 6 && (n & 3) != 0) ||
+           (ITK_DEV_RELU == 7 && (n & 3) == 0);
+}
+
+constexpr float kSatUnscale = 33554432.0f;   // 2^25
+
+// One fragment (all 64 accumulator columns of a query row for TMEM lanes l and l+8: r[4n], r[4n+1]
+// belong to lane l, r[4n+2], r[4n+3] to lane l+8, column pair n = 0..7) into the packed partial
+// sums of the two lanes.
+__device__ __forceinline__ void fragment_fma(uint32_t (&r)[32], const uint64_t (&w)[8], uint64_t& acc_a,
+                                             uint64_t& acc_b) {
+#define ITK_STEP(N, F)                                                      \
+    relu_fma<relu_sat(N), F>(r[4 * N + 0], r[4 * N + 1], w[N], acc_a);       \
+    relu_fma<relu_sat(N), F>(r[4 * N + 2], r[4 * N + 3], w[N], acc_b);
+    ITK_STEP(0, true)
+    ITK_STEP(1, false)
+    ITK_STEP(2, false)
+    ITK_STEP(3, false)
+    ITK_STEP(4, false)
+    ITK_STEP(5, false)
+    ITK_STEP(6, false)
+    ITK_STEP(7, false)
+#undef ITK_STEP
+}
+
+__device__ __forceinline__ float pair_sum(uint64_t packed) {
+    float lo, hi;
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(packed));
+    return lo + hi;
 }
 
-__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
+// Threshold filter and store of one score in the Top-K mode, without a branch and without a warp
+// vote: the thread appends to its own candidate list (entry j of lane l of the segment sits at index
+// j * 32 + l, so the stores of a warp never meet in a bank).  score_at / id_at are the byte addresses
+// of the thread's next free entry, limit_at the end of its list.  Returns nonzero when the score is a
+// candidate but the list is full (the caller spills it).
+__device__ __forceinline__ uint32_t filter_store(float score, uint32_t score_bits, int key, int row_lo, unsigned row_span,
+                                                 float threshold, uint32_t id16, uint32_t& score_at, uint32_t& id_at,
+                                                 uint32_t limit_at) {
+    uint32_t full;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred in_range, active, room;\n\t"
+        ".reg .u32 offset;\n\t"
+        "sub.u32 offset, %3, %4;\n\t"
+        "setp.lt.u32 in_range, offset, %5;\n\t"
+        "setp.ge.and.f32 active, %6, %7, in_range;\n\t"
+        "setp.lt.and.u32 room, %0, %8, active;\n\t"
+        "@room st.shared.u32 [%0], %9;\n\t"
+        "@room st.shared.u16 [%1], %10;\n\t"
+        "@room add.u32 %0, %0, 128;\n\t"
+        "@room add.u32 %1, %1, 64;\n\t"
+        "xor.pred room, room, active;\n\t"
+        "selp.u32 %2, 1, 0, room;\n\t"
+        "}"
+        : "+r"(score_at), "+r"(id_at), "=r"(full)
+        : "r"(key), "r"(row_lo), "r"(row_span), "f"(score), "f"(threshold), "r"(limit_at), "r"(score_bits),
+          "h"(static_cast<uint16_t>(id16))
+        : "memory");
+    return full;
 }
 
-// ------------------------------------------------------------------ epilogue helpers
+// One lane of the warp (elected by the hardware) arrives on the barrier; no branch.
+__device__ __forceinline__ void mbar_arrive_elected(uint32_t bar_address) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred leader;\n\t"
+        "elect.sync _|leader, 0xffffffff;\n\t"
+        "@leader mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+        "}"
+        ::"r"(bar_address)
+        : "memory");
+}
 
 // What the epilogue needs to know about one query row of a unit.
 struct RowState {
@@ -940,10 +1096,10 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
 
 // Lane 0 waits on the barrier, the warp then reconverges: one poller per warp.
 template <bool DIAG, uint32_t PARK_NS = kWaitParkNs>
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane,
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int lane,
                                           long long& cycles) {
     int ok = 1;
-    if (lane == 0) ok = timed_wait<DIAG, PARK_NS>(bar, parity, abort_flag, cycles) ? 1 : 0;
+    if (lane == 0) ok = timed_wait<DIAG, PARK_NS>(bar, parity, ctl, cycles) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     return ok != 0;
 }
@@ -956,14 +1112,12 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 // the phase.  Bounded like mbar_wait.
 constexpr uint32_t kTileParkNs = 2000;
 // The UMMA issuer usually waits for the epilogue (an accumulator buffer to come back).  It shares its
-// scheduler with four epilogue warps, so it parks between probes instead of spinning; the park is short
-// because the hand-off it waits for is one tile (a microsecond or so) away.
+// scheduler with four epilogue warps, so it parks between probes instead of spinning.
 constexpr uint32_t kIssuerParkNs = 200;
 
 template <bool DIAG>
-__device__ __forceinline__ bool warp_tile_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                               long long& cycles) {
-    if (__all_sync(0xffffffffu, mbar_test_wait(bar, parity))) return true;
+__device__ __noinline__ bool warp_tile_wait_slow(uint32_t bar_address, uint32_t parity, const WaitCtl ctl, long long* cycles) {
+    uint64_t* bar = reinterpret_cast<uint64_t*>(__cvta_shared_to_generic(bar_address));
     const long long begin = DIAG ? clock64() : 0;
     uint64_t deadline = 0;
     bool ok = true;
@@ -971,32 +1125,53 @@ __device__ __forceinline__ bool warp_tile_wait(uint64_t* bar, uint32_t parity, v
         if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity, kTileParkNs))) break;
         if ((spin & 63u) == 0u) {
             const uint64_t now = global_timer_ns();
-            if (deadline == 0) deadline = now + kWaitLimitNs;
-            if (__any_sync(0xffffffffu, *abort_flag != 0 || now > deadline)) {
-                *abort_flag = 1;
+            if (deadline == 0) deadline = now + ctl.limit_ns;
+            if (__any_sync(0xffffffffu, *ctl.abort_flag != 0 || now > deadline)) {
+                *ctl.abort_flag = 1;
                 ok = false;
                 break;
             }
         }
     }
-    if (DIAG) cycles += clock64() - begin;
+    if (DIAG) *cycles += clock64() - begin;
     return ok;
+}
+
+// The common case in one probe and one vote: the tile is there already.
+template <bool DIAG>
+__device__ __forceinline__ bool warp_tile_wait(uint32_t bar_address, uint32_t parity, const WaitCtl& ctl, long long& cycles) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "vote.sync.all.pred p, p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar_address), "r"(parity)
+        : "memory");
+    if (done != 0u) return true;
+    return warp_tile_wait_slow<DIAG>(bar_address, parity, ctl, &cycles);
 }
 
 template <int MODE, bool DIAG, bool PAGED = false>
 __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_constant__ FusedParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    // Align by pointer arithmetic on the shared array (not through an integer cast) so that the
-    // compiler keeps the shared address space: LDS/STS/ATOMS instead of generic accesses.
-    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // The operand tiles (128-byte swizzle) and the histogram blocks need a 1 KB-aligned base; the
+    // kernel has no static shared memory in front of the dynamic block, and checks the address below.
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* smem_q = smem;
     uint8_t* smem_kv = smem + kQBytes;
     FusedShared& sh = *reinterpret_cast<FusedShared*>(smem + kSmemTileBytes);
-    volatile int* abort_flag = &sh.abort;
+    const WaitCtl ctl{&sh.abort, p.wait_limit_ns};
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
 
+    if ((smem_u32(smem) & 1023u) != 0u) {   // the same in every thread
+        if (threadIdx.x == 0) atomicOr(p.status, kStatusBadSharedBase);
+        return;
+    }
     if (MODE == kModeRepair) {
         // The usual case is that the fast path flagged no row: find that out with one parallel scan
         // of the flags before any barrier, TMEM or descriptor is set up.
@@ -1006,9 +1181,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         if (__syncthreads_or(any) == 0) return;
     }
 
-    for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * kScoreBins / 2; i += kThreads)
+    for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * kScoreBins; i += kThreads) {
         (&sh.row_hist[0][0])[i] = 0u;
-    for (int i = static_cast<int>(threadIdx.x); i < kBlockQ * 256; i += kThreads) sh.select[i >> 8].hist[i & 255] = 0;
+        sh.select[i >> 8].hist[i & 255] = 0;
+    }
+    if (threadIdx.x < kBlockQ * kSegments) (&sh.spill_counts[0][0])[threadIdx.x] = 0;
     if (threadIdx.x < kBlockQ) {
         sh.select[threadIdx.x].position = 0;
         sh.select[threadIdx.x].tickets = 0;
@@ -1040,10 +1217,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = sh.tmem_base;
-    ITK_BEAT(2);
 
-    const bool is_epilogue = warp >= kEpilogueWarp0 && warp < kEpilogueWarp0 + kEpilogueWarps;
-    if (!is_epilogue) {
     if (warp == 0) {
         // ============================================================ TMA producer
         if (lane == 0) {
@@ -1051,17 +1225,17 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             bool ok = true;
             long long wait_kv = 0, wait_q = 0;
             const long long role_begin = DIAG ? clock64() : 0;
-            for (int iter = 0; ok; ++iter) {
+            const bool withhold = DIAG && p.withhold_q_loads != 0;
+            for (int iter = 0; ok && !withhold; ++iter) {
                 Unit u;
                 if (!load_unit<MODE>(p, iter, u)) break;
                 if (u.tile_end == u.tile_begin) continue;
-                ok = timed_wait<DIAG>(&sh.q_empty, (q_iter & 1) ^ 1, abort_flag, wait_q);
+                ok = timed_wait<DIAG>(&sh.q_empty, (q_iter & 1) ^ 1, ctl, wait_q);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&sh.q_full, kQBytes);
                 tma_load_2d(smem_q, &p.map_q, &sh.q_full, 0, u.block * kUmmaN);
-                ITK_BEAT(10);
                 const int ws = q_iter & 1;
-                ok = timed_wait<DIAG>(&sh.w_empty[ws], ((q_iter >> 1) & 1) ^ 1, abort_flag, wait_q);
+                ok = timed_wait<DIAG>(&sh.w_empty[ws], ((q_iter >> 1) & 1) ^ 1, ctl, wait_q);
                 if (!ok) break;
                 const uint32_t w_bytes = static_cast<uint32_t>(u.nrows) * kHeads * sizeof(float);
                 mbar_arrive_expect_tx(&sh.w_full[ws], w_bytes);
@@ -1069,16 +1243,11 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                           &sh.w_full[ws]);
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
                     const int stage = kv_iter % kKvStages;
-                    ok = timed_wait<DIAG>(&sh.tile_done[stage], ((kv_iter / kKvStages) & 1) ^ 1, abort_flag, wait_kv);
+                    ok = timed_wait<DIAG>(&sh.tile_done[stage], ((kv_iter / kKvStages) & 1) ^ 1, ctl, wait_kv);
                     if (!ok) break;
-#if ITK_EXPERIMENT == 4
-                    mbar_arrive(&sh.kv_full[stage]);
-#else
                     mbar_arrive_expect_tx(&sh.kv_full[stage], kKvBytes);
                     tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0,
                                 (PAGED ? __ldg(p.tile_table + t) : t) * kTileKeys);
-#endif
-                    ITK_BEAT(100 + kv_iter);
                 }
                 ++q_iter;
             }
@@ -1101,6 +1270,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(kTileKeys, kUmmaN);
             const uint64_t desc_q = umma_desc_sw128_kmajor(smem_u32(smem_q));
+            const uint64_t desc_kv0 = umma_desc_sw128_kmajor(smem_u32(smem_kv));
             int kv_iter = 0, q_iter = 0;
             bool ok = true;
             long long wait_acc = 0, wait_kv = 0, wait_q = 0;
@@ -1109,33 +1279,30 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 Unit u;
                 if (!load_unit<MODE>(p, iter, u)) break;
                 if (u.tile_end == u.tile_begin) continue;
-                ok = timed_wait<DIAG>(&sh.q_full, q_iter & 1, abort_flag, wait_q);
+                ok = timed_wait<DIAG>(&sh.q_full, q_iter & 1, ctl, wait_q);
                 if (!ok) break;
-                ITK_BEAT(10);
-                // The tensor pipe accepts only a couple of UMMAs ahead of the one it executes, so
-                // every cycle this thread spends between two batches of issues is a bubble.  The
-                // barriers of tile t+1 are therefore probed while the UMMAs of tile t execute
-                // (a probe takes less time than one UMMA); the blocking waits at the top are
-                // normally satisfied already.
+                // Issuing a tile's four UMMAs occupies this thread for about as long as the tensor pipe
+                // needs for them, so the barriers of tile t+1 are probed while the UMMAs of tile t
+                // execute; the blocking waits at the top are normally satisfied already.
                 bool acc_ready = false, kv_ready = false;
                 for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
                     const int buffer = kv_iter & 1;
                     const int stage = kv_iter % kKvStages;
-                    ITK_BEAT(1000 + kv_iter * 10 + 1);
                     if (!acc_ready) {
-                        ok = timed_wait<DIAG, kIssuerParkNs>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, abort_flag, wait_acc);
+                        ok = timed_wait<DIAG, kIssuerParkNs>(&sh.acc_empty[buffer], ((kv_iter >> 1) & 1) ^ 1, ctl, wait_acc);
                         if (!ok) break;
                     }
                     if (!kv_ready) {
-                        ok = timed_wait<DIAG, kHotWait>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, abort_flag, wait_kv);
+                        ok = timed_wait<DIAG, kHotWait>(&sh.kv_full[stage], (kv_iter / kKvStages) & 1, ctl, wait_kv);
                         if (!ok) break;
                     }
                     tcgen05_fence_after_sync();
-                    const uint64_t desc_kv = umma_desc_sw128_kmajor(smem_u32(smem_kv + stage * kKvBytes));
+                    // key tile of the stage: 16 KB = 1024 descriptor address units apart; both operands
+                    // advance by 32 bytes (= 2 units) per K step
+                    const uint64_t desc_kv = desc_kv0 + static_cast<uint64_t>(stage * (kKvBytes >> 4));
                     const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buffer * kUmmaN);
                     const int next = kv_iter + 1;
                     const bool more = t + 1 < u.tile_end;
-                    // advance both operands by 32 bytes (= 2 descriptor address units) per K step
                     umma_f8(tmem_d, desc_kv, desc_q, idesc, 0u);
                     acc_ready = more && mbar_test_wait(&sh.acc_empty[next & 1], ((next >> 1) & 1) ^ 1);
                     umma_f8(tmem_d, desc_kv + 2, desc_q + 2, idesc, 1u);
@@ -1145,7 +1312,6 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     umma_f8(tmem_d, desc_kv + 6, desc_q + 6, idesc, 1u);
                     // a single commit per tile frees the key stage and publishes the accumulator
                     umma_commit(&sh.tile_done[stage]);
-                    ITK_BEAT(1000 + kv_iter * 10 + 2);
                 }
                 if (!ok) break;
                 umma_commit(&sh.q_empty);
@@ -1164,46 +1330,51 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) atomicOr(p.status, kStatusWaitExpired);
         }
-    }
     } else {
         // ============================================================ epilogue
         // Sixteen warps share every tile: warp (quarter, row) reads the 32 TMEM lanes (= keys) of
         // its lane quarter, which is also its candidate segment, and the 64 accumulator columns
         // (= heads) of one query row.  Accumulators come out of TMEM in the 16x256b fragment
-        // layout, 32 columns at a time: thread t of a warp holds, for lanes l = t/4 and l+8 of a
-        // 16-lane half, the column pairs 8n + 2(t%4) + {0,1}, n = 0..3.  So a thread needs only 16
+        // layout, 16 lanes at a time: thread t of a warp holds, for lanes l = t/4 and l+8 of a
+        // 16-lane half, the column pairs 8n + 2(t%4) + {0,1}, n = 0..7.  So a thread needs only 16
         // of the row's 64 head weights, kept in registers for the whole unit: no shared-memory
         // traffic in the hot loop.  The four threads of a quad combine their partial head sums
         // with two shuffles, after which every thread owns the score of exactly one key of the
         // tile.  Four warps per scheduler hide one another's TMEM and arithmetic latencies.
         const int ew = warp - kEpilogueWarp0;
-        const int quarter = ew & 3;             // = warp % 4, the TMEM lane quarter this warp may read
+        const int quarter = warp & 3;           // the TMEM lane quarter this warp may read
         const int own_r = ew >> 2;              // query row of the unit this warp finishes
         const int quad = lane & 3;              // column-pair selector inside the fragment
-        int own_lane = (lane >> 2) + 8 * quad;   // key (TMEM lane) of the quarter this thread finishes
+        int own_key = quarter * 32 + (lane >> 2) + 8 * quad;   // key of a tile (= TMEM lane) this thread finishes
         uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(own_r * kHeads);
-        keep_in_register(own_lane);
+        keep_in_register(own_key);
         keep_in_register(tmem_lane);
+        // this thread's candidate list: entries j * 32 + lane of the (row, quarter) segment
+        uint32_t score_list = smem_u32(&sh.cand_scores[own_r][quarter * kSegCap + lane]);
+        uint32_t id_list = smem_u32(&sh.cand_ids[own_r][quarter * kSegCap + lane]);
+        keep_in_register(score_list);
+        keep_in_register(id_list);
+        const uint32_t tile_done_bars = smem_u32(&sh.tile_done[0]);
+        const uint32_t acc_empty_bars = smem_u32(&sh.acc_empty[0]);
         int unit_iter = 0;  // units with tiles
         int acc_iter = 0;   // tiles
         bool ok = true;
         long long wait_acc = 0, wait_w = 0, select_cycles = 0;
+
         const long long role_begin = DIAG ? clock64() : 0;
         if (DIAG && p.trace != nullptr && ew == 0 && lane == 0)
             p.trace[static_cast<long long>(blockIdx.x) * kTraceFields + kTraceNsBegin] = global_timer_ns();
         // What the row's four warps do when the unit's candidates are complete (or the unit has no tile
         // at all): exact Top-K of the row, or its sampled threshold.  All four warps of a row call it.
-        long long laps[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-        RowBarrier rb{&sh.row_bar[own_r], 0u, abort_flag, DIAG ? laps : nullptr, 0};
-        const auto finish_row = [&](const Unit& u, bool has_tiles) {
+        long long laps[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        RowBarrier rb{&sh.row_bar[own_r], 0u, ctl, DIAG ? laps : nullptr, 0};
+        const auto finish_row = [&](const Unit& u, bool has_tiles, int lane_entries) {
             const long long begin = DIAG ? clock64() : 0;
             bool solo = false;
             if (own_r < u.nrows) {
                 if (MODE == kModeTopK) {
-#if ITK_EXPERIMENT < 6
-                    if (!(DIAG && (p.debug_skip & 1))) select_topk_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
-#endif
+                    select_topk_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane, lane_entries);
                 } else if (MODE == kModeSample) {
                     solo = sample_threshold_row(sh, p, u, own_r, has_tiles, rb, quarter * 32 + lane);
                 }
@@ -1218,22 +1389,14 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             Unit u;
             if (!load_unit<MODE>(p, iter, u)) break;
             if (u.tile_end == u.tile_begin) {
-                finish_row(u, false);
+                finish_row(u, false, 0);
                 continue;
             }
             const int slot = unit_iter & 1;   // weight buffer of the unit
             const uint32_t use_parity = (unit_iter >> 1) & 1;
-            ok = warp_wait<DIAG>(&sh.w_full[slot], use_parity, abort_flag, lane, wait_w);
+            ok = warp_wait<DIAG>(&sh.w_full[slot], use_parity, ctl, lane, wait_w);
             if (!ok) break;
-            ITK_BEAT(11 + 100000 * unit_iter);
 
-            // candidate segment of (row, quarter) and the number of candidates in it (warp-uniform)
-            uint32_t score_slots = smem_u32(&sh.cand_scores[own_r][quarter * kSegCap]);
-            uint32_t id_slots = smem_u32(&sh.cand_ids[own_r][quarter * kSegCap]);
-            keep_in_register(score_slots);
-            keep_in_register(id_slots);
-            const uint32_t hist_slots = smem_u32(&sh.row_hist[own_r][0]);
-            int count = 0;
             // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
             // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
             // that keep every key); a row that is switched off has an empty range.
@@ -1246,50 +1409,27 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             keep_in_register(row_span);
             keep_in_register(threshold);
 
-            // head weights of this thread's column pairs
+            // head weights of this thread's column pairs; a pair whose ReLUs are the saturating
+            // multiply by 2^-25 carries the factor 2^25 in its weights
             uint64_t w[8];
 #pragma unroll
-            for (int n = 0; n < 8; ++n)
-                w[n] = *reinterpret_cast<const uint64_t*>(&sh.weights[slot][own_r * kHeads + 8 * n + 2 * quad]);
+            for (int n = 0; n < 8; ++n) {
+                const float2 pair = *reinterpret_cast<const float2*>(&sh.weights[slot][own_r * kHeads + 8 * n + 2 * quad]);
+                const float lo = relu_sat(n) ? pair.x * kSatUnscale : pair.x;
+                const float hi = relu_sat(n) ? pair.y * kSatUnscale : pair.y;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(w[n]) : "f"(lo), "f"(hi));
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh.w_empty[slot]);   // weights are in registers now
-            ITK_BEAT(12 + 100000 * unit_iter);
 
             // scale and range key of the key this thread finishes in tile t
             const auto per_key = [&](int t, float& scale, int& range_key) {
-                const int key = t * kTileKeys + quarter * 32 + own_lane;
+                const int key = t * kTileKeys + own_key;
                 const bool key_ok = key < p.keys;
                 // a paged key keeps its logical position (ids, ranges); only its storage moves
-                const int stored = PAGED ? __ldg(p.tile_table + t) * kTileKeys + quarter * 32 + own_lane : key;
+                const int stored = PAGED ? __ldg(p.tile_table + t) * kTileKeys + own_key : key;
                 scale = key_ok ? __ldg(p.kv_scales + stored) : 0.0f;
                 if (MODE == kModeSample) range_key = key_ok ? __ldg(p.sample_ids + key) : 0x7fffffff;
-            };
-            // ReLU is applied in place on the fragment registers, which are consecutive pairs
-            // already, so the packed multiply-add can read them without any move.
-            const auto relu_fma = [](uint32_t& x0, uint32_t& x1, uint64_t wpair, uint64_t& acc) {
-                asm("{\n\t"
-                    ".reg .b64 t;\n\t"
-                    "max.f32 %0, %0, 0f00000000;\n\t"
-                    "max.f32 %1, %1, 0f00000000;\n\t"
-                    "mov.b64 t, {%0, %1};\n\t"
-                    "fma.rn.f32x2 %2, t, %3, %2;\n\t"
-                    "}"
-                    : "+f"(*reinterpret_cast<float*>(&x0)), "+f"(*reinterpret_cast<float*>(&x1)), "+l"(acc)
-                    : "l"(wpair));
-            };
-            // one fragment (32 columns, lanes l and l+8) into the packed accumulators of the two lanes
-            const auto partial = [&](uint32_t (&r)[16], int w0, uint64_t (&acc_a)[2], uint64_t (&acc_b)[2]) {
-#pragma unroll
-                for (int n = 0; n < 4; ++n) {
-                    relu_fma(r[4 * n + 0], r[4 * n + 1], w[w0 + n], acc_a[n & 1]);
-                    relu_fma(r[4 * n + 2], r[4 * n + 3], w[w0 + n], acc_b[n & 1]);
-                }
-            };
-            const auto head_sum = [](const uint64_t (&acc)[2]) -> float {
-                float x0, x1, x2, x3;
-                unpack_pair(acc[0], x0, x1);
-                unpack_pair(acc[1], x2, x3);
-                return (x0 + x1) + (x2 + x3);
             };
             // Quad reduce-scatter of the four partial sums (lanes l, l+8, l+16, l+24 of the quarter):
             // thread `quad` ends up with the complete head sum number `quad`.
@@ -1302,13 +1442,18 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 const bool upper = (quad & 2) != 0;
                 return (upper ? keep_b : keep_a) + __shfl_xor_sync(0xffffffffu, upper ? keep_a : keep_b, 2);
             };
-            // threshold filter and warp-level compaction of the 32 scores of this warp in one tile
-            // Filter and warp-level compaction of the 32 scores of this warp in one tile.
+
+            // Top-K mode: the thread's own candidate list (next free entry, end of the list)
+            uint32_t score_at = score_list, id_at = id_list;
+            const uint32_t limit_at = score_list + static_cast<uint32_t>(kSegCap / 32) * 128u;
+            int count = 0;   // sample mode: candidates of the warp's segment (dense, warp-uniform)
+
+            // What happens to the 32 scores of this warp in one tile.
             const auto finish = [&](int t, float sum, float scale, int sample_key) {
-                const float score = sum * scale;
-                const int key = t * kTileKeys + quarter * 32 + own_lane;
+                // the fused add of +0 turns a -0 product into +0 and changes no other value
+                const float score = __fmaf_rn(sum, scale, 0.0f);
+                const int key = t * kTileKeys + own_key;
                 const int range_key = MODE == kModeSample ? sample_key : key;   // the sampled key's position in the context
-                const bool in_range = static_cast<unsigned>(range_key - row_lo) < row_span;
                 if (DIAG) {
                     const bool key_ok = key < p.keys;
                     if (own_r < u.nrows && key_ok && p.diag_logits != nullptr) {
@@ -1325,117 +1470,68 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     }
                     return;
                 }
-                bool active = in_range;
-                if (DIAG && (p.debug_skip & 2)) active = false;
-                if (MODE == kModeTopK) active = active && score >= threshold;
-                else active = active && (fabsf(score) <= 3.4028234663852886e38f);  // finite
-                const unsigned ballot = __ballot_sync(0xffffffffu, active);
-                const int position = count + __popc(ballot & ((1u << lane) - 1u));
-                count += __popc(ballot);
-                const uint32_t score_bits = ordered_bits(score);
-                if (MODE == kModeTopK && active) {
-                    // one more candidate in its bin of the row's score histogram (16-bit counters)
-                    const uint32_t bin = __float_as_uint(ordered_to_float(score_bits) - threshold) >> 23;
-                    red_shared_add_u32(hist_slots + 4u * (bin >> 1), 1u << ((bin & 1u) * 16u));
-                }
-                if (active && position < kSegCap) {
-                    st_shared_u32(score_slots + 4u * static_cast<uint32_t>(position), score_bits);
-                    // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
-                    st_shared_u16(id_slots + 2u * static_cast<uint32_t>(position), static_cast<uint32_t>(t * 32 + own_lane));
-                }
-                if (MODE == kModeTopK && count > kSegCap) {
-                    // warp-uniform and rare: the segment is full, later candidates go to the global spill
-                    if (active && position >= kSegCap && position < kSegCap + kSpillSegCap) {
-                        const long long row_slot = static_cast<long long>(u.shard) * p.rows + u.row0 + own_r;
-                        p.spill[row_slot * kSpillRow + quarter * kSpillSegCap + (position - kSegCap)] =
-                            pack_score_id(score, static_cast<uint32_t>(key));
+                const uint32_t bits = __float_as_uint(score);
+                const uint32_t score_bits = bits ^ (static_cast<uint32_t>(static_cast<int32_t>(bits) >> 31) | 0x80000000u);
+                // id = (tile << 5) | (key & 31); the segment number carries the lane quarter
+                const uint32_t id16 = static_cast<uint32_t>(t * 32 + (own_key & 31));
+                if (MODE == kModeTopK) {
+                    if (filter_store(score, bits, key, row_lo, row_span, threshold, id16, score_at, id_at, limit_at)) {
+                        // rare: this thread's list is full, the candidate goes to the segment's global spill
+                        const int at = atomicAdd(&sh.spill_counts[own_r][quarter], 1);
+                        if (at < kSpillSegCap)
+                            p.spill[row.slot * kSpillRow + quarter * kSpillSegCap + at] =
+                                (static_cast<uint64_t>(score_bits) << 32) | static_cast<uint32_t>(key);
+                    }
+                } else {
+                    // sample mode: dense segment, filled in warp-vote order
+                    const bool active = static_cast<unsigned>(range_key - row_lo) < row_span &&
+                                        fabsf(score) <= 3.4028234663852886e38f;   // finite
+                    const unsigned ballot = __ballot_sync(0xffffffffu, active);
+                    const int position = count + __popc(ballot & lanemask_lt());
+                    count += __popc(ballot);
+                    if (active && position < kSegCap) {
+                        sh.cand_scores[own_r][quarter * kSegCap + position] = score_bits;
+                        sh.cand_ids[own_r][quarter * kSegCap + position] = static_cast<uint16_t>(id16);
                     }
                 }
             };
 
-            // Four fragment loads per tile, (half 0, heads 0-31), (half 0, heads 32-63), (half 1, heads
-            // 0-31), (half 1, heads 32-63), through one 16-register buffer: the register budget has no
-            // room for a second one, and the other three epilogue warps of the scheduler cover the TMEM
-            // latency.  The accumulator buffer goes back to the UMMA issuer as soon as the fourth
-            // fragment has landed; the first fragment of the next tile is requested before the filter step.
-            uint32_t fa[16];
+            // Two fragment loads per tile, one per 16-lane half of the quarter, through one 32-register
+            // buffer; the other three epilogue warps of the scheduler cover the TMEM latency.  The
+            // accumulator buffer goes back to the UMMA issuer as soon as the second fragment has landed.
+            uint32_t frag[32];
             float scale, next_scale = 0.0f;
             int range_key = 0, next_range_key = 0;   // sample mode only
             per_key(u.tile_begin, scale, range_key);
-            ok = warp_tile_wait<DIAG>(&sh.tile_done[acc_iter % kKvStages], (acc_iter / kKvStages) & 1, abort_flag, wait_acc);
-            if (!ok) break;
-            tcgen05_fence_after_sync();
-            tmem_load_frag16(tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN), fa);
             for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
-                ITK_BEAT(100 * acc_iter + 20);
+                ok = warp_tile_wait<DIAG>(tile_done_bars + 8u * static_cast<uint32_t>(acc_iter % kKvStages),
+                                          (acc_iter / kKvStages) & 1, ctl, wait_acc);
+                if (!ok) break;
+                tcgen05_fence_after_sync();
                 const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
-                const uint32_t upper_half = 16u << 16;
-                const bool more = t + 1 < u.tile_end;
-                if (more) per_key(t + 1, next_scale, next_range_key);
-                uint64_t acc_a[2] = {0, 0}, acc_b[2] = {0, 0};
-
-                tmem_load_wait16(fa);                                 // (half 0, heads 0-31)
-                ITK_BEAT(100 * acc_iter + 21);
-#if ITK_EXPERIMENT != 1
-                partial(fa, 0, acc_a, acc_b);
-#else
-                if (fa[3] == 0x7fc12345u) count += 1;
-#endif
-                tmem_load_frag16(taddr + 32, fa);
-                tmem_load_wait16(fa);                                 // (half 0, heads 32-63)
-                ITK_BEAT(100 * acc_iter + 22);
-#if ITK_EXPERIMENT != 1
-                partial(fa, 4, acc_a, acc_b);
-#else
-                if (fa[3] == 0x7fc12345u) count += 1;
-#endif
-                tmem_load_frag16(taddr + upper_half, fa);
-                const float sum0 = head_sum(acc_a), sum1 = head_sum(acc_b);   // lanes l and l+8 of the quarter
-                acc_a[0] = acc_a[1] = acc_b[0] = acc_b[1] = 0;
-                tmem_load_wait16(fa);                                 // (half 1, heads 0-31)
-                ITK_BEAT(100 * acc_iter + 23);
-#if ITK_EXPERIMENT != 1
-                partial(fa, 0, acc_a, acc_b);
-#else
-                if (fa[3] == 0x7fc12345u) count += 1;
-#endif
-                tmem_load_frag16(taddr + upper_half + 32, fa);
-                tmem_load_wait16(fa);                                 // (half 1, heads 32-63): buffer fully read
-                ITK_BEAT(100 * acc_iter + 24);
+                tmem_load_frag(taddr, frag);                          // lanes 0-15 of the quarter
+                if (t + 1 < u.tile_end) per_key(t + 1, next_scale, next_range_key);
+                uint64_t acc_a, acc_b;
+                tmem_load_wait(frag);
+                fragment_fma(frag, w, acc_a, acc_b);
+                tmem_load_frag(taddr + (16u << 16), frag);            // lanes 16-31 of the quarter
+                const float sum0 = pair_sum(acc_a), sum1 = pair_sum(acc_b);   // lanes l and l+8 of the quarter
+                tmem_load_wait(frag);                                 // the accumulator buffer is fully read
                 tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sh.acc_empty[acc_iter & 1]);
-                ITK_BEAT(100 * acc_iter + 25);
-#if ITK_EXPERIMENT != 1
-                partial(fa, 4, acc_a, acc_b);
-#else
-                if (fa[3] == 0x7fc12345u) count += 1;
-#endif
-                if (more) {
-                    const int next = acc_iter + 1;
-                    ok = warp_tile_wait<DIAG>(&sh.tile_done[next % kKvStages], (next / kKvStages) & 1, abort_flag, wait_acc);
-                    if (!ok) break;
-                    tcgen05_fence_after_sync();
-                    tmem_load_frag16(tmem_lane + static_cast<uint32_t>((next & 1) * kUmmaN), fa);
-                }
-                ITK_BEAT(100 * acc_iter + 26);
-#if ITK_EXPERIMENT == 0 || ITK_EXPERIMENT == 6
-                finish(t, quad_reduce(sum0, sum1, head_sum(acc_a), head_sum(acc_b)), scale, range_key);
-#elif ITK_EXPERIMENT == 7   // no filter / compaction
-                if (quad_reduce(sum0, sum1, head_sum(acc_a), head_sum(acc_b)) * scale >= threshold) count += 1;
-#elif ITK_EXPERIMENT == 2
-                if (sum0 + sum1 + head_sum(acc_a) + head_sum(acc_b) == 1.2345e38f) count += 1;
-#endif
+                mbar_arrive_elected(acc_empty_bars + 8u * static_cast<uint32_t>(acc_iter & 1));
+                fragment_fma(frag, w, acc_a, acc_b);
+                finish(t, quad_reduce(sum0, sum1, pair_sum(acc_a), pair_sum(acc_b)), scale, range_key);
                 scale = next_scale;
                 range_key = next_range_key;
-                ITK_BEAT(100 * acc_iter + 27);
             }
             if (!ok) break;
-            if (MODE != kModeRepair) {
+            int lane_entries = 0;
+            if (MODE == kModeTopK) lane_entries = static_cast<int>(score_at - score_list) >> 7;
+            if (MODE == kModeSample) {
                 if (lane == 0) sh.counts[own_r][quarter] = count;
                 row_sync(rb);   // the four segments of the row are complete and counted
             }
-            finish_row(u, true);
+            finish_row(u, true, lane_entries);
             ++unit_iter;
         }
         if (DIAG && p.trace != nullptr && quarter == 0 && own_r < 2 && lane == 0) {
@@ -1446,18 +1542,12 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             trace[kTraceEpiWaitW] = wait_w;
             if (own_r == 0) {
                 long long* cta_trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
-                cta_trace[27] = laps[0];   // candidate caching
-                cta_trace[28] = laps[1];   // octave from the histogram
-                cta_trace[29] = laps[2];   // second-level histogram
-                cta_trace[30] = laps[3];   // list gathering
-                cta_trace[31] = laps[4];   // list ranking
-                cta_trace[20] = laps[11];  // emission: placing
-                cta_trace[22] = laps[12];  // emission: counting
-                cta_trace[23] = laps[13];  // emission: position reservation
-                cta_trace[21] = laps[6];   // clean-up and last barrier
-                cta_trace[5] = laps[8];    // second level: histogram pass
-                cta_trace[6] = laps[9];    // second level: barrier
-                cta_trace[7] = laps[10];   // gathering pass
+                cta_trace[27] = laps[1];   // octave histogram pass
+                cta_trace[28] = laps[2];   // sub-bin histogram pass
+                cta_trace[29] = laps[3];   // emission
+                cta_trace[30] = laps[4];   // list ranking
+                cta_trace[31] = laps[5];   // whole selection incl. fallback
+                cta_trace[20] = laps[6];   // clean-up
                 cta_trace[kTraceNsEnd] = global_timer_ns();
             }
         }
@@ -1465,10 +1555,16 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
     }
 
     // ---------------------------------------------------------------- teardown
-    ITK_BEAT(900000);
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
+        if (sh.abort != 0) {
+            // a wait expired: UMMAs issued before that may still be in the tensor pipe (a tile takes
+            // well under a microsecond); TMEM is not freed under them
+            const uint64_t until = global_timer_ns() + 2000000ull;
+            while (global_timer_ns() < until) {
+            }
+        }
         __syncwarp();
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemColumns);

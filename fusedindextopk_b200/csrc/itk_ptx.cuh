@@ -75,18 +75,19 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Wall-clock limit of one wait.  The longest legitimate wait is the UMMA issuer or the
-// TMA producer waiting out the Top-K selection at the end of a unit (tens of microseconds).
+// Default wall-clock limit of one wait.  The longest legitimate wait is the UMMA issuer or the
+// TMA producer waiting out the Top-K selection at the end of a unit (microseconds).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// Waits for the phase with the given parity.  Returns false when the limit
+// Waits for the phase with the given parity.  Returns false when limit_ns
 // expired or another thread of the CTA already gave up (*abort_flag != 0); the
 // caller then leaves its role loop.  PARK_NS = 0 polls without parking, otherwise a
 // failed probe suspends the thread for up to PARK_NS nanoseconds.
 constexpr uint32_t kHotWait = 0;
 
 template <uint32_t PARK_NS = kWaitParkNs>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     constexpr bool kHot = PARK_NS == kHotWait;
     if (mbar_test_wait(bar, parity)) return true;
     uint64_t deadline = 0;
@@ -96,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag != 0) return false;
             const uint64_t now = global_timer_ns();
             if (deadline == 0) {
-                deadline = now + kWaitLimitNs;
+                deadline = now + limit_ns;
             } else if (now > deadline) {
                 *abort_flag = 1;
                 return false;

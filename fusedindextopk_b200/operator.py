@@ -243,7 +243,8 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
 
 
 def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, thresholds=None,
-                   diag_logits=None, trace=None, debug_skip: int = 0, force_compute: bool = False, max_ctas: int = 0,
+                   diag_logits=None, trace=None, force_compute: bool = False, max_ctas: int = 0,
+                   wait_limit_ns: int = 0, withhold_loads: bool = False,
                    key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
     """Stage ``fused_topk``: one launch of the persistent fused kernel.
 
@@ -266,7 +267,8 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.diag_logits = ptr(diag_logits)
     args.diag_stride = 0 if diag_logits is None else int(diag_logits.stride(0))
     args.trace = ptr(trace)
-    args.debug_skip = debug_skip
+    args.wait_limit_ns = int(wait_limit_ns)
+    args.withhold_loads = 1 if withhold_loads else 0
     args.status = ptr(ws.status)
     args.rows, args.keys = ws.rows, ws.keys
     args.key_lo = key_lo

@@ -120,8 +120,11 @@ typedef struct itk_fused_args {
                                  * Counterpart of the ITK_LONG_DIAGNOSTIC trace
                                  * (kernel/csrc/include/fused_index_topk/long_cta_topk.cuh:8-29) */
     int* status;                /* device status word (or-ed) */
-    int debug_skip;             /* diagnostic build only, timing experiments: 1 no selection, 2 no compaction,
-                                 * 4 no head reduction (results are then meaningless) */
+    unsigned long long wait_limit_ns; /* wall-clock limit of every wait inside the kernel; 0 = 2 s.  A wait that
+                                 * runs out sets bit 0 of *status, the kernel drains and returns */
+    int withhold_loads;         /* diagnostic build only, for tests of the expiry path: the kernel issues no
+                                 * load, so its first wait runs into wait_limit_ns and it returns with the
+                                 * status bit set; nothing is computed */
     int rows;                   /* Q */
     int keys;                   /* N */
     int key_lo;                 /* first key scored (multiple of 128) */
@@ -131,7 +134,8 @@ typedef struct itk_fused_args {
     int block_stride;           /* stride between owned blocks (number of ranks) */
     int num_blocks;             /* owned blocks */
     int force_compute;          /* 1: score rows even when all their keys are selected anyway */
-    int max_ctas;               /* 0 = one CTA per SM */
+    int max_ctas;               /* 0 = one CTA per SM; otherwise the grid is capped (the reference plugin's
+                                 * debug_ctas option, kernel/plugin.py:95-130) */
     int thresholds_per_row;     /* with shards > 1: thresholds has [Q] entries (one per row, shared by its
                                  * shards) and a shard that finds fewer than 2048 candidates returns them
                                  * all instead of failing; the merge decides whether the row is complete */
