@@ -40,10 +40,6 @@
 #include <cstddef>
 #include <type_traits>
 
-// Development switch (timing studies): which unit computes the ReLUs of the epilogue.
-#ifndef ITK_DEV_RELU
-#define ITK_DEV_RELU 2
-#endif
 
 namespace itk {
 
@@ -66,8 +62,8 @@ constexpr int kRepairChunk = 16384;
 
 // Warp 0: TMA producer; warp 1: UMMA issuer; warps 2-17: epilogue and per-row selection (a warp may
 // only read the TMEM lane quarter warp % 4, so sixteen consecutive warps cover every quarter four
-// times: once per query row of the unit).  65536 / 576 rounded down to the allocation unit of 8
-// gives every thread 112 registers, of which the five warps of a scheduler can use 96.
+// times: once per query row of the unit).  Five warps share the first two schedulers, which caps
+// the kernel at 96 registers per thread.
 constexpr int kThreads = 576;
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueThreads = 512;
@@ -272,6 +268,10 @@ constexpr int kRowThreads = 128;
 // expires (or another role already gave up) the abort flag is set and the call returns as if the
 // barrier had completed: the results are garbage then, but every later wait sees the flag, the
 // kernel ends and the host reads the failure from the status word.
+// A waiting warp parks in the hardware between probes: the warps of the other three rows share its
+// scheduler and its shared-memory pipe, and a warp that polls without pause slows them several times.
+constexpr uint32_t kRowParkNs = 200;
+
 struct RowBarrier {
     uint64_t* bar;
     uint32_t phase;
@@ -292,7 +292,7 @@ __device__ __forceinline__ void lap(RowBarrier& rb, int index) {
 __device__ __forceinline__ void row_sync(RowBarrier& rb) {
     __syncwarp();
     if ((threadIdx.x & 31u) == 0u) mbar_arrive(rb.bar);   // one arrival per warp
-    if (!mbar_wait<kHotWait>(rb.bar, rb.phase & 1u, rb.ctl.abort_flag, rb.ctl.limit_ns)) *rb.ctl.abort_flag = 1;
+    if (!mbar_wait<kRowParkNs>(rb.bar, rb.phase & 1u, rb.ctl.abort_flag, rb.ctl.limit_ns)) *rb.ctl.abort_flag = 1;
     ++rb.phase;
 }
 
@@ -948,44 +948,32 @@ __device__ __forceinline__ bool sample_threshold_row(FusedShared& sh, const Fuse
 // ------------------------------------------------------------------ epilogue arithmetic
 
 // ReLU of two neighbouring accumulator columns and their packed multiply-add with the two head
-// weights.  A ReLU is either max(x, 0) on the integer/compare pipe (which issues it at half rate) or
-// fma.rn.sat(x, 2^-25, 0) on the FMA pipe: |x| <= 128 * 448^2 < 2^25, so the saturating multiply
+// weights.  The ReLU is fma.rn.sat(x, 2^-25, 0) on the FMA pipe rather than max(x, 0), which the
+// integer/compare pipe issues at half rate: |x| <= 128 * 448^2 < 2^25, so the saturating multiply
 // by 2^-25 is exact for x > 0, clamps x <= 0 (and NaN) to +0 and never reaches the upper clamp; the
-// weights of such a column pair are pre-multiplied by 2^25 (exact for |w| < 2^103), so that every
-// product, and with it every partial sum, is bit-identical to the max form.  Splitting the ReLUs
-// over both pipes balances them.  The two accumulator registers are neighbours of an even/odd
-// register pair already (they come out of one tcgen05.ld), so packing them costs no move; both
-// ReLUs of a pair use the same form (mixed pairs made the assembler insert a register move each).
-template <bool SAT, bool FIRST>
+// head weights are pre-multiplied by 2^25 (exact for |w| < 2^103), so that every product, and with
+// it every partial sum, is bit-identical to the max form.  The two accumulator registers are
+// neighbours of an even/odd register pair already (they come out of one tcgen05.ld), so packing them
+// costs no move.
+template <bool FIRST>
 __device__ __forceinline__ void relu_fma(uint32_t& x0, uint32_t& x1, uint64_t wpair, uint64_t& acc) {
     float& f0 = *reinterpret_cast<float*>(&x0);
     float& f1 = *reinterpret_cast<float*>(&x1);
-#define ITK_RELU_MAX(r) "max.f32 " r ", " r ", 0f00000000;\n\t"
-#define ITK_RELU_SAT(r) "fma.rn.sat.f32 " r ", " r ", 0f33000000, 0f00000000;\n\t"
-#define ITK_RELU_BODY(OP)                                                                                \
-    if (FIRST) {                                                                                         \
-        asm("{\n\t.reg .b64 t;\n\t" OP("%0") OP("%1") "mov.b64 t, {%0, %1};\n\tmul.rn.f32x2 %2, t, %3;\n\t}" \
-            : "+f"(f0), "+f"(f1), "=l"(acc)                                                              \
-            : "l"(wpair));                                                                               \
-    } else {                                                                                             \
-        asm("{\n\t.reg .b64 t;\n\t" OP("%0") OP("%1") "mov.b64 t, {%0, %1};\n\tfma.rn.f32x2 %2, t, %3, %2;\n\t}" \
-            : "+f"(f0), "+f"(f1), "+l"(acc)                                                              \
-            : "l"(wpair));                                                                               \
-    }
-    if (SAT) {
-        ITK_RELU_BODY(ITK_RELU_SAT)
+    if (FIRST) {
+        asm("{\n\t.reg .b64 t;\n\t"
+            "fma.rn.sat.f32 %0, %0, 0f33000000, 0f00000000;\n\t"
+            "fma.rn.sat.f32 %1, %1, 0f33000000, 0f00000000;\n\t"
+            "mov.b64 t, {%0, %1};\n\tmul.rn.f32x2 %2, t, %3;\n\t}"
+            : "+f"(f0), "+f"(f1), "=l"(acc)
+            : "l"(wpair));
     } else {
-        ITK_RELU_BODY(ITK_RELU_MAX)
+        asm("{\n\t.reg .b64 t;\n\t"
+            "fma.rn.sat.f32 %0, %0, 0f33000000, 0f00000000;\n\t"
+            "fma.rn.sat.f32 %1, %1, 0f33000000, 0f00000000;\n\t"
+            "mov.b64 t, {%0, %1};\n\tfma.rn.f32x2 %2, t, %3, %2;\n\t}"
+            : "+f"(f0), "+f"(f1), "+l"(acc)
+            : "l"(wpair));
     }
-#undef ITK_RELU_BODY
-#undef ITK_RELU_SAT
-#undef ITK_RELU_MAX
-}
-
-// Which column pairs (n = 0..7 of a thread's 16 heads) take their ReLUs on the FMA pipe.
-__host__ __device__ constexpr bool relu_sat(int n) {
-    return ITK_DEV_RELU == 2 || (ITK_DEV_RELU == 5 && (n & 1)) || (ITK_DEV_RELU == 6 && (n & 3) != 0) ||
-           (ITK_DEV_RELU == 7 && (n & 3) == 0);
 }
 
 constexpr float kSatUnscale = 33554432.0f;   // 2^25
@@ -995,9 +983,9 @@ constexpr float kSatUnscale = 33554432.0f;   // 2^25
 // sums of the two lanes.
 __device__ __forceinline__ void fragment_fma(uint32_t (&r)[32], const uint64_t (&w)[8], uint64_t& acc_a,
                                              uint64_t& acc_b) {
-#define ITK_STEP(N, F)                                                      \
-    relu_fma<relu_sat(N), F>(r[4 * N + 0], r[4 * N + 1], w[N], acc_a);       \
-    relu_fma<relu_sat(N), F>(r[4 * N + 2], r[4 * N + 3], w[N], acc_b);
+#define ITK_STEP(N, F)                                          \
+    relu_fma<F>(r[4 * N + 0], r[4 * N + 1], w[N], acc_a);       \
+    relu_fma<F>(r[4 * N + 2], r[4 * N + 3], w[N], acc_b);
     ITK_STEP(0, true)
     ITK_STEP(1, false)
     ITK_STEP(2, false)
@@ -1057,6 +1045,167 @@ __device__ __forceinline__ void mbar_arrive_elected(uint32_t bar_address) {
         ::"r"(bar_address)
         : "memory");
 }
+
+// ------------------------------------------------------------------ the Top-K tile loop in PTX
+
+// The tile loop of an epilogue warp in the Top-K mode, written in PTX as one block: every branch in
+// it is uniform (warp votes decide), every per-thread decision is a predicate, and the addresses and
+// counters that change from tile to tile are carried in registers.  The same loop written in C++
+// compiled to about a third more instructions per tile (divergence scaffolding around votes,
+// shuffles and the one-lane barrier arrival, re-derived indices, register moves), and the epilogue
+// is bound by instruction issue.
+//
+// Per tile: wait for the accumulator (one parked probe and a vote; if that fails the loop is left
+// so that the caller can do the bounded wait), load the 16-lane halves of the warp's TMEM quarter
+// one after the other through the same 32 registers, ReLU and packed multiply-add with the head
+// weights, hand the accumulator back after the second load, reduce the four partial head sums of a
+// quad so that every thread owns the score of one key, multiply by the key scale (prefetched one
+// tile ahead), filter against range and threshold and append the candidate to the thread's own list.
+//
+// Returns why it stopped: kLoopDone (tile_end reached), kLoopNeedWait (the accumulator of tile t is
+// not there yet), kLoopSpill (some thread's list is full: `full` is nonzero in those threads, whose
+// candidate of the tile just finished, key - 128 with score last_score, goes to the spill).
+constexpr uint32_t kLoopDone = 0, kLoopNeedWait = 1, kLoopSpill = 2;
+
+#define ITK_PTX_RELU(r) "fma.rn.sat.f32 " r ", " r ", 0f33000000, 0f00000000;\n\t"
+// column pair of TMEM lane l (registers a0, a1) and of lane l+8 (b0, b1) with weight pair W
+#define ITK_PTX_PAIR_FIRST(a0, a1, b0, b1, W)                                                        \
+    ITK_PTX_RELU(a0) ITK_PTX_RELU(a1) "mov.b64 pa, {" a0 ", " a1 "};\n\tmul.rn.f32x2 acc_a, pa, " W ";\n\t" \
+    ITK_PTX_RELU(b0) ITK_PTX_RELU(b1) "mov.b64 pb, {" b0 ", " b1 "};\n\tmul.rn.f32x2 acc_b, pb, " W ";\n\t"
+#define ITK_PTX_PAIR(a0, a1, b0, b1, W)                                                                      \
+    ITK_PTX_RELU(a0) ITK_PTX_RELU(a1) "mov.b64 pa, {" a0 ", " a1 "};\n\tfma.rn.f32x2 acc_a, pa, " W ", acc_a;\n\t" \
+    ITK_PTX_RELU(b0) ITK_PTX_RELU(b1) "mov.b64 pb, {" b0 ", " b1 "};\n\tfma.rn.f32x2 acc_b, pb, " W ", acc_b;\n\t"
+#define ITK_PTX_FRAGMENT                                       \
+    ITK_PTX_PAIR_FIRST("r0", "r1", "r2", "r3", "%21")          \
+    ITK_PTX_PAIR("r4", "r5", "r6", "r7", "%22")                \
+    ITK_PTX_PAIR("r8", "r9", "r10", "r11", "%23")              \
+    ITK_PTX_PAIR("r12", "r13", "r14", "r15", "%24")            \
+    ITK_PTX_PAIR("r16", "r17", "r18", "r19", "%25")            \
+    ITK_PTX_PAIR("r20", "r21", "r22", "r23", "%26")            \
+    ITK_PTX_PAIR("r24", "r25", "r26", "r27", "%27")            \
+    ITK_PTX_PAIR("r28", "r29", "r30", "r31", "%28")
+#define ITK_PTX_LOAD_FRAGMENT                                                                                  \
+    "tcgen05.ld.sync.aligned.16x256b.x8.b32 "                                                                  \
+    "{r0, r1, r2, r3, r4, r5, r6, r7, r8, r9, r10, r11, r12, r13, r14, r15, "                                  \
+    "r16, r17, r18, r19, r20, r21, r22, r23, r24, r25, r26, r27, r28, r29, r30, r31}, [taddr];\n\t"
+
+__device__ __forceinline__ uint32_t topk_tile_loop(int& t, int& acc_iter, int& key, uint16_t& id16, float& scale,
+                                                   uint32_t& score_at, uint32_t& id_at, uint32_t& full,
+                                                   float& last_score, int tile_end, uint32_t limit_at, int row_lo,
+                                                   unsigned row_span, float threshold, const float* kv_scales,
+                                                   int last_key, uint32_t tile_done_bars, uint32_t acc_empty_bars,
+                                                   uint32_t tmem_lane, int lane, const uint64_t (&w)[8]) {
+    uint32_t why;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p_odd, p_upper, p_ready, p_in, p_act, p_room, p_full, p_any, p_more, p_lead;\n\t"
+        ".reg .b32 r<32>;\n\t"
+        ".reg .b64 acc_a, acc_b, pa, pb, scale_at;\n\t"
+        ".reg .f32 lo, hi, v0, v1, v2, v3, sa, sb, ka, kb, ra, rb, kk, ss, rr, sum, nscale;\n\t"
+        ".reg .u32 stage, bar, parity, buf, taddr, abar, off, tmp;\n\t"
+        ".reg .s32 knext;\n\t"
+        "and.b32 tmp, %20, 1;\n\t"
+        "setp.ne.u32 p_odd, tmp, 0;\n\t"
+        "and.b32 tmp, %20, 2;\n\t"
+        "setp.ne.u32 p_upper, tmp, 0;\n\t"
+        "mov.u32 %8, 0;\n\t"
+        "mov.f32 %9, 0f00000000;\n\t"
+        "mov.u32 %7, 0;\n\t"
+        "setp.lt.s32 p_more, %0, %10;\n\t"
+        "@!p_more bra.uni ITK_LOOP_END;\n"
+        "ITK_LOOP:\n\t"
+        // the tile's barrier: stage = tile counter % 4, phase parity = (tile counter / 4) % 2
+        "and.b32 stage, %1, 3;\n\t"
+        "mad.lo.u32 bar, stage, 8, %17;\n\t"
+        "shr.u32 parity, %1, 2;\n\t"
+        "and.b32 parity, parity, 1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p_ready, [bar], parity, 2000;\n\t"
+        "vote.sync.all.pred p_ready, p_ready, 0xffffffff;\n\t"
+        "@!p_ready bra.uni ITK_LOOP_WAIT;\n\t"
+        "tcgen05.fence::after_thread_sync;\n\t"
+        "and.b32 buf, %1, 1;\n\t"
+        "mad.lo.u32 taddr, buf, 256, %19;\n\t"
+        ITK_PTX_LOAD_FRAGMENT
+        // the next tile's key scale (an index past the last key is clamped: such a key is outside every range)
+        "add.s32 knext, %2, 128;\n\t"
+        "min.s32 knext, knext, %16;\n\t"
+        "mad.wide.s32 scale_at, knext, 4, %15;\n\t"
+        "ld.global.nc.f32 nscale, [scale_at];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t"
+        ITK_PTX_FRAGMENT
+        "add.u32 taddr, taddr, 1048576;\n\t"   // TMEM lanes 16-31 of the quarter
+        ITK_PTX_LOAD_FRAGMENT
+        "mov.b64 {lo, hi}, acc_a;\n\t"
+        "add.f32 v0, lo, hi;\n\t"
+        "mov.b64 {lo, hi}, acc_b;\n\t"
+        "add.f32 v1, lo, hi;\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n\t"
+        // the accumulator buffer is fully read: hand it back
+        "tcgen05.fence::before_thread_sync;\n\t"
+        "mad.lo.u32 abar, buf, 8, %18;\n\t"
+        "elect.sync _|p_lead, 0xffffffff;\n\t"
+        "@p_lead mbarrier.arrive.shared::cta.b64 _, [abar];\n\t"
+        ITK_PTX_FRAGMENT
+        "mov.b64 {lo, hi}, acc_a;\n\t"
+        "add.f32 v2, lo, hi;\n\t"
+        "mov.b64 {lo, hi}, acc_b;\n\t"
+        "add.f32 v3, lo, hi;\n\t"
+        // reduce-scatter of the four partial sums over the four threads of a quad
+        "selp.f32 sa, v0, v1, p_odd;\n\t"
+        "selp.f32 sb, v2, v3, p_odd;\n\t"
+        "selp.f32 ka, v1, v0, p_odd;\n\t"
+        "selp.f32 kb, v3, v2, p_odd;\n\t"
+        "shfl.sync.bfly.b32 ra, sa, 1, 0x1f, 0xffffffff;\n\t"
+        "shfl.sync.bfly.b32 rb, sb, 1, 0x1f, 0xffffffff;\n\t"
+        "add.f32 ka, ka, ra;\n\t"
+        "add.f32 kb, kb, rb;\n\t"
+        "selp.f32 kk, kb, ka, p_upper;\n\t"
+        "selp.f32 ss, ka, kb, p_upper;\n\t"
+        "shfl.sync.bfly.b32 rr, ss, 2, 0x1f, 0xffffffff;\n\t"
+        "add.f32 sum, kk, rr;\n\t"
+        // score (the fused add of +0 turns a -0 product into +0), filter, append to the thread's list
+        "fma.rn.f32 %9, sum, %4, 0f00000000;\n\t"
+        "sub.u32 off, %2, %12;\n\t"
+        "setp.lt.u32 p_in, off, %13;\n\t"
+        "setp.ge.and.f32 p_act, %9, %14, p_in;\n\t"
+        "setp.lt.and.u32 p_room, %5, %11, p_act;\n\t"
+        "@p_room st.shared.b32 [%5], %9;\n\t"
+        "@p_room st.shared.u16 [%6], %3;\n\t"
+        "@p_room add.u32 %5, %5, 128;\n\t"
+        "@p_room add.u32 %6, %6, 64;\n\t"
+        "xor.pred p_full, p_room, p_act;\n\t"
+        "vote.sync.any.pred p_any, p_full, 0xffffffff;\n\t"
+        // next tile
+        "add.s32 %0, %0, 1;\n\t"
+        "add.s32 %1, %1, 1;\n\t"
+        "add.s32 %2, %2, 128;\n\t"
+        "add.u16 %3, %3, 32;\n\t"
+        "mov.f32 %4, nscale;\n\t"
+        "@p_any bra.uni ITK_LOOP_SPILL;\n\t"
+        "setp.lt.s32 p_more, %0, %10;\n\t"
+        "@p_more bra.uni ITK_LOOP;\n\t"
+        "bra.uni ITK_LOOP_END;\n"
+        "ITK_LOOP_WAIT:\n\t"
+        "mov.u32 %7, 1;\n\t"
+        "bra.uni ITK_LOOP_END;\n"
+        "ITK_LOOP_SPILL:\n\t"
+        "selp.u32 %8, 1, 0, p_full;\n\t"
+        "mov.u32 %7, 2;\n"
+        "ITK_LOOP_END:\n\t"
+        "}"
+        : "+r"(t), "+r"(acc_iter), "+r"(key), "+h"(id16), "+f"(scale), "+r"(score_at), "+r"(id_at), "=&r"(why),
+          "=&r"(full), "=&f"(last_score)
+        : "r"(tile_end), "r"(limit_at), "r"(row_lo), "r"(row_span), "f"(threshold), "l"(kv_scales), "r"(last_key),
+          "r"(tile_done_bars), "r"(acc_empty_bars), "r"(tmem_lane), "r"(lane), "l"(w[0]), "l"(w[1]), "l"(w[2]),
+          "l"(w[3]), "l"(w[4]), "l"(w[5]), "l"(w[6]), "l"(w[7])
+        : "memory");
+    return why;
+}
+#undef ITK_PTX_LOAD_FRAGMENT
+#undef ITK_PTX_FRAGMENT
+#undef ITK_PTX_PAIR
+#undef ITK_PTX_PAIR_FIRST
+#undef ITK_PTX_RELU
 
 // What the epilogue needs to know about one query row of a unit.
 struct RowState {
@@ -1330,7 +1479,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             }
             if (!ok) atomicOr(p.status, kStatusWaitExpired);
         }
-    } else {
+    } else if (warp >= kEpilogueWarp0) {
         // ============================================================ epilogue
         // Sixteen warps share every tile: warp (quarter, row) reads the 32 TMEM lanes (= keys) of
         // its lane quarter, which is also its candidate segment, and the 64 accumulator columns
@@ -1409,14 +1558,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             keep_in_register(row_span);
             keep_in_register(threshold);
 
-            // head weights of this thread's column pairs; a pair whose ReLUs are the saturating
-            // multiply by 2^-25 carries the factor 2^25 in its weights
+            // head weights of this thread's column pairs, times 2^25 (the ReLU is a saturating multiply
+            // by 2^-25)
             uint64_t w[8];
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
                 const float2 pair = *reinterpret_cast<const float2*>(&sh.weights[slot][own_r * kHeads + 8 * n + 2 * quad]);
-                const float lo = relu_sat(n) ? pair.x * kSatUnscale : pair.x;
-                const float hi = relu_sat(n) ? pair.y * kSatUnscale : pair.y;
+                const float lo = pair.x * kSatUnscale, hi = pair.y * kSatUnscale;
                 asm("mov.b64 %0, {%1, %2};" : "=l"(w[n]) : "f"(lo), "f"(hi));
             }
             __syncwarp();
@@ -1503,7 +1651,33 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             float scale, next_scale = 0.0f;
             int range_key = 0, next_range_key = 0;   // sample mode only
             per_key(u.tile_begin, scale, range_key);
-            for (int t = u.tile_begin; t < u.tile_end; ++t, ++acc_iter) {
+            int t = u.tile_begin;
+            if (MODE == kModeTopK && !DIAG && !PAGED) {
+                // the product path of the Top-K mode runs the tile loop in its PTX form; this C++ loop
+                // serves the diagnostic, paged, sample and repair instances (same arithmetic, same order)
+                int key = t * kTileKeys + own_key;
+                uint16_t id16 = static_cast<uint16_t>(t * 32 + (own_key & 31));
+                for (;;) {
+                    uint32_t full;
+                    float last_score;
+                    const uint32_t why = topk_tile_loop(t, acc_iter, key, id16, scale, score_at, id_at, full, last_score,
+                                                        u.tile_end, limit_at, row_lo, row_span, threshold, p.kv_scales,
+                                                        p.keys - 1, tile_done_bars, acc_empty_bars, tmem_lane, lane, w);
+                    if (why == kLoopDone) break;
+                    if (why == kLoopNeedWait) {
+                        ok = warp_tile_wait_slow<DIAG>(tile_done_bars + 8u * static_cast<uint32_t>(acc_iter % kKvStages),
+                                                       (acc_iter / kKvStages) & 1, ctl, &wait_acc);
+                        if (!ok) break;
+                    } else if (full != 0u) {
+                        const int at = atomicAdd(&sh.spill_counts[own_r][quarter], 1);
+                        if (at < kSpillSegCap)
+                            p.spill[row.slot * kSpillRow + quarter * kSpillSegCap + at] =
+                                pack_score_id(last_score, static_cast<uint32_t>(key - kTileKeys));
+                    }
+                }
+                t = u.tile_end;
+            }
+            for (; t < u.tile_end; ++t, ++acc_iter) {
                 ok = warp_tile_wait<DIAG>(tile_done_bars + 8u * static_cast<uint32_t>(acc_iter % kKvStages),
                                           (acc_iter / kKvStages) & 1, ctl, wait_acc);
                 if (!ok) break;

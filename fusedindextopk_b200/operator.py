@@ -217,6 +217,27 @@ def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
 # --------------------------------------------------------------------------- stages
 
 
+def _on_workspace_device(function):
+    """Run a stage with the workspace's device current.
+
+    The library sizes its grid, resolves its per-device state and launches on the current device, so a
+    call for tensors on cuda:1 while cuda:0 is current would use a foreign stream handle.
+    """
+
+    import functools
+
+    @functools.wraps(function)
+    def wrapper(ws, *args, **kwargs):
+        import torch
+
+        with torch.cuda.device(ws.device):
+            return function(ws, *args, **kwargs)
+
+    return wrapper
+
+
+
+@_on_workspace_device
 def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None,
                           trace=None, tile_table=None) -> Any:
     """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph."""
@@ -242,6 +263,7 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
     return ws.thresholds
 
 
+@_on_workspace_device
 def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, thresholds=None,
                    diag_logits=None, trace=None, force_compute: bool = False, max_ctas: int = 0,
                    wait_limit_ns: int = 0, withhold_loads: bool = False,
@@ -304,6 +326,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     return ws.output_ids
 
 
+@_on_workspace_device
 def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
                key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
     """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags."""
@@ -402,18 +425,25 @@ def fused_index_topk(q, kv_pair, weights, k_start, k_end, top_k: int = TOP_K, *,
     return replay_or_run(workspace, (q, kv, kv_scales, weights, k_start, k_end), use_graph=use_graph)
 
 
-def replay_or_run(workspace: Workspace, tensors, *, tile_table=None, use_graph: bool = True) -> Any:
-    """One operator call: a graph replay from the second call with the same tensor addresses on."""
+@_on_workspace_device
+def replay_or_run(workspace: Workspace, tensors, *, tile_table=None, use_graph: bool = True, prologue=None,
+                  key_extra: tuple = ()) -> Any:
+    """One operator call: a graph replay from the second call with the same tensor addresses on.
+
+    ``prologue`` (optional callable) is enqueued in front of the operator and is part of the replayed
+    graph: device-side preparation that has to be redone on every call (the paged variant expands the
+    live block table there); ``key_extra`` are the addresses it reads.
+    """
 
     import torch
 
     if use_graph and not torch.cuda.is_current_stream_capturing():
-        key = tuple(int(tensor.data_ptr()) for tensor in tensors)
+        key = tuple(int(tensor.data_ptr()) for tensor in tensors) + tuple(key_extra)
         if tile_table is not None:
             key += (int(tile_table.data_ptr()),)
         graph = workspace.graphs.get(key)
         if graph is None and key in workspace.seen_inputs and len(workspace.graphs) < 4:
-            graph = _capture_operator(workspace, tensors, tile_table)
+            graph = _capture_operator(workspace, tensors, tile_table, prologue)
             if graph is not None:
                 workspace.graphs[key] = graph
         if len(workspace.seen_inputs) < 64:
@@ -421,10 +451,12 @@ def replay_or_run(workspace: Workspace, tensors, *, tile_table=None, use_graph: 
         if graph is not None:
             graph.replay()
             return workspace.output_ids
+    if prologue is not None:
+        prologue()
     return run_operator(workspace, *tensors, tile_table=tile_table)
 
 
-def _capture_operator(workspace: Workspace, tensors, tile_table=None) -> Any:
+def _capture_operator(workspace: Workspace, tensors, tile_table=None, prologue=None) -> Any:
     """One operator call as a CUDA graph, or None when the capture fails (the caller launches directly)."""
 
     import torch
@@ -433,11 +465,29 @@ def _capture_operator(workspace: Workspace, tensors, tile_table=None) -> Any:
     try:
         torch.cuda.synchronize(workspace.device)
         with torch.cuda.graph(graph):
+            if prologue is not None:
+                prologue()
             run_operator(workspace, *tensors, tile_table=tile_table)
         return graph
-    except Exception:   # noqa: BLE001 - any capture problem falls back to direct launches
+    except _lib.ItkError:
+        raise   # an argument or launch error of the library is not a capture problem
+    except RuntimeError as error:
+        # stream capture refused (e.g. another capture is active on the device): launch directly
+        _warn_once(f"CUDA graph capture of the operator failed, launching directly: {error}")
         torch.cuda.synchronize(workspace.device)
         return None
+
+
+_WARNED: set[str] = set()
+
+
+def _warn_once(message: str) -> None:
+    import warnings
+
+    key = message.split(":")[0]
+    if key not in _WARNED:
+        _WARNED.add(key)
+        warnings.warn(message, RuntimeWarning, stacklevel=3)
 
 
 # --------------------------------------------------------------------------- host buffers
@@ -522,6 +572,11 @@ class HostPipeline:
                  and k_start.dtype == torch.int32 and k_end.dtype == torch.int32, "k_start and k_end must be int32 [Q]")
         _require(tuple(out.shape) == (self.rows, TOP_K) and out.dtype == torch.int32, "out must be int32 [Q, 2048]")
         tensors = (q, kv, kv_scales, weights, k_start, k_end, out)
+        with torch.cuda.device(self.device):
+            return self._run(tensors)
+
+    def _run(self, tensors) -> Any:
+        out = tensors[-1]
         if self.use_graph:
             key = tuple(int(tensor.data_ptr()) for tensor in tensors)
             graph = self._graphs.get(key)
@@ -547,7 +602,10 @@ class HostPipeline:
             with torch.cuda.graph(graph):
                 self._enqueue(tensors)
             return graph
-        except Exception:   # noqa: BLE001 - any capture problem falls back to the stream version
+        except _lib.ItkError:
+            raise
+        except RuntimeError as error:
+            _warn_once(f"CUDA graph capture of the host pipeline failed, using the stream version: {error}")
             self.use_graph = False
             torch.cuda.synchronize(self.device)
             return None

@@ -37,27 +37,54 @@ def expand_block_table(block_table: Any, page_size: int) -> Any:
     return (block_table.unsqueeze(1) * per_page + within.unsqueeze(0)).reshape(-1).contiguous()
 
 
-_TILE_TABLES: dict[tuple, Any] = {}
+def _tile_table_buffers(workspace: Workspace, pages_used: int, per_page: int, device: Any) -> dict[str, Any]:
+    """Workspace-owned buffers of the per-call block-table expansion (allocated once per table length)."""
+
+    import torch
+
+    key = f"paged_{pages_used}_{per_page}"
+    buffers = workspace.buffers.get(key)
+    if buffers is None:
+        buffers = {
+            "pages": torch.empty(pages_used, device=device, dtype=torch.int32),
+            "tiles": torch.empty(pages_used * per_page, device=device, dtype=torch.int32),
+            "within": torch.arange(per_page, device=device, dtype=torch.int32),
+            "bad": torch.zeros(pages_used, device=device, dtype=torch.bool),
+            "bad_any": torch.zeros(1, device=device, dtype=torch.bool),
+        }
+        workspace.buffers[key] = buffers
+    return buffers
 
 
-def _checked_tile_table(block_table: Any, page_size: int, pages: int) -> Any:
-    """Range-checked expansion, remembered while the table's storage and version stay the same.
+def _expand_on_device(buffers: dict[str, Any], block_table: Any, pages: int) -> None:
+    """Physical 128-key tiles of the block table as it is NOW, into the workspace's buffer.
 
-    The range check reads the table back to the host (one synchronisation); a serving loop that
-    reuses a block table for many calls pays it once.
+    Enqueued on every call (and part of the replayed CUDA graph), because a serving engine updates its
+    block table in place, often from its own kernels, without any host-visible version change.  An
+    entry outside the pool is clamped, so that the kernels never read outside the pool, and recorded:
+    ``block_table_was_valid`` reports it.
     """
 
-    key = (int(block_table.data_ptr()), int(block_table._version), int(block_table.numel()), page_size, pages,
-           str(block_table.device))
-    cached = _TILE_TABLES.get(key)
-    if cached is None:
-        _require(int(block_table.min()) >= 0 and int(block_table.max()) < pages,
-                 "block_table names a page outside the pool")
-        cached = expand_block_table(block_table, page_size)
-        if len(_TILE_TABLES) >= 64:
-            _TILE_TABLES.clear()
-        _TILE_TABLES[key] = cached
-    return cached
+    import torch
+
+    per_page = int(buffers["within"].numel())
+    torch.clamp(block_table, 0, pages - 1, out=buffers["pages"])
+    torch.ne(block_table, buffers["pages"], out=buffers["bad"])
+    torch.any(buffers["bad"], dim=0, keepdim=True, out=buffers["bad_any"])
+    torch.mul(buffers["pages"], per_page, out=buffers["pages"])
+    torch.add(buffers["pages"].unsqueeze(1), buffers["within"].unsqueeze(0), out=buffers["tiles"].view(-1, per_page))
+
+
+def block_table_was_valid(workspace: Workspace) -> bool:
+    """Whether every block-table entry of the paged calls made through this workspace named a pool page.
+
+    Synchronises; meant for tests and for debugging a serving integration, not for the hot path.
+    """
+
+    for name, buffers in workspace.buffers.items():
+        if name.startswith("paged_") and bool(buffers["bad_any"].item()):
+            return False
+    return True
 
 
 def scatter_to_pages(kv: Any, kv_scales: Any, page_size: int, *, pool_pages: int | None = None,
@@ -117,8 +144,8 @@ def fused_index_topk_paged(q: Any, kv_pool_pair: tuple[Any, Any], block_table: A
                          ("k_start", k_start), ("k_end", k_end), ("block_table", block_table)):
         _require(tensor.is_contiguous(), f"{name} must be contiguous")
         _require(tensor.device == q.device, f"{name} must live on the same device as q")
+    _require(block_table.dtype == torch.int32 and block_table.dim() == 1, "block_table must be int32 [pages]")
     _require(int(block_table.numel()) * page_size >= keys, "block_table does not cover the keys")
-    tile_table = _checked_tile_table(block_table, page_size, pages)
 
     if workspace is None:
         key = (rows, keys, str(q.device), int(seed))
@@ -129,8 +156,10 @@ def fused_index_topk_paged(q: Any, kv_pool_pair: tuple[Any, Any], block_table: A
     _require(workspace.rows == rows and workspace.keys == keys, "workspace was made for a different problem size")
     flat_kv = kv_pool.view(pages * page_size, _lib.HEAD_DIM)
     flat_scales = scale_pool.view(pages * page_size)
-    return replay_or_run(workspace, (q, flat_kv, flat_scales, weights, k_start, k_end), tile_table=tile_table,
-                         use_graph=use_graph)
+    buffers = _tile_table_buffers(workspace, int(block_table.numel()), page_size // TILE_KEYS, q.device)
+    return replay_or_run(workspace, (q, flat_kv, flat_scales, weights, k_start, k_end), tile_table=buffers["tiles"],
+                         use_graph=use_graph, prologue=lambda: _expand_on_device(buffers, block_table, pages),
+                         key_extra=(int(block_table.data_ptr()),))
 
 
-__all__ = ["expand_block_table", "fused_index_topk_paged", "scatter_to_pages"]
+__all__ = ["block_table_was_valid", "expand_block_table", "fused_index_topk_paged", "scatter_to_pages"]

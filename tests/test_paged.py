@@ -8,7 +8,7 @@ import math
 import pytest
 import torch
 
-from fusedindextopk_b200 import paged
+from fusedindextopk_b200 import operator, paged
 from fusedindextopk_b200.inputs import make_workload_inputs
 
 
@@ -143,6 +143,16 @@ def test_repeated_paged_calls_replay_a_graph_and_follow_a_changed_table(device):
     block_table[0], block_table[1] = b, a
     again = paged.fused_index_topk_paged(q, (pool, scale_pool), block_table, 8192, weights, k_start, k_end).clone()
     assert torch.equal(again.sort(dim=-1).values, want)
+    # ... also when the table is rewritten behind torch's back (a serving engine's own kernel): the
+    # expansion is redone on the device on every call, replayed graphs included
+    c, d = int(block_table[2]), int(block_table[3])
+    raw[[c, d]] = raw[[d, c]]
+    scale_pool[[c, d]] = scale_pool[[d, c]]
+    alias = torch.as_strided(block_table.detach(), block_table.shape, block_table.stride())
+    alias.data[2], alias.data[3] = d, c
+    for _ in range(3):
+        again = paged.fused_index_topk_paged(q, (pool, scale_pool), block_table, 8192, weights, k_start, k_end).clone()
+        assert torch.equal(again.sort(dim=-1).values, want)
 
 
 @pytest.mark.gpu
@@ -153,10 +163,14 @@ def test_paged_argument_errors(device):
     pool, scale_pool, block_table = paged.scatter_to_pages(kv, scales, 256, generator=torch.Generator().manual_seed(4))
     with pytest.raises(ValueError, match="does not cover"):
         paged.fused_index_topk_paged(q, (pool, scale_pool), block_table[:-1].contiguous(), 2048, weights, k_start, k_end)
+    # a page outside the pool is clamped on the device (nothing is read outside the pool) and recorded
     bad = block_table.clone()
     bad[0] = pool.shape[0]
-    with pytest.raises(ValueError, match="outside the pool"):
-        paged.fused_index_topk_paged(q, (pool, scale_pool), bad, 2048, weights, k_start, k_end)
+    workspace = operator.make_workspace(8, 2048, device)
+    paged.fused_index_topk_paged(q, (pool, scale_pool), bad, 2048, weights, k_start, k_end, workspace=workspace)
+    assert not paged.block_table_was_valid(workspace)
+    paged.fused_index_topk_paged(q, (pool, scale_pool), block_table, 2048, weights, k_start, k_end, workspace=workspace)
+    assert paged.block_table_was_valid(workspace)
     with pytest.raises(ValueError, match="multiple of 128"):
         paged.fused_index_topk_paged(q, (pool.view(-1, 64, 128), scale_pool.view(-1, 64)), block_table, 2048,
                                      weights, k_start, k_end)
