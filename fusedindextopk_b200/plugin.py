@@ -240,7 +240,6 @@ class FusedIndexTopK:
                 "repair_merge": "online-exact-top2048-pairs",
                 "spill_workspace_bytes": sizes.spill_bytes,
                 "same_kernel_exact_topk": True,
-                "workspace": ws,
                 "resources": _lib.resource_report() if torch.cuda.is_available() else {},
             },
         )

@@ -9,8 +9,9 @@ available on B200 boxes without its JIT.  This variant has the same graph shape
 the scores written by the fused kernel's diagnostic output (every in-range key,
 ``-inf`` outside ``[k_start,k_end)``) and the selection left to ``torch.topk``.
 
-It is a harness component (what ``lifecycle.CaseLifecycle`` builds its oracle
-from), not an operator path: nothing in ``operator.py`` or ``plugin.py`` uses it,
+It is a harness component (what the reference's ``CaseLifecycle`` builds its
+oracle from when this package is checked under the reference harness,
+``src/fused_index_topk/lifecycle.py:240-291``), not an operator path: nothing in ``operator.py`` or ``plugin.py`` uses it,
 it allocates 4*Q*N bytes, and it exists to give an independent selection over
 identical fp32 scores.
 """
@@ -123,7 +124,7 @@ class DenseScoresTorchTopK:
             descriptor=self.descriptor, nodes=nodes, initial_artifacts={"inputs": inputs},
             terminal_artifact="indices",
             metadata={"algorithm": "dense-logits-torch-topk", "dense_logits_materialized": True,
-                      "logits_bytes": int(logits.numel()) * 4, "workspace": ws},
+                      "logits_bytes": int(logits.numel()) * 4},
         )
 
 
