@@ -124,6 +124,8 @@ def test_fused_scores_and_topk_against_oracle(device, workload, rows, keys):
     score_threshold_check(indices, logits.cpu(), case)          # (ii) bit-exact on own scores
     report = tolerance_set_report(indices, want, case, relative_tolerance=RELATIVE_TOLERANCE)  # (iii)
     assert report["status"] == "passed"
+    print(f"\nPARITY {workload} Q={rows} N={keys}: rows_with_set_difference {report['rows_with_set_difference']}, "
+          f"ids_swapped_within_tolerance {report['ids_swapped_within_tolerance']}")
 
 
 @pytest.mark.parametrize("threshold", [-math.inf, math.inf])
@@ -342,22 +344,34 @@ def test_invalid_arguments_raise(device):
     assert ws.status.item() == 0
 
 
+ORACLE_ROWS = 128   # evenly spaced query rows compared with the float64 oracle at full size
+
+
 @pytest.mark.parametrize(
     "workload,rows,keys",
-    [("c1", 4096, 16384), ("c2", 256, 65536), ("c3", 64, 163840), ("c3s", 64, 131072), ("c4", 512, 32768)],
+    [("c1", 4096, 16384), ("c2", 4096, 65536), ("c3", 4096, 163840), ("c3s", 64, 131072), ("c4", 512, 32768)],
 )
-def test_full_size_properties(device, workload, rows, keys):
-    """Benchmark-sized cases: the result is a bit-exact Top-K of the kernel's own dense
-    scores (tie rule), satisfies the output contract and leaves no row flagged."""
+def test_full_size_parity(device, workload, rows, keys):
+    """The benchmark configurations at their full size, all three levels.
+
+    (ii) on the device over every row: the result is a bit-exact Top-K of the kernel's own dense
+    scores (tie rule), satisfies the output contract and leaves no row flagged; the production build
+    (no dense output) returns the same sets where scores are distinct.  (i) and (iii) against the
+    float64 oracle on 128 evenly spaced rows: scores within 1e-3 of the row maximum, set differences
+    only inside the tolerance window of the oracle's 2048th value, counted and printed.
+    """
 
     host = make_workload_inputs(workload, query_tokens=rows, context_tokens=keys)
     case = PrefillCase("full", rows, keys, 2048, 0)
     ws, logits, fast_flags = _run_with_diagnostics(host, device)
     assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    if workload == "c3":
+        # at 160 K keys the sampled threshold starves about one row in a thousand: the fast path must
+        # flag it and the exact repair must complete it
+        assert int(fast_flags.sum()) >= 1, "expected the fast path to flag at least one row at this size"
     indices = ws.output_ids.unsqueeze(1).contiguous()
     validate_topk_indices(indices, case)
-    score_threshold_check(indices, logits, case)
-    # the production build (no dense output) returns the same sets where scores are distinct
+    own = score_threshold_check(indices, logits, case)
     gpu = inputs_to(host, device)
     first = indices.clone()
     operator.run_operator(ws, *_tensors(gpu))
@@ -368,3 +382,15 @@ def test_full_size_properties(device, workload, rows, keys):
     score_threshold_check(again, logits, case)
     if workload != "c4":
         assert torch.equal(first.sort(dim=-1).values, again.sort(dim=-1).values)
+
+    sample = torch.linspace(0, rows - 1, min(rows, ORACLE_ROWS)).round().long().unique()
+    want = oracle.dense_logits(host.q[sample], host.kv, host.kv_scales, host.weights[sample], host.k_start[sample],
+                               host.k_end[sample])
+    worst = _assert_close_to_oracle(logits[sample.to(device)].cpu(), want)
+    report = tolerance_set_report(again[sample.to(device)].cpu(), want, case, relative_tolerance=RELATIVE_TOLERANCE,
+                                  rows=sample)
+    assert report["status"] == "passed" and report["rows_checked"] > 0
+    print(f"\nPARITY {workload} Q={rows} N={keys}: fast-path flags {int(fast_flags.sum())}, rows with cutoff ties "
+          f"{own['rows_with_cutoff_ties']}/{own['rows_checked']}; vs oracle on {int(sample.numel())} rows: score error "
+          f"{worst:.2e} of row max, rows_with_set_difference {report['rows_with_set_difference']}, "
+          f"ids_swapped_within_tolerance {report['ids_swapped_within_tolerance']}")
