@@ -13,6 +13,10 @@ then costs the slowest rank's time ("strong" scaling).  For the short-Q workload
 c3s the key range is sharded instead, and the step includes the NCCL all-gather of
 the per-rank Top-2048 candidates and the merge.
 
+Steps alternate between two fixtures of the same shape and different content (A, B), as the
+reference's benchmark does (src/fused_index_topk/benchmark.py:384-386); the line carries the mean
+(`value`) and the median, 95th percentile, minimum and maximum of the K per-step times.
+
 Rank 0 prints ONE JSON line.  `value` is microseconds per call of the public callable
 `fused_index_topk` with inputs resident in HBM (CUDA events around every call, summed
 over the K timed steps, max over ranks; the callable replays one CUDA graph from its
@@ -149,8 +153,12 @@ class ClockSampler:
         }
 
 
-def cpu_reference_time(host, sample_rows: int, threads: int) -> dict:
-    """Time the CPU restatement (dense fp32 scores + torch.topk) on evenly spaced rows."""
+def cpu_reference_time(host, sample_rows: int, threads: int, *, keep_scores: bool = False) -> dict:
+    """Time the CPU restatement (dense fp32 scores + torch.topk) on evenly spaced rows.
+
+    All rows are timed when ``sample_rows`` covers them; otherwise the time of the sample is scaled
+    to the whole call and the record says so (``extrapolated``, ``rows_timed``).
+    """
 
     import torch
 
@@ -168,12 +176,56 @@ def cpu_reference_time(host, sample_rows: int, threads: int) -> dict:
     oracle.reference_topk_indices(logits, k_end)
     elapsed = time.perf_counter() - begin
     per_row = elapsed / picked.numel()
-    return {
+    whole = int(picked.numel()) == rows
+    record = {
         "value": per_row * rows * 1e6, "unit": UNIT, "cores": threads, "kind": "port",
-        "sample": f"{picked.numel()} evenly spaced query rows of {rows}, {elapsed:.2f} s of CPU work, "
-                  f"extrapolated per row x Q (torch dense fp32 scores + torch.topk, the reference's exact path)",
+        "extrapolated": not whole, "rows_timed": int(picked.numel()),
+        "sample": (f"all {rows} query rows" if whole else f"{picked.numel()} evenly spaced query rows of {rows}, "
+                   "scaled per row to the whole call") +
+                  f", {elapsed:.2f} s of CPU work (torch dense fp32 scores + torch.topk, the reference's exact path)",
         "seconds": elapsed,
     }
+    if keep_scores:
+        record["_rows"], record["_scores"] = picked, logits
+    return record
+
+
+def pinned_copy_bandwidth(device, megabytes: int = 64) -> tuple[float, float]:
+    """GB/s of a pinned host -> device copy and of a device -> host copy running at the same time."""
+
+    import torch
+
+    count = megabytes << 20
+    host_in = torch.empty(count, dtype=torch.uint8).pin_memory()
+    host_out = torch.empty(count, dtype=torch.uint8).pin_memory()
+    dev_in = torch.empty(count, dtype=torch.uint8, device=device)
+    dev_out = torch.empty(count, dtype=torch.uint8, device=device)
+    up, down = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    best = [0.0, 0.0]
+    for _ in range(4):
+        torch.cuda.synchronize(device)
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        with torch.cuda.stream(up):
+            events[0].record()
+            dev_in.copy_(host_in, non_blocking=True)
+            events[1].record()
+        with torch.cuda.stream(down):
+            events[2].record()
+            host_out.copy_(dev_out, non_blocking=True)
+            events[3].record()
+        torch.cuda.synchronize(device)
+        best[0] = max(best[0], count / (events[0].elapsed_time(events[1]) * 1e-3) / 1e9)
+        best[1] = max(best[1], count / (events[2].elapsed_time(events[3]) * 1e-3) / 1e9)
+    return best[0], best[1]
+
+
+def spread(samples_ms: list) -> dict:
+    """Median and 95th percentile of per-step times, in microseconds."""
+
+    ordered = sorted(samples_ms)
+    p95 = ordered[min(len(ordered) - 1, max(0, math.ceil(0.95 * len(ordered)) - 1))]
+    return {"median_us": statistics.median(ordered) * 1e3, "p95_us": p95 * 1e3,
+            "min_us": ordered[0] * 1e3, "max_us": ordered[-1] * 1e3}
 
 
 def hbm_peak_gbs() -> tuple[float, str]:
@@ -310,7 +362,11 @@ def main() -> None:
         if rank != 0:
             return
         host = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys)
-        rows_per_step = max(8, min(args.cpu_sample_rows, host.case.query_tokens) // 2)
+        # every step times the whole call while that stays near three seconds (c0, c1, c4); the long
+        # contexts time a row sample per step and say so
+        rows_per_step = min(args.cpu_sample_rows, host.case.query_tokens)
+        if host.case.query_tokens * host.case.context_tokens > 4096 * 16384:
+            rows_per_step = max(8, (4096 * 16384) // host.case.context_tokens)
         for _ in range(min(args.warmup, 1)):
             cpu_reference_time(host, 8, threads)
         values = [cpu_reference_time(host, rows_per_step, threads) for _ in range(args.steps)]
@@ -319,7 +375,11 @@ def main() -> None:
             "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": value / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "extrapolated": values[0]["extrapolated"], "rows_timed": values[0]["rows_timed"],
+            "seconds_per_step": statistics.mean(item["seconds"] for item in values),
+            **spread([item["value"] / 1e3 for item in values]),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "extrapolated": values[0]["extrapolated"], "rows_timed": values[0]["rows_timed"],
                              "sample": f"each step: {values[0]['sample']}"},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "queries_per_s": host.case.query_tokens / (value * 1e-6),
@@ -339,32 +399,35 @@ def main() -> None:
 
         dist.init_process_group("nccl", device_id=device)
 
-    from fusedindextopk_b200 import operator
-
     from fusedindextopk_b200 import distributed as shards
+    from fusedindextopk_b200 import fused_index_topk, operator
 
     host_full = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys)
+    host_full_b = make_workload_inputs(workload, query_tokens=args.rows, context_tokens=args.keys, fixture_id="B")
     key_mode = args.workload == "c3s" and world > 1
     key_offset = 0
     if key_mode:
         # short-Q long-context: shard the key range, all-gather the per-rank Top-2048 pairs, merge
         host, key_offset = shards.shard_keys(host_full, rank, world)
+        host_b, _ = shards.shard_keys(host_full_b, rank, world)
         config["partitioning"] = (f"key range cut into {world} slices of whole 128-key tiles, per-rank exact "
                                   "Top-2048 pairs all-gathered over NCCL and merged on every rank")
     else:
         host, _ = shard_rows(host_full, rank, world)
+        host_b, _ = shard_rows(host_full_b, rank, world)
+    config["fixtures"] = "two fixtures of the same shape and different content (A, B) alternate from step to step"
     rows, keys = host.case.query_tokens, host.case.context_tokens
     gpu = inputs_to(host, device)
+    gpu_b = inputs_to(host_b, device)
     tensors = (gpu.q, gpu.kv, gpu.kv_scales, gpu.weights, gpu.k_start, gpu.k_end)
+    tensors_b = (gpu_b.q, gpu_b.kv, gpu_b.kv_scales, gpu_b.weights, gpu_b.k_start, gpu_b.k_end)
     ws = operator.make_workspace(rows, keys, device, seed=host.case.seed, with_pairs=key_mode)
     merged_ids = torch.empty((rows, 2048), dtype=torch.int32, device=device) if key_mode else None
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     chunks = (keys + 16383) // 16384
-    if ws.repair_pairs.dim() == 3:
-        # all chunks of the flagged rows in one producer launch, one local Top-K launch, merges of up to 8 lists
-        repair_launches = 1 + 1 + 1 + (1 if chunks <= 8 else 1 + math.ceil((chunks - 8) / 7)) + 1
-    else:
-        repair_launches = 1 + 3 * chunks + 1
+    # the retry of flagged rows (compaction, thresholds, fused kernel, merge) and the dense rescan
+    # (a producer and a merge launch per 16384-key chunk); all of them return at once when no row is flagged
+    repair_launches = (4 if ws.retry is not None else 0) + 2 * chunks
     launches_per_step = ((2 if ws.plan.enabled else 0) + 1 + repair_launches + (1 if key_mode else 0)
                          + (1 if "shard_pairs" in ws.buffers else 0))   # the merge of intra-GPU key shards
 
@@ -373,55 +436,60 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if not key_mode:
+        # set-up, not warm-up: the public callable captures its CUDA graph on the second call with the
+        # same tensors, so both fixtures are called twice here and every warm-up and timed step is a replay
+        for t in (tensors, tensors_b, tensors, tensors_b):
+            fused_index_topk(t[0], (t[1], t[2]), t[3], t[4], t[5], workspace=ws)
+        torch.cuda.synchronize()
+
     def timed_calls(count: int):
         """The step as a user makes it (the public callable, which replays one CUDA graph from its
         second call on), then the fused launch alone, timed in a pass of its own for the roofline."""
 
         from fusedindextopk_b200 import fused_index_topk
 
-        total_ms, fused_ms = 0.0, 0.0
         events = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(count)]
-        for ev in events:
+        for step, ev in enumerate(events):
+            t = tensors if step % 2 == 0 else tensors_b
             flush.fill_(1)
             ev[0].record()
-            fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end, workspace=ws)
+            fused_index_topk(t[0], (t[1], t[2]), t[3], t[4], t[5], workspace=ws)
             ev[1].record()
         torch.cuda.synchronize()
-        total_ms = sum(ev[0].elapsed_time(ev[1]) for ev in events)
-        for ev in events:
+        step_ms = [ev[0].elapsed_time(ev[1]) for ev in events]
+        for step, ev in enumerate(events):
+            t = tensors if step % 2 == 0 else tensors_b
             flush.fill_(1)
-            operator.run_sample_thresholds(ws, *tensors)
+            operator.run_sample_thresholds(ws, *t)
             ev[0].record()
-            operator.run_fused_topk(ws, *tensors)
+            operator.run_fused_topk(ws, *t)
             ev[1].record()
-            operator.run_repair(ws, *tensors)
+            operator.run_repair(ws, *t)
         torch.cuda.synchronize()
-        fused_ms = sum(ev[0].elapsed_time(ev[1]) for ev in events)
-        return total_ms, fused_ms
+        fused_step_ms = [ev[0].elapsed_time(ev[1]) for ev in events]
+        return step_ms, fused_step_ms
 
     def timed_steps(count: int):
         if not key_mode:
             return timed_calls(count)
-        total_ms, fused_ms = 0.0, 0.0
         events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(count)]
-        for ev in events:
+        for step, ev in enumerate(events):
+            t = tensors if step % 2 == 0 else tensors_b
             flush.fill_(1)
             ev[0].record()
-            operator.run_sample_thresholds(ws, *tensors)
+            operator.run_sample_thresholds(ws, *t)
             ev[1].record()
-            operator.run_fused_topk(ws, *tensors, want_pairs=key_mode)
+            operator.run_fused_topk(ws, *t, want_pairs=key_mode)
             ev[2].record()
-            operator.run_repair(ws, *tensors, want_pairs=key_mode)
+            operator.run_repair(ws, *t, want_pairs=key_mode)
             if key_mode:
                 gathered_pairs = shards.dist_all_gather(ws.output_pairs + key_offset)
                 gathered_counts = shards.dist_all_gather(ws.output_counts)
                 shards.gpu_merge(gathered_pairs, gathered_counts, merged_ids)
             ev[3].record()
         torch.cuda.synchronize()
-        for ev in events:
-            total_ms += ev[0].elapsed_time(ev[3])
-            fused_ms += ev[1].elapsed_time(ev[2])
-        return total_ms, fused_ms
+        return [ev[0].elapsed_time(ev[3]) for ev in events], [ev[1].elapsed_time(ev[2]) for ev in events]
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -432,11 +500,15 @@ def main() -> None:
     ws.check_status()
     barrier()
     mark_begin = sampler.mark()
-    total_ms, fused_ms = timed_steps(args.steps)
+    step_ms, fused_step_ms = timed_steps(args.steps)
     barrier()
     mark_end = sampler.mark()
     ws.check_status()
     unrepaired = int(ws.failure_flags.sum().item())
+    total_ms, fused_ms = sum(step_ms), sum(fused_step_ms)
+    # the ids of the last timed call (fixture A when the step count is odd, else B), for the parity count below
+    last_is_a = (args.steps - 1) % 2 == 0
+    last_ids = ws.output_ids.clone() if not key_mode else None
 
     # ------------------------------------------------------------------ end to end from pinned host memory
     e2e_ms = 0.0
@@ -446,30 +518,34 @@ def main() -> None:
     if not args.no_e2e:
         from fusedindextopk_b200.operator import HostPipeline
 
-        pinned = {name: getattr(host, name).contiguous().pin_memory()
-                  for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")}
+        names = ("q", "kv", "kv_scales", "weights", "k_start", "k_end")
+        pinned = {name: getattr(host, name).contiguous().pin_memory() for name in names}
+        pinned_b = {name: getattr(host_b, name).contiguous().pin_memory() for name in names}
         out_host = torch.empty((rows, 2048), dtype=torch.int32).pin_memory()
         h2d_bytes = sum(t.numel() * t.element_size() for t in pinned.values())
         d2h_bytes = out_host.numel() * out_host.element_size()
         # the package's host-buffer entry: row chunks over three streams (copies in, kernels, ids out)
         pipeline = HostPipeline(rows, keys, device, seed=host.case.seed, chunk_units=args.e2e_chunk_units)
 
-        def e2e_step():
-            pipeline(pinned["q"], (pinned["kv"], pinned["kv_scales"]), pinned["weights"], pinned["k_start"],
-                     pinned["k_end"], out_host)
+        def e2e_step(step: int):
+            src = pinned if step % 2 == 0 else pinned_b
+            pipeline(src["q"], (src["kv"], src["kv_scales"]), src["weights"], src["k_start"], src["k_end"], out_host)
 
-        for _ in range(3):
-            e2e_step()
+        for step in range(4):
+            e2e_step(step)
         barrier()
-        for _ in range(args.steps):
+        e2e_step_ms = []
+        for step in range(args.steps):
             flush.fill_(1)
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
-            e2e_step()
+            e2e_step(step)
             end.record()
             end.synchronize()
-            e2e_ms += begin.elapsed_time(end)
+            e2e_step_ms.append(begin.elapsed_time(end))
+        e2e_ms = sum(e2e_step_ms)
         pipeline.check_status()
+        up_gbs, down_gbs = pinned_copy_bandwidth(device)
         barrier()
 
     clocks = sampler.stop(mark_begin, mark_end) if rank == 0 else None
@@ -497,7 +573,9 @@ def main() -> None:
         "queries_per_s": total_rows / (us_per_call * 1e-6),
         "algorithmic_tflops": flops_total / (us_per_call * 1e-6) / 1e12,
         "fraction_of_fp8_peak_end_to_end": flops_total / (us_per_call * 1e-6) / 1e12 / (peak * args.gpus),
+        **spread(step_ms),
         "fused_kernel_us": fused_us,
+        "fused_kernel": spread(fused_step_ms),
         "unrepaired_rows": unrepaired,
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {
@@ -511,18 +589,37 @@ def main() -> None:
     }
     if not args.no_e2e:
         e2e_us = e2e_ms * 1e3 / args.steps
-        line["e2e"] = {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes}
+        # what the copies alone cost on this box: the link is full duplex, so the longer direction bounds a call
+        floor_us = max(h2d_bytes / (up_gbs * 1e9), d2h_bytes / (down_gbs * 1e9)) * 1e6
+        line["e2e"] = {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                       **spread(e2e_step_ms), "pcie_floor_us": floor_us,
+                       "pinned_copy_gbs": {"h2d": up_gbs, "d2h": down_gbs,
+                                           "how": "64 MiB pinned copies in both directions at once, best of 4"}}
     if not args.no_cpu_baseline and args.gpus == 1:
         # about ten seconds of CPU work: repeat the sample and report the mean
         passes, spent = [], 0.0
+        reference_host = host_full if last_is_a else host_full_b
+        sample_rows = args.cpu_sample_rows
+        if reference_host.case.query_tokens * reference_host.case.context_tokens > 4096 * 16384:
+            sample_rows = min(sample_rows, max(8, (4096 * 16384) // reference_host.case.context_tokens))
         while spent < 10.0 and len(passes) < 8:
-            passes.append(cpu_reference_time(host_full, args.cpu_sample_rows, threads))
+            passes.append(cpu_reference_time(reference_host, sample_rows, threads, keep_scores=not passes))
             spent += passes[-1]["seconds"]
         baseline = passes[0]
         baseline["value"] = statistics.mean(item["value"] for item in passes)
         baseline["sample"] += f"; mean of {len(passes)} passes, {spent:.1f} s of CPU work in all"
         baseline.pop("seconds", None)
+        picked, cpu_scores = baseline.pop("_rows"), baseline.pop("_scores")
         line["cpu_baseline"] = baseline
+        if last_ids is not None:
+            # the ids of the last timed call against the CPU path's fp32 scores of the same fixture and rows:
+            # differences only among keys within 1e-3 of the row maximum around the 2048th value, counted
+            from fusedindextopk_b200.correctness import tolerance_set_report
+
+            report = tolerance_set_report(last_ids[picked.to(device)].unsqueeze(1).cpu(), cpu_scores, reference_host.case,
+                                          relative_tolerance=1e-3, rows=picked)
+            line["parity"] = {"against": "CPU port (fp32 dense scores + torch.topk) on the rows it timed",
+                              "fixture": "A" if last_is_a else "B", **report}
     print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()

@@ -24,7 +24,8 @@ BLOCK_Q = 4
 REPAIR_CHUNK = 16384
 SPILL_U64_PER_ROW = 5632
 MAX_KEYS = 262144
-MAX_PAIR_SOURCES = 8
+MAX_PAIR_SOURCES = 16
+MAX_CTAS = 256
 STATIC_MAX_ROWS = 256
 STATUS_WAIT_EXPIRED = 1
 
@@ -34,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
     "itk_merge_candidate_lists", "itk_fused_topk_static", "itk_quantize_rows_e4m3",
     "itk_gather_sampled_kv_paged", "itk_repair_produce_paged", "itk_merge_shard_lists",
-    "itk_repair_produce_all", "itk_chunk_local_topk_all", "itk_merge_local_lists",
+    "itk_compact_flagged_rows", "itk_repair_merge_chunk",
 )
 
 
@@ -61,6 +62,7 @@ class FusedArgs(ctypes.Structure):
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
         ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
         ("force_compute", c_int), ("max_ctas", c_int), ("thresholds_per_row", c_int),
+        ("exit_when_no_keys", c_int),
         ("tile_table", c_void_p), ("physical_keys", c_int),
     ]
 
@@ -87,7 +89,7 @@ def load_library() -> ctypes.CDLL:
     library.itk_workspace_bytes.argtypes = [c_int, c_int, c_int, POINTER(WorkspaceSizes)]
     library.itk_gather_sampled_kv.argtypes = [c_void_p] * 5 + [c_int, c_int, c_void_p]
     library.itk_sample_thresholds.argtypes = (
-        [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]
+        [c_void_p] * 8 + [c_int] * 8 + [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p]
     )
     library.itk_fused_topk.argtypes = [POINTER(FusedArgs), c_void_p]
     library.itk_fused_topk_static.argtypes = [POINTER(FusedArgs), c_void_p]
@@ -101,11 +103,12 @@ def load_library() -> ctypes.CDLL:
     )
     library.itk_merge_shard_lists.argtypes = (
         [POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int]
-        + [c_void_p] * 4 + [c_int, c_int, c_void_p]
+        + [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]
     )
-    library.itk_repair_produce_all.argtypes = [c_void_p] * 8 + [c_int] * 5 + [c_void_p, c_int, c_void_p, c_void_p]
-    library.itk_chunk_local_topk_all.argtypes = [c_void_p] * 7 + [c_int, c_int, c_void_p]
-    library.itk_merge_local_lists.argtypes = [c_void_p, c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_void_p]
+    library.itk_compact_flagged_rows.argtypes = [c_void_p] * 5 + [c_int, c_int] + [c_void_p] * 6
+    library.itk_repair_merge_chunk.argtypes = (
+        [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 4
+    )
     library.itk_gather_sampled_kv_paged.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p]
     library.itk_repair_produce_paged.argtypes = [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_int, c_void_p, c_void_p]
     library.itk_quantize_rows_e4m3.argtypes = [c_void_p, c_int] + [c_void_p] * 4 + [c_longlong, c_void_p]

@@ -128,6 +128,7 @@ int fused_grid(int device, long long units, int max_ctas) {
     long long grid = g_sm_count[device];
     if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
     if (units < grid) grid = units;
+    if (grid > ITK_MAX_CTAS) grid = ITK_MAX_CTAS;   // the spill workspace has one region per CTA and unit row
     return static_cast<int>(grid < 1 ? 1 : grid);
 }
 
@@ -209,7 +210,11 @@ int itk_workspace_bytes(int rows, int keys, int shards, itk_workspace_sizes* siz
     ITK_REQUIRE(rows > 0 && keys > 0 && shards >= 1 && shards <= ITK_MAX_PAIR_SOURCES,
                 "need rows > 0, keys > 0 and 1 <= shards <= %d", ITK_MAX_PAIR_SOURCES);
     const size_t slots = static_cast<size_t>(rows) * shards;
-    sizes->spill_bytes = slots * kSpillRow * sizeof(uint64_t);
+    // the spill is addressed by CTA and row of the CTA's current unit: 4 regions per CTA, never more CTAs than units
+    const size_t unit_rows = static_cast<size_t>((rows + kBlockQ - 1) / kBlockQ) * shards * kBlockQ;
+    const size_t spill_rows = unit_rows < static_cast<size_t>(ITK_MAX_CTAS) * kBlockQ ? unit_rows
+                                                                                      : static_cast<size_t>(ITK_MAX_CTAS) * kBlockQ;
+    sizes->spill_bytes = spill_rows * kSpillRow * sizeof(uint64_t);
     sizes->repair_pairs_bytes = slots * kRepairChunk * sizeof(uint64_t);
     sizes->pairs_bytes = slots * kTopK * sizeof(uint64_t);
     sizes->counts_bytes = slots * sizeof(int32_t);
@@ -265,6 +270,7 @@ int itk_quantize_rows_e4m3(const void* source, int source_dtype, const float* fo
 int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,
                           const int32_t* sample_ids, const int32_t* k_start, const int32_t* k_end,
                           float* thresholds, int rows, int samples, int sample_rank, int target_candidates,
+                          int block_begin, int block_stride, int num_blocks, int exit_when_no_keys,
                           float* diag_logits, long long diag_stride, long long* trace, int* status,
                           itk_stream_t stream) {
     ITK_REQUIRE(q && sampled_kv && sampled_scales && weights && sample_ids && k_start && k_end && thresholds && status,
@@ -276,6 +282,11 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
     ITK_REQUIRE(target_candidates > 0, "target_candidates must be positive");
     ITK_REQUIRE(aligned16(q) && aligned16(sampled_kv) && aligned16(weights), "q, sampled_kv, weights must be 16-byte aligned");
     ITK_REQUIRE(diag_logits == nullptr || diag_stride >= samples, "diag_stride must cover the samples");
+    const int sample_blocks = (rows + kBlockQ - 1) / kBlockQ;
+    ITK_REQUIRE(block_stride >= 1 && block_begin >= 0 && num_blocks >= 0 &&
+                    (num_blocks == 0 || block_begin + static_cast<long long>(num_blocks - 1) * block_stride < sample_blocks),
+                "owned query blocks must lie inside the %d blocks of the problem", sample_blocks);
+    if (num_blocks == 0) return ITK_OK;
     int device = 0;
     int rc = init_current_device(&device);
     if (rc != ITK_OK) return rc;
@@ -298,13 +309,14 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
     params.key_hi = samples;
     params.shard_keys = (samples + kTileKeys - 1) / kTileKeys * kTileKeys;
     params.shards = 1;
-    params.block_begin = 0;
-    params.block_stride = 1;
-    params.num_blocks = (rows + kBlockQ - 1) / kBlockQ;
+    params.block_begin = block_begin;
+    params.block_stride = block_stride;
+    params.num_blocks = num_blocks;
     params.sample_rank = sample_rank;
     params.target_candidates = target_candidates;
     params.top_k_min_valid = kTopK;
     params.wait_limit_ns = kWaitLimitNs;
+    params.exit_when_no_keys = exit_when_no_keys != 0 ? 1 : 0;
     return launch_fused<kModeSample>(params, diag_logits != nullptr || trace != nullptr,
                                      fused_grid(device, params.num_blocks, 0), stream);
 }
@@ -369,6 +381,7 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.num_blocks = a.num_blocks;
     params.top_k_min_valid = a.force_compute ? 0 : kTopK;
     params.row_thresholds = a.thresholds_per_row != 0 ? 1 : 0;
+    params.exit_when_no_keys = a.exit_when_no_keys != 0 ? 1 : 0;
     const long long units = static_cast<long long>(a.num_blocks) * a.shards;
     return launch_fused<kModeTopK>(params, a.diag_logits != nullptr || a.trace != nullptr,
                                    fused_grid(device, units, a.max_ctas), stream);
@@ -441,53 +454,6 @@ int itk_repair_produce_paged(const void* q, const void* kv, const float* kv_scal
     return launch_fused<kModeRepair>(params, false, fused_grid(device, num_blocks, 0), stream);
 }
 
-int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales, const float* weights,
-                           const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
-                           uint64_t* repair_pairs, int rows, int keys, int block_begin, int block_stride,
-                           int num_blocks, const int32_t* tile_table, int physical_keys, int* status,
-                           itk_stream_t stream) {
-    ITK_REQUIRE(q && kv && kv_scales && weights && k_start && k_end && failure_flags && repair_pairs && status,
-                "repair producer pointers must not be null");
-    ITK_REQUIRE(rows > 0 && keys > 0 && keys <= ITK_MAX_KEYS, "need rows > 0 and 0 < keys <= %d", ITK_MAX_KEYS);
-    ITK_REQUIRE(tile_table == nullptr || (physical_keys >= kTileKeys && physical_keys % kTileKeys == 0),
-                "physical_keys must be a positive multiple of 128");
-    const int total_blocks = (rows + kBlockQ - 1) / kBlockQ;
-    ITK_REQUIRE(block_stride >= 1 && block_begin >= 0 && num_blocks >= 0 &&
-                    (num_blocks == 0 || block_begin + static_cast<long long>(num_blocks - 1) * block_stride < total_blocks),
-                "owned query blocks must lie inside the %d blocks of the problem", total_blocks);
-    ITK_REQUIRE(aligned16(q) && aligned16(kv) && aligned16(weights), "q, kv, weights must be 16-byte aligned");
-    if (num_blocks == 0) return ITK_OK;
-    int device = 0;
-    int rc = init_current_device(&device);
-    if (rc != ITK_OK) return rc;
-    const int chunks = (keys + kRepairChunk - 1) / kRepairChunk;
-    FusedParams params{};
-    if ((rc = make_row_map(&params.map_q, q, static_cast<long long>(rows) * kHeads, kUmmaN)) != ITK_OK) return rc;
-    if ((rc = make_row_map(&params.map_kv, kv, tile_table != nullptr ? physical_keys : keys, kTileKeys)) != ITK_OK) return rc;
-    params.kv_scales = kv_scales;
-    params.tile_table = tile_table;
-    params.weights = weights;
-    params.k_start = k_start;
-    params.k_end = k_end;
-    params.failure_flags = const_cast<uint8_t*>(failure_flags);
-    params.repair_pairs = repair_pairs;
-    params.status = status;
-    params.rows = rows;
-    params.keys = keys;
-    params.key_lo = 0;
-    params.key_hi = keys;
-    params.shard_keys = kRepairChunk;
-    params.shards = chunks;          // one work unit per (query block, chunk)
-    params.flags_per_row = 1;
-    params.block_begin = block_begin;
-    params.block_stride = block_stride;
-    params.num_blocks = num_blocks;
-    params.top_k_min_valid = kTopK;
-    params.wait_limit_ns = kWaitLimitNs;
-    return launch_fused<kModeRepair>(params, false, fused_grid(device, static_cast<long long>(num_blocks) * chunks, 0),
-                                     stream);
-}
-
 int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_start, const int32_t* chunk_end,
                          const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
                          uint8_t* repair_error_flags, int rows, int first_chunk, itk_stream_t stream) {
@@ -499,9 +465,8 @@ int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_star
     const int rc = init_current_device(&device);
     if (rc != ITK_OK) return rc;
     PairTopKParams params{};
-    params.sources[0] = PairSource{repair_pairs, nullptr};
+    params.sources[0] = PairSource{repair_pairs, nullptr, kRepairChunk};
     params.num_sources = 1;
-    params.capacity = kRepairChunk;
     params.rows = rows;
     params.row_mask = failure_flags;
     params.error_flags = repair_error_flags;
@@ -516,75 +481,6 @@ int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_star
     return launch_check("itk_pair_topk_kernel (chunk)");
 }
 
-int itk_chunk_local_topk_all(const uint64_t* repair_pairs, const int32_t* chunk_starts, const int32_t* chunk_ends,
-                             const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
-                             uint8_t* repair_error_flags, int rows, int chunks, itk_stream_t stream) {
-    ITK_REQUIRE(repair_pairs && chunk_starts && chunk_ends && failure_flags && local_pairs && local_counts &&
-                    repair_error_flags,
-                "chunk top-k pointers must not be null");
-    ITK_REQUIRE(rows > 0 && chunks > 0 && static_cast<long long>(rows) * chunks <= 0x7fffffffll,
-                "need rows > 0, chunks > 0 and rows * chunks below 2^31");
-    int device = 0;
-    const int rc = init_current_device(&device);
-    if (rc != ITK_OK) return rc;
-    // the chunks of a row run at the same time, so the error flags are cleared here, not by a first chunk
-    ITK_CUDA(cudaMemsetAsync(repair_error_flags, 0, static_cast<size_t>(rows), stream));
-    PairTopKParams params{};
-    params.sources[0] = PairSource{repair_pairs, nullptr};
-    params.num_sources = 1;
-    params.capacity = kRepairChunk;
-    params.rows = rows * chunks;
-    params.row_period = rows;
-    params.row_mask = failure_flags;
-    params.error_flags = repair_error_flags;
-    params.expect_start = chunk_starts;
-    params.expect_end = chunk_ends;
-    params.error_count_mismatch = ITK_REPAIR_ERR_COUNT;
-    params.error_selection = ITK_REPAIR_ERR_LOCAL_SELECT;
-    params.out_pairs = local_pairs;
-    params.out_counts = local_counts;
-    itk_pair_topk_kernel<<<pair_grid(device, rows * chunks), kPairThreads, kPairSmemBytes, stream>>>(params);
-    return launch_check("itk_pair_topk_kernel (all chunks)");
-}
-
-int itk_merge_local_lists(const uint64_t* local_pairs, const int32_t* local_counts, int chunks,
-                          uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint8_t* failure_flags,
-                          uint8_t* repair_error_flags, int rows, itk_stream_t stream) {
-    ITK_REQUIRE(local_pairs && local_counts && accumulator_pairs && accumulator_counts && failure_flags &&
-                    repair_error_flags,
-                "merge pointers must not be null");
-    ITK_REQUIRE(rows > 0 && chunks > 0, "need rows > 0 and chunks > 0");
-    int device = 0;
-    const int rc = init_current_device(&device);
-    if (rc != ITK_OK) return rc;
-    // up to eight lists per launch: the first launch takes eight chunks, every further one the
-    // accumulator and seven more
-    int next = 0;
-    while (next < chunks) {
-        PairTopKParams params{};
-        int used = 0;
-        if (next > 0) params.sources[used++] = PairSource{accumulator_pairs, accumulator_counts};
-        while (used < kMaxPairSources && next < chunks) {
-            params.sources[used++] = PairSource{local_pairs + static_cast<size_t>(next) * rows * kTopK,
-                                                local_counts + static_cast<size_t>(next) * rows};
-            ++next;
-        }
-        params.num_sources = used;
-        params.capacity = kTopK;
-        params.rows = rows;
-        params.row_mask = failure_flags;
-        params.error_flags = repair_error_flags;
-        params.error_count_mismatch = ITK_REPAIR_ERR_MERGE_SELECT;
-        params.error_selection = ITK_REPAIR_ERR_MERGE_SELECT;
-        params.out_pairs = accumulator_pairs;
-        params.out_counts = accumulator_counts;
-        itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
-        const int launched = launch_check("itk_pair_topk_kernel (merge of chunk lists)");
-        if (launched != ITK_OK) return launched;
-    }
-    return ITK_OK;
-}
-
 int itk_merge_topk_pairs(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* local_pairs,
                          const int32_t* local_counts, const uint8_t* failure_flags, uint8_t* repair_error_flags,
                          int rows, int first_chunk, itk_stream_t stream) {
@@ -596,11 +492,10 @@ int itk_merge_topk_pairs(uint64_t* accumulator_pairs, int32_t* accumulator_count
     const int rc = init_current_device(&device);
     if (rc != ITK_OK) return rc;
     PairTopKParams params{};
-    params.sources[0] = PairSource{accumulator_pairs, accumulator_counts};
-    params.sources[1] = PairSource{local_pairs, local_counts};
+    params.sources[0] = PairSource{accumulator_pairs, accumulator_counts, kTopK};
+    params.sources[1] = PairSource{local_pairs, local_counts, kTopK};
     params.num_sources = 2;
     params.first_source = first_chunk ? 1 : 0;
-    params.capacity = kTopK;
     params.rows = rows;
     params.row_mask = failure_flags;
     params.error_flags = repair_error_flags;
@@ -628,30 +523,38 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream) {
     return itk_merge_shard_lists(source_pairs, source_counts, sources, out_ids, out_pairs, out_counts, rows, nullptr,
-                                 nullptr, nullptr, nullptr, 0, 0, stream);
+                                 nullptr, nullptr, nullptr, 0, 0, 0, 1, 0, nullptr, stream);
 }
 
 int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
                           int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                           const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
-                          const int32_t* k_end, int key_lo, int key_hi, itk_stream_t stream) {
+                          const int32_t* k_end, int key_lo, int key_hi, int block_begin, int block_stride,
+                          int num_blocks, const int32_t* out_rows, itk_stream_t stream) {
     ITK_REQUIRE(source_pairs && source_counts, "source tables must not be null");
     ITK_REQUIRE(failure_flags == nullptr || (shard_flags && k_start && k_end && key_hi > key_lo && key_lo >= 0),
                 "a row verdict needs shard_flags, k_start, k_end and 0 <= key_lo < key_hi");
     ITK_REQUIRE(sources >= 1 && sources <= kMaxPairSources, "need 1 <= sources <= %d", kMaxPairSources);
     ITK_REQUIRE(out_ids != nullptr || out_pairs != nullptr, "need out_ids or out_pairs");
     ITK_REQUIRE(rows > 0, "need rows > 0");
+    const int total_blocks = (rows + kBlockQ - 1) / kBlockQ;
+    ITK_REQUIRE(block_stride >= 1 && block_begin >= 0 && num_blocks >= 0 &&
+                    (num_blocks == 0 || block_begin + static_cast<long long>(num_blocks - 1) * block_stride < total_blocks),
+                "owned query blocks must lie inside the %d blocks of the problem", total_blocks);
     int device = 0;
     const int rc = init_current_device(&device);
     if (rc != ITK_OK) return rc;
     PairTopKParams params{};
     for (int s = 0; s < sources; ++s) {
         ITK_REQUIRE(source_pairs[s] && source_counts[s], "source %d has a null pointer", s);
-        params.sources[s] = PairSource{source_pairs[s], source_counts[s]};
+        params.sources[s] = PairSource{source_pairs[s], source_counts[s], kTopK};
     }
     params.num_sources = sources;
-    params.capacity = kTopK;
     params.rows = rows;
+    params.block_begin = block_begin;
+    params.block_stride = block_stride;
+    params.owned_blocks = num_blocks;
+    params.out_rows = out_rows;
     params.out_ids = out_ids;
     params.out_pairs = out_pairs;
     params.out_counts = out_counts;
@@ -661,8 +564,69 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
     params.k_end = k_end;
     params.key_lo = key_lo;
     params.key_hi = key_hi;
-    itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
+    const int items = num_blocks > 0 ? num_blocks * kBlockQ : rows;
+    itk_pair_topk_kernel<<<pair_grid(device, items), kPairThreads, kPairSmemBytes, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (lists)");
+}
+
+int itk_compact_flagged_rows(const uint8_t* failure_flags, const void* q, const float* weights, const int32_t* k_start,
+                             const int32_t* k_end, int rows, int slots, void* q_out, float* weights_out,
+                             int32_t* k_start_out, int32_t* k_end_out, int32_t* slot_rows, itk_stream_t stream) {
+    ITK_REQUIRE(failure_flags && q && weights && k_start && k_end && q_out && weights_out && k_start_out && k_end_out &&
+                    slot_rows,
+                "compaction pointers must not be null");
+    ITK_REQUIRE(rows > 0 && slots > 0 && slots <= 4096, "need rows > 0 and 0 < slots <= 4096");
+    ITK_REQUIRE(aligned16(failure_flags) && aligned16(q) && aligned16(q_out),
+                "failure_flags, q and q_out must be 16-byte aligned");
+    itk_compact_flagged_kernel<<<slots, kCompactThreads, 0, stream>>>(
+        failure_flags, rows, static_cast<const uint4*>(q), weights, k_start, k_end, static_cast<uint4*>(q_out),
+        weights_out, k_start_out, k_end_out, slot_rows);
+    return launch_check("itk_compact_flagged_kernel");
+}
+
+int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* repair_pairs,
+                           const int32_t* k_start, const int32_t* k_end, int chunk_lo, int chunk_hi,
+                           uint8_t* failure_flags, uint8_t* repair_error_flags, int rows, int first_chunk,
+                           int last_chunk, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts,
+                           itk_stream_t stream) {
+    ITK_REQUIRE(accumulator_pairs && accumulator_counts && repair_pairs && k_start && k_end && failure_flags &&
+                    repair_error_flags,
+                "repair merge pointers must not be null");
+    ITK_REQUIRE(rows > 0, "need rows > 0");
+    ITK_REQUIRE(chunk_lo >= 0 && chunk_hi > chunk_lo && chunk_hi - chunk_lo <= kRepairChunk,
+                "need a chunk of at most %d keys", kRepairChunk);
+    ITK_REQUIRE(!last_chunk || out_ids != nullptr || out_pairs != nullptr, "the last chunk needs out_ids or out_pairs");
+    int device = 0;
+    const int rc = init_current_device(&device);
+    if (rc != ITK_OK) return rc;
+    PairTopKParams params{};
+    params.sources[0] = PairSource{accumulator_pairs, accumulator_counts, kTopK};
+    params.sources[1] = PairSource{repair_pairs, nullptr, kRepairChunk};
+    params.num_sources = 2;
+    params.first_source = first_chunk ? 1 : 0;
+    params.rows = rows;
+    params.row_mask = failure_flags;
+    params.error_flags = repair_error_flags;
+    params.clear_errors = first_chunk ? 1 : 0;
+    params.k_start = k_start;
+    params.k_end = k_end;
+    params.dense_lo = chunk_lo;
+    params.dense_hi = chunk_hi;
+    params.error_count_mismatch = ITK_REPAIR_ERR_COUNT;
+    params.error_selection = ITK_REPAIR_ERR_MERGE_SELECT;
+    if (last_chunk) {
+        // the result of the last chunk is the row's answer: it goes to the operator output and a full
+        // result clears the row's failure flag
+        params.out_ids = out_ids;
+        params.out_pairs = out_pairs;
+        params.out_counts = out_counts;
+        params.clear_flags = failure_flags;
+    } else {
+        params.out_pairs = accumulator_pairs;
+        params.out_counts = accumulator_counts;
+    }
+    itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
+    return launch_check("itk_pair_topk_kernel (chunk merge)");
 }
 
 }  // extern "C"

@@ -103,7 +103,7 @@ struct FusedParams {
     uint64_t* out_pairs;        // [shards, rows, 2048] kModeTopK optional (ordered score << 32 | key)
     int32_t* out_counts;        // [shards, rows]      number of pairs written (with out_pairs)
     uint8_t* failure_flags;     // [shards, rows]      kModeTopK output / kModeRepair input
-    uint64_t* spill;            // [shards, rows, 8, kSpillSegCap]
+    uint64_t* spill;            // [4 * grid, 4, kSpillSegCap]: one region per CTA and query row of its current unit
     uint64_t* repair_pairs;     // [shards*rows, 16384] kModeRepair output, dense by key - chunk_lo
     float* diag_logits;         // [rows, diag_stride] dense scores, diagnostic builds only
     long long diag_stride;
@@ -126,8 +126,7 @@ struct FusedParams {
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
     int row_thresholds;         // 1: thresholds are per row (shared by the row's shards); a shard that finds
                                 // fewer than 2048 candidates returns them all instead of failing
-    int flags_per_row;          // kModeRepair with shards > 1: failure_flags has [rows] entries (one launch over
-                                // all repair chunks of every flagged row), repair_pairs stays [shards*rows, 16384]
+    int exit_when_no_keys;      // 1: return at once when every row's key range is empty (nothing is written then)
 };
 
 // Per-row scratch of the selection.
@@ -238,7 +237,7 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
             if (MODE == kModeTopK) {
                 needed = e - s > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
             } else {
-                needed = e > s && p.failure_flags[(p.flags_per_row ? 0ll : static_cast<long long>(u.shard) * p.rows) + row] != 0;
+                needed = e > s && p.failure_flags[static_cast<long long>(u.shard) * p.rows + row] != 0;
             }
         }
         if (needed) {
@@ -329,6 +328,10 @@ __device__ __forceinline__ int decode_key(uint32_t packed, int segment) {
 // Score words in shared memory are the float itself in the Top-K mode (RAW = true in the functions
 // below: the selection works on distances to the row threshold) and its ordered integer image in the
 // sample mode; the spill always holds (ordered score << 32 | key).
+// A unit's spill is written and read back by the same CTA before its next unit starts, so the
+// spill is addressed by CTA and row of the unit, not by query row: 4 regions per CTA.
+__device__ __forceinline__ long long spill_slot(int r) { return static_cast<long long>(blockIdx.x) * kBlockQ + r; }
+
 struct RowView {
     const uint32_t* scores;        // [kSegCap] of the warp's segment
     const uint16_t* ids;           // [kSegCap]
@@ -756,7 +759,7 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     view.segment = segment;
     view.scores = sh.cand_scores[r] + segment * kSegCap;
     view.ids = sh.cand_ids[r] + segment * kSegCap;
-    view.spill = p.spill + row_slot * kSpillRow + segment * kSpillSegCap;
+    view.spill = p.spill + spill_slot(r) * kSpillRow + segment * kSpillSegCap;
     view.lane_entries = lane_entries;
     view.max_entries = __reduce_max_sync(0xffffffffu, lane_entries);
     // Every warp publishes the number of candidates in its segment and the median distance to the
@@ -1212,7 +1215,7 @@ struct RowState {
     int lo, hi;          // key range of the row inside the unit's key slice
     float threshold;
     bool on;             // the row takes part in this launch
-    long long slot;      // row index in the per-shard arrays (thresholds, spill, repair pairs)
+    long long slot;      // row index in the per-shard arrays (thresholds, repair pairs)
 };
 
 template <int MODE>
@@ -1236,7 +1239,7 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
                 if (valid > kTopK) state.threshold = __ldg(p.thresholds + (p.row_thresholds ? row : state.slot));
                 state.on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
             } else {
-                state.on = p.failure_flags[p.flags_per_row ? row : state.slot] != 0;
+                state.on = p.failure_flags[state.slot] != 0;
             }
         }
     }
@@ -1325,8 +1328,13 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         // The usual case is that the fast path flagged no row: find that out with one parallel scan
         // of the flags before any barrier, TMEM or descriptor is set up.
         int any = 0;
-        const int flags = (p.flags_per_row ? 1 : p.shards) * p.rows;
+        const int flags = p.shards * p.rows;
         for (int i = static_cast<int>(threadIdx.x); i < flags; i += kThreads) any |= p.failure_flags[i];
+        if (__syncthreads_or(any) == 0) return;
+    } else if (p.exit_when_no_keys) {
+        // The compacted retry problem usually has no row at all (every slot has an empty key range).
+        int any = 0;
+        for (int i = static_cast<int>(threadIdx.x); i < p.rows; i += kThreads) any |= p.k_end[i] > p.k_start[i] ? 1 : 0;
         if (__syncthreads_or(any) == 0) return;
     }
 
@@ -1627,7 +1635,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                         // rare: this thread's list is full, the candidate goes to the segment's global spill
                         const int at = atomicAdd(&sh.spill_counts[own_r][quarter], 1);
                         if (at < kSpillSegCap)
-                            p.spill[row.slot * kSpillRow + quarter * kSpillSegCap + at] =
+                            p.spill[spill_slot(own_r) * kSpillRow + quarter * kSpillSegCap + at] =
                                 (static_cast<uint64_t>(score_bits) << 32) | static_cast<uint32_t>(key);
                     }
                 } else {
@@ -1671,7 +1679,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                     } else if (full != 0u) {
                         const int at = atomicAdd(&sh.spill_counts[own_r][quarter], 1);
                         if (at < kSpillSegCap)
-                            p.spill[row.slot * kSpillRow + quarter * kSpillSegCap + at] =
+                            p.spill[spill_slot(own_r) * kSpillRow + quarter * kSpillSegCap + at] =
                                 pack_score_id(last_score, static_cast<uint32_t>(key - kTileKeys));
                     }
                 }

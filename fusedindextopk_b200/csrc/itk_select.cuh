@@ -14,8 +14,8 @@
 namespace itk {
 
 constexpr int kPairThreads = 512;
-constexpr int kPairCapacity = 16384;           // pairs one CTA can hold: 128 KB of shared memory
-constexpr int kMaxPairSources = 8;
+constexpr int kPairCapacity = 16384 + 2048;    // pairs one CTA can hold (a dense chunk and one list): 144 KB of shared memory
+constexpr int kMaxPairSources = 16;
 
 // ------------------------------------------------------------------ gather
 
@@ -51,27 +51,115 @@ __global__ void itk_chunk_ranges_kernel(const int32_t* __restrict__ k_start, con
     chunk_end[index] = min(width, max(0, k_end[row] - offset));
 }
 
+// ------------------------------------------------------------------ flagged rows, compacted
+
+// Slot b of the retry problem takes the b-th flagged row (in row order): its query tile, head weights
+// and key range are copied into the compact arrays and slot_rows[b] names the row; slots beyond the
+// number of flagged rows get an empty key range and slot_rows[b] = -1.  One CTA per slot; every CTA
+// scans the flags itself (16 rows per thread and step), which for a few thousand rows is cheaper
+// than a second launch that would hand out the slots.
+constexpr int kCompactThreads = 256;
+
+__global__ void __launch_bounds__(kCompactThreads) itk_compact_flagged_kernel(
+    const uint8_t* __restrict__ flags, int rows, const uint4* __restrict__ q, const float* __restrict__ weights,
+    const int32_t* __restrict__ k_start, const int32_t* __restrict__ k_end, uint4* __restrict__ q_out,
+    float* __restrict__ weights_out, int32_t* __restrict__ k_start_out, int32_t* __restrict__ k_end_out,
+    int32_t* __restrict__ slot_rows) {
+    __shared__ int warp_sums[kCompactThreads / 32];
+    __shared__ int found_row;
+    const int tx = threadIdx.x;
+    const int lane = tx & 31;
+    const int slot = blockIdx.x;
+    if (tx == 0) found_row = -1;
+    int seen = 0;          // flagged rows below `base`
+    bool located = false;
+    for (int base = 0; base < rows && !located; base += kCompactThreads * 16) {
+        const int first = base + tx * 16;
+        uint32_t mask = 0;   // bit i: row first + i is flagged
+        if (first + 16 <= rows) {
+            const uint4 word = *reinterpret_cast<const uint4*>(flags + first);
+            const uint32_t parts[4] = {word.x, word.y, word.z, word.w};
+#pragma unroll
+            for (int i = 0; i < 16; ++i) mask |= ((parts[i >> 2] >> ((i & 3) * 8)) & 0xffu) != 0u ? 1u << i : 0u;
+        } else {
+            for (int i = 0; i < 16 && first + i < rows; ++i) mask |= flags[first + i] != 0 ? 1u << i : 0u;
+        }
+        const int mine = __popc(mask);
+        if (__syncthreads_count(mask != 0u) == 0) continue;   // no flag in this step (the usual case)
+        // inclusive scan of the per-thread counts over the CTA
+        int scan = mine;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const int other = __shfl_up_sync(0xffffffffu, scan, offset);
+            if (lane >= offset) scan += other;
+        }
+        if (lane == 31) warp_sums[tx >> 5] = scan;
+        __syncthreads();
+        int before = 0, step_total = 0;
+#pragma unroll
+        for (int w = 0; w < kCompactThreads / 32; ++w) {
+            if (w < (tx >> 5)) before += warp_sums[w];
+            step_total += warp_sums[w];
+        }
+        const int through = seen + before + scan;   // flagged rows up to and including this thread's 16
+        if (slot >= through - mine && slot < through) {
+            int skip = slot - (through - mine);
+            uint32_t rest = mask;
+            while (skip-- > 0) rest &= rest - 1u;
+            found_row = first + __ffs(rest) - 1;
+        }
+        located = slot < seen + step_total;
+        seen += step_total;
+        __syncthreads();   // warp_sums may be rewritten by the next step
+    }
+    __syncthreads();
+    const int row = found_row;
+    if (row < 0) {
+        if (tx == 0) {
+            slot_rows[slot] = -1;
+            k_start_out[slot] = 0;
+            k_end_out[slot] = 0;
+        }
+        return;
+    }
+    constexpr int kRowVectors = kHeads * kHeadDim / 16;   // 512 x 16 B per query row
+    for (int i = tx; i < kRowVectors; i += kCompactThreads)
+        q_out[static_cast<long long>(slot) * kRowVectors + i] = q[static_cast<long long>(row) * kRowVectors + i];
+    if (tx < kHeads) weights_out[slot * kHeads + tx] = weights[static_cast<long long>(row) * kHeads + tx];
+    if (tx == 0) {
+        slot_rows[slot] = row;
+        k_start_out[slot] = k_start[row];
+        k_end_out[slot] = k_end[row];
+    }
+}
+
 // ------------------------------------------------------------------ pair reducers
 
 struct PairSource {
     const uint64_t* pairs;    // [rows, capacity]
-    const int32_t* counts;    // [rows] live entries per row; null: scan all `capacity` entries, 0 = empty
+    const int32_t* counts;    // [rows] live entries per row; null: a dense chunk, entry i belongs to key
+                              // dense_lo + i, scanned over the row's key range only, 0 = empty
+    int capacity;             // entries per row
 };
 
 struct PairTopKParams {
     PairSource sources[kMaxPairSources];
     int num_sources;
     int first_source;               // sources below this index are ignored (empty accumulator)
-    int capacity;                   // entries per row of every source
     int rows;
-    int row_period;                 // > 0: `rows` counts (chunk, row) pairs, chunk-major; row_mask and error_flags
-                                    // are indexed by row % row_period (one entry per query row)
+    // Rows taken: all of them, or (owned_blocks > 0) the blocks of 4 rows block_begin + i * block_stride.
+    int block_begin, block_stride, owned_blocks;
+    const int32_t* out_rows;        // null, or the row of the outputs (ids, pairs, counts, flags) for source row r;
+                                    // negative: the source row is an empty slot and is skipped
     const uint8_t* row_mask;        // null, or only rows with row_mask[row] != 0 are processed
     uint8_t* error_flags;           // null, or per-row error code; rows with a nonzero code are skipped
     int clear_errors;               // reset error_flags[row] of processed rows first
-    const int32_t* expect_start;    // null, or dense sources are scanned over [expect_start, expect_end) only
-                                    // and the live-entry total must equal expect_end - expect_start
+    // Dense sources: the chunk holds keys [dense_lo, dense_hi); the live-entry total must equal the number
+    // of keys of the row's range [k_start, k_end) inside the chunk (expect_start / expect_end, when given,
+    // hold that range rebased into the chunk instead).
+    const int32_t* expect_start;
     const int32_t* expect_end;
+    int dense_lo, dense_hi;
     int error_count_mismatch;       // code stored when that check fails
     int error_selection;            // code stored when the selection is inconsistent
     uint64_t* out_pairs;            // null or [rows, 2048]
@@ -88,12 +176,12 @@ struct PairTopKParams {
     int key_lo, key_hi;
 };
 
-__device__ __forceinline__ void write_shard_verdict(const PairTopKParams& p, int row, int produced) {
+__device__ __forceinline__ void write_shard_verdict(const PairTopKParams& p, int row, int out_row, int produced) {
     if (p.verdict_flags == nullptr) return;
     int failed = 0;
     for (int s = 0; s < p.num_sources; ++s) failed |= p.shard_flags[static_cast<long long>(s) * p.rows + row];
     const int wanted = min(max(min(p.k_end[row], p.key_hi) - max(p.k_start[row], p.key_lo), 0), kTopK);
-    p.verdict_flags[row] = (failed != 0 || produced < wanted) ? 1 : 0;
+    p.verdict_flags[out_row] = (failed != 0 || produced < wanted) ? 1 : 0;
 }
 
 struct PairShared {
@@ -106,8 +194,8 @@ struct PairShared {
     int skip;
 };
 
-// Exact Top-2048 of the union of up to eight pair lists per row.  One CTA per
-// row (grid-strided); the union (at most 16384 pairs) is staged in shared memory,
+// Exact Top-2048 of the union of up to sixteen pair lists per row.  One CTA per
+// row (grid-strided); the union (at most kPairCapacity pairs) is staged in shared memory,
 // the 2048-th largest score is found by four 8-bit radix rounds over the ordered
 // score bits, then everything above it and the needed number of ties are
 // written.  Rows with at most 2048 pairs are copied through.
@@ -116,26 +204,35 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
     __shared__ PairShared sh;
     const int tx = threadIdx.x;
     const int lane = tx & 31;
+    const int items = p.owned_blocks > 0 ? p.owned_blocks * kBlockQ : p.rows;
+    const auto row_of = [&](int item) {
+        return p.owned_blocks > 0 ? (p.block_begin + (item >> 2) * p.block_stride) * kBlockQ + (item & 3) : item;
+    };
 
     if (p.row_mask != nullptr) {
         // The usual case of the repair graph is that no row is flagged: look at all of this CTA's
         // rows at once instead of paying one dependent global load per row.
         int any = 0;
-        for (int row = static_cast<int>(blockIdx.x) + tx * static_cast<int>(gridDim.x); row < p.rows;
-             row += kPairThreads * static_cast<int>(gridDim.x))
-            any |= p.row_mask[p.row_period > 0 ? row % p.row_period : row];
+        for (int item = static_cast<int>(blockIdx.x) + tx * static_cast<int>(gridDim.x); item < items;
+             item += kPairThreads * static_cast<int>(gridDim.x)) {
+            const int row = row_of(item);
+            if (row < p.rows) any |= p.row_mask[row];
+        }
         if (__syncthreads_or(any) == 0) return;
     }
 
-    for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int row = row_of(item);
+        if (row >= p.rows) continue;
+        const int out_row = p.out_rows != nullptr ? p.out_rows[row] : row;
+        if (out_row < 0) continue;
         __syncthreads();
-        const int flag_row = p.row_period > 0 ? row % p.row_period : row;
         if (tx == 0) {
             int skip = 0;
-            if (p.row_mask != nullptr && p.row_mask[flag_row] == 0) skip = 1;
+            if (p.row_mask != nullptr && p.row_mask[row] == 0) skip = 1;
             if (!skip && p.error_flags != nullptr) {
-                if (p.clear_errors) p.error_flags[flag_row] = 0;
-                else if (p.error_flags[flag_row] != 0) skip = 1;
+                if (p.clear_errors) p.error_flags[row] = 0;
+                else if (p.error_flags[row] != 0) skip = 1;
             }
             sh.skip = skip;
             sh.count = 0;
@@ -146,17 +243,27 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
         if (sh.skip) continue;
 
         // stage the live pairs of every source
+        int error = 0;
         for (int s = p.first_source; s < p.num_sources; ++s) {
-            const uint64_t* source = p.sources[s].pairs + static_cast<long long>(row) * p.capacity;
+            const int capacity = p.sources[s].capacity;
+            const uint64_t* source = p.sources[s].pairs + static_cast<long long>(row) * capacity;
             const bool dense = p.sources[s].counts == nullptr;
             // a dense source is only defined inside the row's own range: entries outside it
             // were never written by the producer
             int first = 0;
-            int live = dense ? p.capacity : min(p.sources[s].counts[row], p.capacity);
-            if (dense && p.expect_start != nullptr) {
-                first = max(p.expect_start[row], 0);
-                live = min(p.expect_end[row], p.capacity);
+            int live = dense ? capacity : min(p.sources[s].counts[row], capacity);
+            if (dense) {
+                if (p.expect_start != nullptr) {
+                    first = max(p.expect_start[row], 0);
+                    live = min(p.expect_end[row], capacity);
+                } else {
+                    const int width = min(capacity, p.dense_hi - p.dense_lo);
+                    first = min(width, max(0, p.k_start[row] - p.dense_lo));
+                    live = min(width, max(0, p.k_end[row] - p.dense_lo));
+                }
+                __syncthreads();
             }
+            const int before = dense ? sh.count : 0;
             for (int base = first & ~31; base < live; base += kPairThreads) {
                 const int i = base + tx;
                 const bool inside = i >= first && i < live;
@@ -165,24 +272,25 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
                 const int position = warp_reserve(&sh.count, keep, lane);
                 if (keep && position < kPairCapacity) staged[position] = pair;
             }
+            if (dense) {
+                __syncthreads();
+                if (sh.count - before != max(live - first, 0)) error = p.error_count_mismatch;
+            }
         }
         __syncthreads();
         const int count = sh.count;
-        int error = 0;
         if (count > kPairCapacity) error = p.error_count_mismatch;
-        if (p.expect_start != nullptr && count != p.expect_end[row] - p.expect_start[row])
-            error = p.error_count_mismatch;
         if (error != 0) {
             if (tx == 0) {
-                if (p.error_flags != nullptr) p.error_flags[flag_row] = static_cast<uint8_t>(error);
-                if (p.out_counts != nullptr) p.out_counts[row] = 0;
-                write_shard_verdict(p, row, 0);
+                if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(error);
+                if (p.out_counts != nullptr) p.out_counts[out_row] = 0;
+                write_shard_verdict(p, row, out_row, 0);
             }
             continue;
         }
 
-        uint64_t* out_pairs = p.out_pairs != nullptr ? p.out_pairs + static_cast<long long>(row) * kTopK : nullptr;
-        int32_t* out_ids = p.out_ids != nullptr ? p.out_ids + static_cast<long long>(row) * kTopK : nullptr;
+        uint64_t* out_pairs = p.out_pairs != nullptr ? p.out_pairs + static_cast<long long>(out_row) * kTopK : nullptr;
+        int32_t* out_ids = p.out_ids != nullptr ? p.out_ids + static_cast<long long>(out_row) * kTopK : nullptr;
         if (count <= kTopK) {
             for (int i = tx; i < kTopK; i += kPairThreads) {
                 const uint64_t pair = i < count ? staged[i] : 0ull;
@@ -190,9 +298,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
                 if (out_ids != nullptr) out_ids[i] = i < count ? static_cast<int32_t>(static_cast<uint32_t>(pair)) : -1;
             }
             if (tx == 0) {
-                if (p.out_counts != nullptr) p.out_counts[row] = count;
-                if (p.clear_flags != nullptr && count == kTopK) p.clear_flags[row] = 0;
-                write_shard_verdict(p, row, count);
+                if (p.out_counts != nullptr) p.out_counts[out_row] = count;
+                if (p.clear_flags != nullptr && count == kTopK) p.clear_flags[out_row] = 0;
+                write_shard_verdict(p, row, out_row, count);
             }
             continue;
         }
@@ -262,13 +370,13 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
         if (tx == 0) {
             const bool consistent = equal_needed > 0 && sh.gcount == greater_total && sh.ecount >= equal_needed;
             if (!consistent) {
-                if (p.error_flags != nullptr) p.error_flags[flag_row] = static_cast<uint8_t>(p.error_selection);
-                if (p.out_counts != nullptr) p.out_counts[row] = 0;
+                if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(p.error_selection);
+                if (p.out_counts != nullptr) p.out_counts[out_row] = 0;
             } else {
-                if (p.out_counts != nullptr) p.out_counts[row] = kTopK;
-                if (p.clear_flags != nullptr) p.clear_flags[row] = 0;
+                if (p.out_counts != nullptr) p.out_counts[out_row] = kTopK;
+                if (p.clear_flags != nullptr) p.clear_flags[out_row] = 0;
             }
-            write_shard_verdict(p, row, consistent ? kTopK : 0);
+            write_shard_verdict(p, row, out_row, consistent ? kTopK : 0);
         }
     }
 }

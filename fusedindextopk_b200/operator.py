@@ -68,9 +68,13 @@ class SamplePlan:
     target_candidates: int
     sample_ids: Any          # int32 [S] on the device, sorted
     enabled: bool            # False: every row has few enough keys, thresholds are -inf
+    retry_rank: int = 0      # sampled rank of the lower threshold that flagged rows are retried with
 
 
-REPAIR_ALL_CHUNKS_BYTES_LIMIT = 16 << 30
+# Flagged rows are retried as a compact problem of this many rows (8 query blocks; with up to 16 key
+# shards each that is one wave of CTAs); rows beyond it go straight to the dense repair.
+RETRY_SLOTS = 32
+RETRY_TARGET_FACTOR = 2      # the retry threshold aims at this many times the first pass's candidates
 
 
 def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigmas: float = 2.0) -> SamplePlan:
@@ -81,7 +85,7 @@ def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigma
     target = sampling.TARGET_CANDIDATES
     if context_tokens <= target:
         empty = torch.zeros(0, dtype=torch.int32, device=device)
-        return SamplePlan(context_tokens, 0, 0, target, empty, False)
+        return SamplePlan(context_tokens, 0, 0, target, empty, False, 0)
     # Beyond the reference's longest context (163840 keys) its schedule would ask for more samples than
     # the prepass kernel keeps per row (2048); the guarded rank is valid for any sample size, so clamp.
     elements = min(sampling.production_sample_elements(context_tokens), TOP_K)
@@ -91,7 +95,14 @@ def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigma
     ids = sampling.common_random_sample_ids(
         torch, context_tokens, elements, seed=sampling.sampling_seed(seed), device=device
     )
-    return SamplePlan(context_tokens, elements, rank, target, ids, True)
+    # A row whose first threshold came out too high (fewer than 2048 keys above it) or too low (more
+    # candidates than the bounded lists hold) is rerun with a threshold aimed at twice as many candidates,
+    # spread over key shards with a list each.
+    retry_rank = sampling.guarded_sample_rank(
+        elements, context_tokens, target_candidates=min(RETRY_TARGET_FACTOR * target, context_tokens),
+        guard_sigmas=guard_sigmas,
+    )
+    return SamplePlan(context_tokens, elements, rank, target, ids, True, retry_rank)
 
 
 @dataclass
@@ -109,6 +120,7 @@ class Workspace:
     # CUDA graphs of whole operator calls, keyed by the input tensors' addresses (they die with the workspace)
     graphs: dict = field(default_factory=dict)
     seen_inputs: set = field(default_factory=set)
+    retry: Any = None        # RetryBuffers, or None when no row of this problem can be flagged
 
     def __getattr__(self, name: str) -> Any:
         buffers = self.__dict__.get("buffers", {})
@@ -160,32 +172,23 @@ def make_workspace(
         "output_ids": empty((rows, TOP_K), i32),
         "failure_flags": torch.zeros(rows, device=device, dtype=u8),
         "thresholds": torch.full((rows,), -math.inf, device=device, dtype=f32),
-        "spill_pairs": empty((rows, _lib.SPILL_U64_PER_ROW), i64),
+        # bounded overflow of the shared-memory lists: one region per CTA and unit row, not per query row
+        "spill_pairs": empty((sizes.spill_bytes // 8,), i64),
         "sampled_kv": empty((samples, _lib.HEAD_DIM), u8),
         "sampled_scales": empty((samples,), f32),
         "status": torch.zeros(1, device=device, dtype=i32),
     }
-    assert buffers["spill_pairs"].numel() * 8 == sizes.spill_bytes
     if with_pairs:
         buffers["output_pairs"] = empty((rows, TOP_K), i64)
         buffers["output_counts"] = torch.zeros(rows, device=device, dtype=i32)
     if repair:
-        chunks = sizes.repair_chunks
-        # One buffer per chunk lets a single launch rescan all chunks of the flagged rows on different SMs
-        # (a flagged row of a 160 K context otherwise keeps one SM busy for a whole pass over the context);
-        # 512 MiB per chunk at 4096 rows, which a 180 GB device affords.  Very large problems keep the
-        # one-chunk buffer and the chunk-by-chunk launches.
-        all_chunks_bytes = chunks * rows * _lib.REPAIR_CHUNK * 8
-        parallel_chunks = chunks > 1 and all_chunks_bytes <= REPAIR_ALL_CHUNKS_BYTES_LIMIT
+        # The dense repair is the last resort behind the retry: one 16384-key chunk of pairs at a time
+        # (128 KiB per row), as in the reference.
         buffers.update(
-            repair_pairs=empty((chunks, rows, _lib.REPAIR_CHUNK) if parallel_chunks else (rows, _lib.REPAIR_CHUNK), i64),
-            local_pairs=empty((chunks, rows, TOP_K) if parallel_chunks else (rows, TOP_K), i64),
-            local_counts=torch.zeros((chunks, rows) if parallel_chunks else (rows,), device=device, dtype=i32),
+            repair_pairs=empty((rows, _lib.REPAIR_CHUNK), i64),
             accumulator_pairs=empty((rows, TOP_K), i64),
             accumulator_counts=torch.zeros(rows, device=device, dtype=i32),
             repair_error_flags=torch.zeros(rows, device=device, dtype=u8),
-            chunk_starts=empty((chunks, rows), i32),
-            chunk_ends=empty((chunks, rows), i32),
         )
     if key_shards is None:
         key_shards = auto_key_shards(owned, keys, torch.cuda.get_device_properties(device).multi_processor_count)
@@ -195,23 +198,96 @@ def make_workspace(
             shard_pairs=empty((key_shards, rows, TOP_K), i64),
             shard_counts=torch.zeros((key_shards, rows), device=device, dtype=i32),
             shard_flags=torch.zeros((key_shards, rows), device=device, dtype=u8),
-            shard_spill=empty((key_shards * rows, _lib.SPILL_U64_PER_ROW), i64),
+            shard_spill=empty((shard_sizes.spill_bytes // 8,), i64),
             merged_counts=torch.zeros(rows, device=device, dtype=i32),
         )
-        assert buffers["shard_spill"].numel() * 8 == shard_sizes.spill_bytes
-    return Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
+    workspace = Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
+    if repair and plan.enabled:
+        workspace.retry = _make_retry_buffers(rows, keys, device)
+    return workspace
+
+
+@dataclass
+class RetryBuffers:
+    """The compact problem that flagged rows are rerun as: ``RETRY_SLOTS`` rows, ``shards`` key shards."""
+
+    shards: int
+    q: Any
+    weights: Any
+    k_start: Any
+    k_end: Any
+    slot_rows: Any           # int32 [slots]: the query row in slot b, -1 for an empty slot
+    thresholds: Any
+    shard_pairs: Any
+    shard_counts: Any
+    shard_flags: Any
+    spill: Any
+    counts: Any              # int32 [rows]: pairs the merge wrote per query row (scratch)
+
+
+def retry_key_shards(keys: int) -> int:
+    """Key shards of the retry problem: units of at least 32 tiles, at most 16 (8 blocks x 16 fill the SMs)."""
+
+    tiles = (keys + 127) // 128
+    return max(1, min(_lib.MAX_PAIR_SOURCES, tiles // 32))
+
+
+def _make_retry_buffers(rows: int, keys: int, device: Any) -> RetryBuffers:
+    import torch
+
+    slots, shards = RETRY_SLOTS, retry_key_shards(keys)
+    u8, i32, i64, f32 = torch.uint8, torch.int32, torch.int64, torch.float32
+    spill_bytes = _lib.workspace_sizes(slots, keys, shards).spill_bytes
+
+    def empty(shape, dtype):
+        return torch.empty(shape, device=device, dtype=dtype)
+
+    return RetryBuffers(
+        shards=shards,
+        q=torch.zeros((slots, _lib.HEADS, _lib.HEAD_DIM), device=device, dtype=u8),
+        weights=torch.zeros((slots, _lib.HEADS), device=device, dtype=f32),
+        k_start=torch.zeros(slots, device=device, dtype=i32),
+        k_end=torch.zeros(slots, device=device, dtype=i32),
+        slot_rows=torch.full((slots,), -1, device=device, dtype=i32),
+        thresholds=torch.full((slots,), -math.inf, device=device, dtype=f32),
+        shard_pairs=empty((shards, slots, TOP_K), i64),
+        shard_counts=torch.zeros((shards, slots), device=device, dtype=i32),
+        shard_flags=torch.zeros((shards, slots), device=device, dtype=u8),
+        spill=empty((spill_bytes // 8,), i64),
+        counts=torch.zeros(rows, device=device, dtype=i32),
+    )
+
+
+# Cost model of one launch of the fused kernel, in microseconds (B200, measured): a 128-key tile of a unit,
+# a full selection per unit, a selection that only copies (a shard that found fewer than 2048 candidates),
+# the fixed cost of a unit, and the merge of a row's shard lists (one CTA per row).
+_TILE_US, _SELECT_US, _COPY_US, _UNIT_US, _MERGE_ROW_US, _MERGE_LAUNCH_US = 0.72, 16.0, 4.0, 3.0, 6.0, 6.0
 
 
 def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
     """Key-range shards per query block for a call with ``query_blocks`` blocks of 4 rows.
 
-    One shard while the blocks alone fill half the SMs; otherwise as many shards as fit the SMs,
-    at most 8 (the merge kernel's source limit) and with at least 4096 keys per shard.
+    The units of a launch run in waves of ``sm_count``; cutting every block's key range into S shards
+    makes S times as many units of 1/S the length, which pays when the last wave is poorly filled
+    (16 blocks of a 160 K context on 148 SMs; 128 blocks per rank of an 8-GPU run, where 8 shards
+    turn one wave of 128 long units into 7 waves of 148 short ones), and costs a selection per shard
+    and a merge launch.  The shard count with the smallest modelled time is returned, 1 on ties;
+    shards have at least 4096 keys.
     """
 
-    if query_blocks <= 0 or 2 * query_blocks > sm_count:
+    if query_blocks <= 0:
         return 1
-    return max(1, min(_lib.MAX_PAIR_SOURCES, sm_count // query_blocks, keys // 4096))
+    tiles = (keys + 127) // 128
+    best, best_time = 1, None
+    for shards in range(1, min(8, keys // 4096) + 1):
+        waves = -(-query_blocks * shards // sm_count)
+        select = _SELECT_US if shards == 1 else _COPY_US
+        time = waves * (_UNIT_US + tiles / shards * _TILE_US + select)
+        if shards > 1:
+            time += _MERGE_LAUNCH_US + -(-query_blocks * 4 // sm_count) * _MERGE_ROW_US
+        if best_time is None or time < best_time * 0.97:   # a new count must win by 3 % to be taken
+            best, best_time = shards, time
+    return best
 
 
 # --------------------------------------------------------------------------- stages
@@ -257,7 +333,8 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
     check(library.itk_sample_thresholds(
         ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
         ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
-        plan.target_candidates, ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
+        plan.target_candidates, ws.block_begin, ws.block_stride, ws.num_blocks, 0,
+        ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
         ptr(trace), ptr(ws.status), stream,
     ))
     return ws.thresholds
@@ -322,68 +399,102 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         check(library.itk_merge_shard_lists(
             pair_table, count_table, shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
             ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows,
-            ptr(ws.shard_flags), ptr(ws.failure_flags), ptr(k_start), ptr(k_end), key_lo, args.key_hi, stream))
+            ptr(ws.shard_flags), ptr(ws.failure_flags), ptr(k_start), ptr(k_end), key_lo, args.key_hi,
+            ws.block_begin, ws.block_stride, ws.num_blocks, None, stream))
+    return ws.output_ids
+
+
+@_on_workspace_device
+def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
+              key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
+    """Flagged rows once more, with a lower threshold and a candidate list per key shard.
+
+    Four launches, all of them over the compact problem of ``RETRY_SLOTS`` rows and returning at once
+    when no row is flagged: compaction of the flagged rows, their thresholds at ``plan.retry_rank``,
+    the fused kernel with key shards, and the merge that writes the ids of repaired rows into the
+    operator output and clears their flags.  What is still flagged afterwards goes to ``run_repair``.
+    The reference has only the dense rescan (``kernel/plugin.py:333-377``).
+    """
+
+    import torch
+
+    retry, plan = ws.retry, ws.plan
+    if retry is None:
+        return ws.output_ids
+    library = load_library()
+    stream = current_stream(torch, ws.device)
+    slots = int(retry.slot_rows.shape[0])
+    key_hi = ws.keys if key_hi is None else key_hi
+    check(library.itk_compact_flagged_rows(
+        ptr(ws.failure_flags), ptr(q), ptr(weights), ptr(k_start), ptr(k_end), ws.rows, slots,
+        ptr(retry.q), ptr(retry.weights), ptr(retry.k_start), ptr(retry.k_end), ptr(retry.slot_rows), stream,
+    ))
+    blocks = slots // _lib.BLOCK_Q
+    check(library.itk_sample_thresholds(
+        ptr(retry.q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(retry.weights), ptr(plan.sample_ids),
+        ptr(retry.k_start), ptr(retry.k_end), ptr(retry.thresholds), slots, plan.sample_elements, plan.retry_rank,
+        plan.target_candidates, 0, 1, blocks, 1, None, 0, None, ptr(ws.status), stream,
+    ))
+    args = FusedArgs()
+    args.q, args.kv, args.kv_scales, args.weights = ptr(retry.q), ptr(kv), ptr(kv_scales), ptr(retry.weights)
+    args.k_start, args.k_end = ptr(retry.k_start), ptr(retry.k_end)
+    args.thresholds = ptr(retry.thresholds)
+    args.out_pairs, args.out_counts = ptr(retry.shard_pairs), ptr(retry.shard_counts)
+    args.failure_flags, args.spill = ptr(retry.shard_flags), ptr(retry.spill)
+    args.status = ptr(ws.status)
+    args.rows, args.keys = slots, ws.keys
+    args.key_lo, args.key_hi = key_lo, key_hi
+    args.shards = retry.shards
+    args.block_begin, args.block_stride, args.num_blocks = 0, 1, blocks
+    args.thresholds_per_row = 1
+    args.exit_when_no_keys = 1
+    args.tile_table = ptr(tile_table)
+    args.physical_keys = int(kv.shape[0]) if tile_table is not None else 0
+    check(library.itk_fused_topk(ctypes.byref(args), stream))
+    pair_table = _lib.pointer_table([retry.shard_pairs[s] for s in range(retry.shards)])
+    count_table = _lib.pointer_table([retry.shard_counts[s] for s in range(retry.shards)])
+    check(library.itk_merge_shard_lists(
+        pair_table, count_table, retry.shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
+        ptr(ws.output_counts) if want_pairs else ptr(retry.counts), slots,
+        ptr(retry.shard_flags), ptr(ws.failure_flags), ptr(retry.k_start), ptr(retry.k_end), key_lo, key_hi,
+        0, 1, 0, ptr(retry.slot_rows), stream))
     return ws.output_ids
 
 
 @_on_workspace_device
 def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
-               key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
-    """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags."""
+               key_hi: int | None = None, want_pairs: bool = False, tile_table=None, retry: bool = True) -> Any:
+    """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags.
+
+    First the retry of the flagged rows (``run_retry``), then, for what is still flagged, the dense
+    rescan: per 16384-key chunk one launch of the dense producer and one that selects the chunk's pairs
+    into the running Top-2048 of each flagged row (the last one writes the ids and clears the flags).
+    """
 
     import torch
 
+    if retry:
+        run_retry(ws, q, kv, kv_scales, weights, k_start, k_end, key_lo=key_lo, key_hi=key_hi,
+                  want_pairs=want_pairs, tile_table=tile_table)
     library = load_library()
     stream = current_stream(torch, ws.device)
     key_hi = ws.keys if key_hi is None else key_hi
-    check(library.itk_update_chunk_ranges(
-        ptr(k_start), ptr(k_end), ptr(ws.chunk_starts), ptr(ws.chunk_ends), ws.rows, ws.keys, stream
-    ))
     physical_keys = int(kv.shape[0]) if tile_table is not None else 0
-    all_chunks = ws.repair_pairs.dim() == 3 and key_lo == 0 and key_hi == ws.keys
-    if all_chunks:
-        check(library.itk_repair_produce_all(
-            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
-            ptr(ws.repair_pairs), ws.rows, ws.keys, ws.block_begin, ws.block_stride, ws.num_blocks,
-            ptr(tile_table), physical_keys, ptr(ws.status), stream,
-        ))
-        chunks = int(ws.repair_pairs.shape[0])
-        check(library.itk_chunk_local_topk_all(
-            ptr(ws.repair_pairs), ptr(ws.chunk_starts), ptr(ws.chunk_ends), ptr(ws.failure_flags),
-            ptr(ws.local_pairs), ptr(ws.local_counts), ptr(ws.repair_error_flags), ws.rows, chunks, stream,
-        ))
-        check(library.itk_merge_local_lists(
-            ptr(ws.local_pairs), ptr(ws.local_counts), chunks, ptr(ws.accumulator_pairs),
-            ptr(ws.accumulator_counts), ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, stream,
-        ))
-    first = True
-    for chunk_index, chunk_lo in enumerate(range(0, ws.keys, _lib.REPAIR_CHUNK)):
-        chunk_hi = min(ws.keys, chunk_lo + _lib.REPAIR_CHUNK)
-        if all_chunks or chunk_hi <= key_lo or chunk_lo >= key_hi:
-            continue
-        chunk_pairs = ws.repair_pairs[0] if ws.repair_pairs.dim() == 3 else ws.repair_pairs
-        local_pairs = ws.local_pairs[0] if ws.local_pairs.dim() == 3 else ws.local_pairs
-        local_counts = ws.local_counts[0] if ws.local_counts.dim() == 2 else ws.local_counts
+    chunks = [(lo, min(ws.keys, lo + _lib.REPAIR_CHUNK)) for lo in range(0, ws.keys, _lib.REPAIR_CHUNK)]
+    chunks = [(lo, hi) for lo, hi in chunks if hi > key_lo and lo < key_hi]
+    for index, (chunk_lo, chunk_hi) in enumerate(chunks):
         check(library.itk_repair_produce_paged(
             ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
-            ptr(chunk_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
+            ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
             ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
         ))
-        check(library.itk_chunk_local_topk(
-            ptr(chunk_pairs), ptr(ws.chunk_starts[chunk_index]), ptr(ws.chunk_ends[chunk_index]),
-            ptr(ws.failure_flags), ptr(local_pairs), ptr(local_counts), ptr(ws.repair_error_flags),
-            ws.rows, 1 if first else 0, stream,
+        last = index == len(chunks) - 1
+        check(library.itk_repair_merge_chunk(
+            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.repair_pairs), ptr(k_start), ptr(k_end),
+            chunk_lo, chunk_hi, ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows,
+            1 if index == 0 else 0, 1 if last else 0, ptr(ws.output_ids),
+            ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None, stream,
         ))
-        check(library.itk_merge_topk_pairs(
-            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(local_pairs), ptr(local_counts),
-            ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, 1 if first else 0, stream,
-        ))
-        first = False
-    check(library.itk_finalize_repair(
-        ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.output_ids),
-        ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None,
-        ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows, stream,
-    ))
     return ws.output_ids
 
 

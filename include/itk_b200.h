@@ -45,7 +45,8 @@ typedef struct CUstream_st* itk_stream_t;
 #define ITK_REPAIR_CHUNK 16384
 #define ITK_SPILL_U64_PER_ROW 5632      /* 4 segments x 1408 entries */
 #define ITK_MAX_KEYS 262144             /* 16-bit segment-relative candidate ids */
-#define ITK_MAX_PAIR_SOURCES 8
+#define ITK_MAX_PAIR_SOURCES 16
+#define ITK_MAX_CTAS 256                /* the fused kernel's grid never exceeds this (one CTA per SM) */
 
 /* bits of the device status word */
 #define ITK_STATUS_WAIT_EXPIRED 1
@@ -69,7 +70,8 @@ int itk_resource_report(char* buffer, size_t buffer_bytes);
  * `shards` key ranges.  Replaces the allocations of FusedIndexTopK.prepare
  * (src/fused_index_topk/kernel/plugin.py:202-257). */
 typedef struct itk_workspace_sizes {
-    size_t spill_bytes;            /* uint64 [shards,Q,4,1408] */
+    size_t spill_bytes;            /* uint64 [min(4*ceil(Q/4)*shards, 4*ITK_MAX_CTAS),4,1408]: one region per CTA
+                                    * and row of the CTA's current unit, not per query row */
     size_t repair_pairs_bytes;     /* uint64 [shards*Q,16384] */
     size_t pairs_bytes;            /* uint64 [shards,Q,2048]: local / accumulator / output pairs, each */
     size_t counts_bytes;           /* int32  [shards,Q] */
@@ -92,10 +94,15 @@ int itk_gather_sampled_kv(const void* kv, const float* kv_scales, const int32_t*
  * valid.  Replaces deep_gemm.fp8_mqa_logits on the sample (kernel/plugin.py:272-282)
  * followed by threshold_out (sampling_threshold.cu:236-292).  diag_logits (optional,
  * fp32 [Q,diag_stride]) receives the dense sampled scores; trace (optional, int64 [CTAs,32])
- * the per-CTA phase trace.  Either selects the diagnostic build. */
+ * the per-CTA phase trace.  Either selects the diagnostic build.  Only the query blocks
+ * block_begin + i * block_stride, i < num_blocks, are scored (the blocks one rank owns; 0, 1,
+ * ceil(Q/4) for all of them); the thresholds of the other rows are left alone.  With
+ * exit_when_no_keys the launch returns at once, writing nothing, when every row's key range is
+ * empty (the compacted retry problem of a call without flagged rows). */
 int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sampled_scales, const float* weights,
                           const int32_t* sample_ids, const int32_t* k_start, const int32_t* k_end,
                           float* thresholds, int rows, int samples, int sample_rank, int target_candidates,
+                          int block_begin, int block_stride, int num_blocks, int exit_when_no_keys,
                           float* diag_logits, long long diag_stride, long long* trace, int* status,
                           itk_stream_t stream);
 
@@ -113,7 +120,8 @@ typedef struct itk_fused_args {
     uint64_t* out_pairs;        /* optional [shards,Q,2048]: (ordered score << 32) | key */
     int32_t* out_counts;        /* optional [shards,Q], with out_pairs */
     uint8_t* failure_flags;     /* [shards,Q]: 1 = row must be repaired */
-    uint64_t* spill;            /* [shards,Q,4,1408] scratch */
+    uint64_t* spill;            /* scratch of itk_workspace_sizes.spill_bytes: bounded overflow of the
+                                 * shared-memory candidate lists, one region per CTA and unit row */
     float* diag_logits;         /* optional fp32 [Q,diag_stride] dense scores (-inf outside the range) */
     long long diag_stride;
     long long* trace;           /* optional int64 [CTAs,32] phase trace; selects the diagnostic build.
@@ -139,6 +147,8 @@ typedef struct itk_fused_args {
     int thresholds_per_row;     /* with shards > 1: thresholds has [Q] entries (one per row, shared by its
                                  * shards) and a shard that finds fewer than 2048 candidates returns them
                                  * all instead of failing; the merge decides whether the row is complete */
+    int exit_when_no_keys;      /* 1: return at once, writing nothing, when every row's key range is empty
+                                 * (the compacted retry problem of a call without flagged rows) */
     const int32_t* tile_table;  /* paged keys (null = contiguous): physical 128-key tile of each logical
                                  * tile, [ceil(keys/128)], every entry in [0, physical_keys/128).  kv and
                                  * kv_scales then are the physical pool ([physical_keys,128], [physical_keys]);
@@ -191,41 +201,46 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
-/* itk_repair_produce for every 16384-key chunk of the context in ONE launch: the work units are
- * (query block, chunk), so the chunks of a flagged row are rescanned by different SMs at the same
- * time instead of one after the other (a single flagged row of a 160 K context otherwise costs a
- * whole pass of one SM over the context).  repair_pairs is [chunks, Q, 16384]; chunk c of row r is
- * repair_pairs[(c*Q + r)*16384 ...], in the layout itk_chunk_local_topk reads.  tile_table /
- * physical_keys as in itk_fused_args (null / 0 for contiguous keys).  The reference launches its
- * repair producer once per chunk (src/fused_index_topk/kernel/plugin.py:333-377). */
-int itk_repair_produce_all(const void* q, const void* kv, const float* kv_scales, const float* weights,
-                           const int32_t* k_start, const int32_t* k_end, const uint8_t* failure_flags,
-                           uint64_t* repair_pairs, int rows, int keys, int block_begin, int block_stride,
-                           int num_blocks, const int32_t* tile_table, int physical_keys, int* status,
-                           itk_stream_t stream);
-
-/* The chunk-local Top-2048 of every (chunk, flagged row) in one launch, and the merge of a row's chunk
- * lists in ceil((chunks-1)/7) launches of up to eight lists: the companions of itk_repair_produce_all.
- * repair_pairs [chunks,Q,16384], chunk_starts / chunk_ends [chunks,Q] (itk_update_chunk_ranges),
- * local_pairs [chunks,Q,2048], local_counts [chunks,Q]; repair_error_flags [Q] is cleared first.
- * Same selection and error codes as itk_chunk_local_topk / itk_merge_topk_pairs. */
-int itk_chunk_local_topk_all(const uint64_t* repair_pairs, const int32_t* chunk_starts, const int32_t* chunk_ends,
-                             const uint8_t* failure_flags, uint64_t* local_pairs, int32_t* local_counts,
-                             uint8_t* repair_error_flags, int rows, int chunks, itk_stream_t stream);
-int itk_merge_local_lists(const uint64_t* local_pairs, const int32_t* local_counts, int chunks,
-                          uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint8_t* failure_flags,
-                          uint8_t* repair_error_flags, int rows, itk_stream_t stream);
-
 /* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1,
  * thresholds_per_row), which also decides per row whether the result is complete:
  * failure_flags[row] = 1 when any shard of the row reported an overflow
  * (shard_flags [sources, rows], the launch's failure_flags) or the union holds fewer than
  * min(2048, number of keys of the row inside [key_lo, key_hi)) pairs, else 0.  Such rows
- * go to the repair graph.  No counterpart in the reference (one unit per query block there). */
+ * go to the repair graph.  Only the rows of the query blocks block_begin + i * block_stride,
+ * i < num_blocks, are merged (num_blocks = 0: every row).  With out_rows (int32 [rows], optional)
+ * the lists, k_start and k_end are those of a compacted problem and row r's ids, pairs, count and
+ * flag go to row out_rows[r] of the outputs; r is skipped when out_rows[r] < 0.
+ * No counterpart in the reference (one unit per query block there). */
 int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
                           int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                           const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
-                          const int32_t* k_end, int key_lo, int key_hi, itk_stream_t stream);
+                          const int32_t* k_end, int key_lo, int key_hi, int block_begin, int block_stride,
+                          int num_blocks, const int32_t* out_rows, itk_stream_t stream);
+
+/* First stage of the retry of flagged rows: the b-th flagged row (in row order) becomes row b of a
+ * compact problem of `slots` rows: its query tile, head weights and key range are copied to
+ * q_out [slots,64,128], weights_out [slots,64], k_start_out / k_end_out [slots], and slot_rows[b]
+ * names it.  Slots beyond the number of flagged rows get an empty key range and slot_rows[b] = -1;
+ * flagged rows beyond the slots stay flagged for the dense repair.  The compact problem is then run
+ * through itk_sample_thresholds (a lower threshold), itk_fused_topk with key shards and
+ * itk_merge_shard_lists with out_rows = slot_rows, which costs the scores of the flagged rows only.
+ * The reference repairs every flagged row by the dense rescan (src/fused_index_topk/kernel/plugin.py:333-377). */
+int itk_compact_flagged_rows(const uint8_t* failure_flags, const void* q, const float* weights, const int32_t* k_start,
+                             const int32_t* k_end, int rows, int slots, void* q_out, float* weights_out,
+                             int32_t* k_start_out, int32_t* k_end_out, int32_t* slot_rows, itk_stream_t stream);
+
+/* itk_chunk_local_topk, itk_merge_topk_pairs and (on the last chunk) itk_finalize_repair in one launch:
+ * accumulator <- Top-2048(accumulator U the dense pairs of chunk [chunk_lo, chunk_hi)) for flagged rows;
+ * the chunk-local key range of each row is derived from k_start / k_end here, so no
+ * itk_update_chunk_ranges launch is needed.  With last_chunk the result goes to out_ids / out_pairs /
+ * out_counts instead and a complete row's failure flag is cleared.  Error codes as in the separate
+ * steps (count mismatch 1, selection 3).  Same kernels of the reference as those three
+ * (long_context_repair.cu:237-426), launched there once each per chunk. */
+int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* repair_pairs,
+                           const int32_t* k_start, const int32_t* k_end, int chunk_lo, int chunk_hi,
+                           uint8_t* failure_flags, uint8_t* repair_error_flags, int rows, int first_chunk,
+                           int last_chunk, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts,
+                           itk_stream_t stream);
 
 /* Paged forms of itk_gather_sampled_kv and itk_repair_produce: the keys live in a pool of
  * 128-key physical tiles addressed through tile_table as in itk_fused_args.  The reference
@@ -263,7 +278,7 @@ int itk_quantize_rows_e4m3(const void* source, int source_dtype, const float* fo
  * forbids foreign allocations, a plugin loaded into a process whose memory budget is
  * fixed at start-up, or code running inside a region where allocation would
  * synchronise the device.  itk_fused_topk needs one scratch buffer from its caller
- * (the bounded overflow spill, 45056 bytes per query row); this variant takes the
+ * (the bounded overflow spill, 45056 bytes per CTA and unit row); this variant takes the
  * spill from an array that is part of the library image instead, so the caller passes
  * only inputs, thresholds and outputs.  It has no counterpart in the reference, whose
  * host bindings always receive the spill workspace from the Python plugin.

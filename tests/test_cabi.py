@@ -40,13 +40,17 @@ def test_version_and_constants(library):
     header = HEADER.read_text()
     for macro, value in (("ITK_TOP_K", _lib.TOP_K), ("ITK_BLOCK_Q", _lib.BLOCK_Q),
                          ("ITK_REPAIR_CHUNK", _lib.REPAIR_CHUNK), ("ITK_SPILL_U64_PER_ROW", _lib.SPILL_U64_PER_ROW),
-                         ("ITK_MAX_KEYS", _lib.MAX_KEYS), ("ITK_MAX_PAIR_SOURCES", _lib.MAX_PAIR_SOURCES)):
+                         ("ITK_MAX_KEYS", _lib.MAX_KEYS), ("ITK_MAX_PAIR_SOURCES", _lib.MAX_PAIR_SOURCES),
+                         ("ITK_MAX_CTAS", _lib.MAX_CTAS)):
         assert re.search(rf"#define {macro} {value}\b", header), macro
 
 
 def test_workspace_sizes_need_no_gpu(library):
     sizes = _lib.workspace_sizes(4096, 16384, 1)
-    assert sizes.spill_bytes == 4096 * _lib.SPILL_U64_PER_ROW * 8
+    # one spill region per CTA and unit row: capped at 4 x ITK_MAX_CTAS regions, never more than the units need
+    assert sizes.spill_bytes == 4 * _lib.MAX_CTAS * _lib.SPILL_U64_PER_ROW * 8
+    assert _lib.workspace_sizes(10, 16384, 1).spill_bytes == 12 * _lib.SPILL_U64_PER_ROW * 8
+    assert _lib.workspace_sizes(10, 16384, 4).spill_bytes == 48 * _lib.SPILL_U64_PER_ROW * 8
     assert sizes.repair_pairs_bytes == 4096 * 16384 * 8
     assert sizes.pairs_bytes == 4096 * 2048 * 8
     assert sizes.repair_chunks == 1

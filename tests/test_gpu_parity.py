@@ -53,19 +53,18 @@ def _assert_close_to_oracle(got: torch.Tensor, want: torch.Tensor) -> float:
     return worst
 
 
-def _run_with_diagnostics(host, device, *, thresholds=None, repair=True):
+def _run_with_diagnostics(host, device, *, thresholds=None, repair=True, retry=True):
     rows, keys = host.case.query_tokens, host.case.context_tokens
     gpu = inputs_to(host, device)
     ws = operator.make_workspace(rows, keys, device, seed=host.case.seed)
-    if thresholds is None:
-        operator.run_sample_thresholds(ws, *_tensors(gpu))
-    else:
+    operator.run_sample_thresholds(ws, *_tensors(gpu))   # also gathers the sampled keys the retry reads
+    if thresholds is not None:
         ws.thresholds.fill_(thresholds)
     logits = torch.full((rows, keys), -math.inf, device=device)
     operator.run_fused_topk(ws, *_tensors(gpu), diag_logits=logits, force_compute=True)
     fast_flags = ws.failure_flags.clone()
     if repair:
-        operator.run_repair(ws, *_tensors(gpu))
+        operator.run_repair(ws, *_tensors(gpu), retry=retry)
     torch.cuda.synchronize()
     ws.check_status()
     return ws, logits, fast_flags
@@ -142,29 +141,120 @@ def test_forced_spill_and_forced_repair(device, threshold):
     score_threshold_check(indices, logits.cpu(), case)
 
 
-@pytest.mark.parametrize("rows,keys", [(10, 40000), (6, 70001), (4, 150000)])   # 3, 5 and 10 chunks (two merge launches)
-def test_forced_repair_over_several_chunks_in_one_producer_launch(device, rows, keys, monkeypatch):
-    """+inf thresholds starve every row; the repair rescans every chunk of every row.  The workspace that holds
-    all chunks (one producer launch) and the one-chunk workspace (a launch per chunk) must agree."""
+@pytest.mark.parametrize("rows,keys", [(10, 40000), (6, 70001), (4, 150000)])   # 3, 5 and 10 chunks
+def test_forced_repair_by_the_dense_rescan_and_by_the_retry(device, rows, keys):
+    """+inf thresholds starve every row.  The dense rescan alone (a producer and a merge launch per 16384-key
+    chunk) and the retry alone (lower sampled threshold, key shards, merge) must both clear every flag and agree."""
 
     host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=keys)
     case = PrefillCase("forced-chunks", rows, keys, 2048, 0)
-    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=math.inf)
-    assert ws.repair_pairs.dim() == 3 and ws.repair_pairs.shape[0] == (keys + 16383) // 16384
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=math.inf, retry=False)
     assert int(fast_flags.sum()) == rows
     assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
     indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
     validate_topk_indices(indices, case)
     score_threshold_check(indices, logits.cpu(), case)
-    monkeypatch.setattr(operator, "REPAIR_ALL_CHUNKS_BYTES_LIMIT", 0)
-    ws_one, _, _ = _run_with_diagnostics(host, device, thresholds=math.inf)
-    assert ws_one.repair_pairs.dim() == 2
-    assert int(ws_one.failure_flags.sum()) == 0
-    assert torch.equal(ws_one.output_ids.sort(dim=-1).values, ws.output_ids.sort(dim=-1).values)
+
+    again, _, again_flags = _run_with_diagnostics(host, device, thresholds=math.inf, repair=False)
+    assert int(again_flags.sum()) == rows
+    again.output_ids.fill_(-7)
+    operator.run_retry(again, *_tensors(inputs_to(host, device)))
+    torch.cuda.synchronize()
+    again.check_status()
+    assert again.retry.shards == operator.retry_key_shards(keys) > 1
+    assert sorted(again.retry.slot_rows.tolist()) == [-1] * (operator.RETRY_SLOTS - rows) + list(range(rows))
+    assert int(again.failure_flags.sum()) == 0
+    retried = again.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(retried, case)
+    verdict = score_threshold_check(retried, logits.cpu(), case)
+    if verdict["rows_with_cutoff_ties"] == 0:
+        assert torch.equal(again.output_ids.sort(dim=-1).values, ws.output_ids.sort(dim=-1).values)
+
+
+def test_flagged_rows_beyond_the_retry_slots_go_to_the_dense_rescan(device):
+    """40 starved rows: the first 32 (in row order) fit the retry problem, the other 8 stay flagged for
+    the dense rescan; the whole repair stage leaves no flag and an exact result."""
+
+    rows, keys = 40, 20000
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=3)
+    case = PrefillCase("beyond-slots", rows, keys, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=math.inf, repair=False)
+    assert int(fast_flags.sum()) == rows
+    tensors = _tensors(inputs_to(host, device))
+    operator.run_retry(ws, *tensors)
+    torch.cuda.synchronize()
+    left = ws.failure_flags.nonzero().flatten().tolist()
+    assert left == list(range(operator.RETRY_SLOTS, rows))
+    operator.run_repair(ws, *tensors, retry=False)
+    torch.cuda.synchronize()
+    ws.check_status()
+    assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+
+
+def test_overflowing_rows_are_retried_with_a_sampled_threshold(device):
+    """-inf thresholds on a 40000-key context overflow lists and spill of every row (10000 candidates per
+    segment); the retry gives each row a sampled threshold and a list per key shard."""
+
+    rows, keys = 8, 40000
+    host = make_workload_inputs("c2", query_tokens=rows, context_tokens=keys, seed=5)
+    case = PrefillCase("overflow", rows, keys, 2048, 0)
+    ws, logits, fast_flags = _run_with_diagnostics(host, device, thresholds=-math.inf, repair=False)
+    assert int(fast_flags.sum()) == rows
+    operator.run_retry(ws, *_tensors(inputs_to(host, device)))
+    torch.cuda.synchronize()
+    ws.check_status()
+    assert int(ws.failure_flags.sum()) == 0
+    assert bool(torch.isfinite(ws.retry.thresholds[:rows]).all())
+    indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    score_threshold_check(indices, logits.cpu(), case)
+
+
+def test_a_rank_touches_only_its_own_query_blocks(device):
+    """Every third query block, with and without key shards: thresholds, ids and flags of the other blocks
+    keep what the caller put there, the owned rows match the full problem's exact sets."""
+
+    rows, keys = 48, 32768
+    host = make_workload_inputs("c2", query_tokens=rows, context_tokens=keys, seed=11)
+    gpu = inputs_to(host, device)
+    tensors = _tensors(gpu)
+    case = PrefillCase("ownership", rows, keys, 2048, 0)
+    full = operator.make_workspace(rows, keys, device, key_shards=1)
+    want = operator.run_operator(full, *tensors).clone()
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(full, *tensors, diag_logits=logits)
+    ties = score_threshold_check(want.unsqueeze(1).contiguous().cpu(), logits.cpu(), case)["rows_with_cutoff_ties"]
+    owned = torch.arange(rows, device=device).view(-1, 4)[1::3].flatten()
+    other = torch.ones(rows, dtype=torch.bool, device=device)
+    other[owned] = False
+    for shards in (1, 4):
+        ws = operator.make_workspace(rows, keys, device, block_begin=1, block_stride=3, key_shards=shards)
+        assert ws.num_blocks == 4
+        ws.thresholds.fill_(123.0)
+        ws.output_ids.fill_(-5)
+        ws.failure_flags.fill_(0)
+        got = operator.run_operator(ws, *tensors)
+        torch.cuda.synchronize()
+        ws.check_status()
+        assert bool((ws.thresholds[other] == 123.0).all()) and bool((ws.thresholds[owned] != 123.0).all())
+        assert bool((got[other] == -5).all())
+        assert int(ws.failure_flags.sum()) == 0
+        if ties == 0:
+            assert torch.equal(got[owned].sort(dim=-1).values, want[owned].sort(dim=-1).values)
+        # exact on the kernel's own scores: nothing outside the set beats anything inside it
+        picked = torch.zeros_like(logits[owned], dtype=torch.bool)
+        picked.scatter_(1, got[owned].long(), True)
+        assert bool((picked.sum(dim=1) == 2048).all())
+        inside = torch.where(picked, logits[owned], torch.full_like(logits[owned], math.inf)).amin(dim=1)
+        outside = torch.where(picked, torch.full_like(logits[owned], -math.inf), logits[owned]).amax(dim=1)
+        assert bool((inside >= outside).all())
 
 
 def test_spill_path_without_overflow(device):
-    """N = 8192 with threshold -inf: 2048 candidates per segment, 1280 in shared memory and 768 spilled;
+    """N = 8192 with threshold -inf: 2048 candidates per segment, 1248 in shared memory and 800 spilled;
     all distances to the threshold are infinite, so the selection takes its radix fallback."""
 
     host = make_workload_inputs("c0", query_tokens=8, context_tokens=8192)
