@@ -86,6 +86,7 @@ bool g_initialised[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
 
 constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairCapacity) * sizeof(uint64_t);
+constexpr int kShardMergeCapacity = 6144;   // pairs staged per row by the merge of one launch's key shards
 
 template <typename Kernel>
 cudaError_t raise_smem(Kernel kernel, size_t bytes) {
@@ -477,6 +478,7 @@ int itk_chunk_local_topk(const uint64_t* repair_pairs, const int32_t* chunk_star
     params.error_selection = ITK_REPAIR_ERR_LOCAL_SELECT;
     params.out_pairs = local_pairs;
     params.out_counts = local_counts;
+    params.stage_capacity = kPairCapacity;
     itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (chunk)");
 }
@@ -503,6 +505,7 @@ int itk_merge_topk_pairs(uint64_t* accumulator_pairs, int32_t* accumulator_count
     params.error_selection = ITK_REPAIR_ERR_MERGE_SELECT;
     params.out_pairs = accumulator_pairs;
     params.out_counts = accumulator_counts;
+    params.stage_capacity = kPairCapacity;
     itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (merge)");
 }
@@ -565,7 +568,18 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
     params.key_lo = key_lo;
     params.key_hi = key_hi;
     const int items = num_blocks > 0 ? num_blocks * kBlockQ : rows;
-    itk_pair_topk_kernel<<<pair_grid(device, items), kPairThreads, kPairSmemBytes, stream>>>(params);
+    // The shards of one launch share the row's threshold, so their union is about as large as the
+    // candidate set of an unsharded row (some 3 to 5 thousand pairs): a small staging area lets three
+    // CTAs share an SM, and the rare row that exceeds it is flagged and goes to the retry.  Merges
+    // without that way out (no verdict, or the retry's own merge) get room for every list in full.
+    int capacity = sources * kTopK < kPairCapacity ? sources * kTopK : kPairCapacity;
+    if (failure_flags != nullptr && out_rows == nullptr && capacity > kShardMergeCapacity) capacity = kShardMergeCapacity;
+    params.stage_capacity = capacity;
+    const size_t smem = static_cast<size_t>(capacity) * sizeof(uint64_t);
+    const int per_sm = smem <= 72 * 1024 ? 3 : (smem <= 110 * 1024 ? 2 : 1);   // the kernel is built for 3 CTAs of 512 threads per SM
+    int grid = g_sm_count[device] * per_sm;
+    if (grid > items) grid = items;
+    itk_pair_topk_kernel<<<grid, kPairThreads, smem, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (lists)");
 }
 
@@ -625,6 +639,7 @@ int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_cou
         params.out_pairs = accumulator_pairs;
         params.out_counts = accumulator_counts;
     }
+    params.stage_capacity = kPairCapacity;
     itk_pair_topk_kernel<<<pair_grid(device, rows), kPairThreads, kPairSmemBytes, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (chunk merge)");
 }

@@ -146,6 +146,8 @@ struct PairTopKParams {
     PairSource sources[kMaxPairSources];
     int num_sources;
     int first_source;               // sources below this index are ignored (empty accumulator)
+    int stage_capacity;             // pairs the launch's shared memory holds (<= kPairCapacity); a row whose
+                                    // union is larger is an error (count mismatch), for a shard merge a failed row
     int rows;
     // Rows taken: all of them, or (owned_blocks > 0) the blocks of 4 rows block_begin + i * block_stride.
     int block_begin, block_stride, owned_blocks;
@@ -199,7 +201,7 @@ struct PairShared {
 // the 2048-th largest score is found by four 8-bit radix rounds over the ordered
 // score bits, then everything above it and the needed number of ties are
 // written.  Rows with at most 2048 pairs are copied through.
-__global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const PairTopKParams p) {
+__global__ void __launch_bounds__(kPairThreads, 3) itk_pair_topk_kernel(const PairTopKParams p) {
     extern __shared__ __align__(16) uint64_t staged[];
     __shared__ PairShared sh;
     const int tx = threadIdx.x;
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
                 const uint64_t pair = inside ? source[i] : 0ull;
                 const bool keep = inside && (!dense || pair != 0ull);
                 const int position = warp_reserve(&sh.count, keep, lane);
-                if (keep && position < kPairCapacity) staged[position] = pair;
+                if (keep && position < p.stage_capacity) staged[position] = pair;
             }
             if (dense) {
                 __syncthreads();
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) itk_pair_topk_kernel(const Pa
         }
         __syncthreads();
         const int count = sh.count;
-        if (count > kPairCapacity) error = p.error_count_mismatch;
+        if (count > p.stage_capacity) error = p.error_count_mismatch != 0 ? p.error_count_mismatch : 1;
         if (error != 0) {
             if (tx == 0) {
                 if (p.error_flags != nullptr) p.error_flags[row] = static_cast<uint8_t>(error);
