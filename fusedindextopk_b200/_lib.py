@@ -56,13 +56,13 @@ class FusedArgs(ctypes.Structure):
         ("q", c_void_p), ("kv", c_void_p), ("kv_scales", c_void_p), ("weights", c_void_p),
         ("k_start", c_void_p), ("k_end", c_void_p), ("thresholds", c_void_p),
         ("out_ids", c_void_p), ("out_pairs", c_void_p), ("out_counts", c_void_p),
-        ("failure_flags", c_void_p), ("spill", c_void_p), ("diag_logits", c_void_p),
+        ("failure_flags", c_void_p), ("spill", c_void_p),
+        ("shard_pairs", c_void_p), ("shard_counts", c_void_p), ("shard_flags", c_void_p), ("diag_logits", c_void_p),
         ("diag_stride", c_longlong), ("trace", c_void_p), ("status", c_void_p),
         ("wait_limit_ns", ctypes.c_ulonglong), ("withhold_loads", c_int),
         ("rows", c_int), ("keys", c_int), ("key_lo", c_int), ("key_hi", c_int), ("shards", c_int),
-        ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
-        ("force_compute", c_int), ("max_ctas", c_int), ("thresholds_per_row", c_int),
-        ("exit_when_no_keys", c_int),
+        ("split_blocks", c_int), ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
+        ("force_compute", c_int), ("max_ctas", c_int), ("exit_when_no_keys", c_int),
         ("tile_table", c_void_p), ("physical_keys", c_int),
     ]
 

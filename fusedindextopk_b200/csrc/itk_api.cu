@@ -325,16 +325,18 @@ int itk_sample_thresholds(const void* q, const void* sampled_kv, const float* sa
 int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     ITK_REQUIRE(args != nullptr, "args must not be null");
     const itk_fused_args& a = *args;
-    ITK_REQUIRE(a.q && a.kv && a.kv_scales && a.weights && a.k_start && a.k_end && a.thresholds && a.failure_flags &&
-                    a.spill && a.status,
+    ITK_REQUIRE(a.q && a.kv && a.kv_scales && a.weights && a.k_start && a.k_end && a.thresholds && a.spill && a.status,
                 "fused top-k pointers must not be null");
-    ITK_REQUIRE(a.out_ids != nullptr || a.out_pairs != nullptr, "need out_ids or out_pairs");
     ITK_REQUIRE(a.rows > 0 && a.keys > 0 && a.keys <= ITK_MAX_KEYS, "need rows > 0 and 0 < keys <= %d", ITK_MAX_KEYS);
     ITK_REQUIRE(a.key_lo >= 0 && a.key_lo % kTileKeys == 0 && a.key_hi > a.key_lo && a.key_hi <= a.keys,
                 "need 0 <= key_lo < key_hi <= keys with key_lo a multiple of 128");
     ITK_REQUIRE(a.shards >= 1 && a.shards <= ITK_MAX_PAIR_SOURCES, "need 1 <= shards <= %d", ITK_MAX_PAIR_SOURCES);
-    ITK_REQUIRE(a.shards == 1 || a.out_pairs != nullptr, "key-range shards need out_pairs");
-    ITK_REQUIRE(a.out_ids == nullptr || a.shards == 1, "out_ids is only defined for a single shard");
+    ITK_REQUIRE(a.shards == 1 || (a.shard_pairs && a.shard_counts && a.shard_flags),
+                "key-range shards need shard_pairs, shard_counts and shard_flags");
+    ITK_REQUIRE(a.split_blocks >= 0 && a.split_blocks <= a.num_blocks, "split_blocks must lie in [0, num_blocks]");
+    const int split_blocks = a.shards == 1 ? 0 : (a.split_blocks == 0 ? a.num_blocks : a.split_blocks);
+    ITK_REQUIRE(split_blocks == a.num_blocks || (a.failure_flags && (a.out_ids != nullptr || a.out_pairs != nullptr)),
+                "whole blocks need failure_flags and out_ids or out_pairs");
     const int total_blocks = (a.rows + kBlockQ - 1) / kBlockQ;
     ITK_REQUIRE(a.block_stride >= 1 && a.block_begin >= 0 && a.num_blocks >= 0 &&
                     (a.num_blocks == 0 || a.block_begin + static_cast<long long>(a.num_blocks - 1) * a.block_stride < total_blocks),
@@ -363,6 +365,9 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.out_counts = a.out_counts;
     params.failure_flags = a.failure_flags;
     params.spill = a.spill;
+    params.shard_pairs = a.shard_pairs;
+    params.shard_counts = a.shard_counts;
+    params.shard_flags = a.shard_flags;
     params.diag_logits = a.diag_logits;
     params.diag_stride = a.diag_stride;
     params.trace = a.trace;
@@ -377,13 +382,13 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     const int per_shard = (span + a.shards - 1) / a.shards;
     params.shard_keys = (per_shard + kTileKeys - 1) / kTileKeys * kTileKeys;
     params.shards = a.shards;
+    params.split_blocks = split_blocks;
     params.block_begin = a.block_begin;
     params.block_stride = a.block_stride;
     params.num_blocks = a.num_blocks;
     params.top_k_min_valid = a.force_compute ? 0 : kTopK;
-    params.row_thresholds = a.thresholds_per_row != 0 ? 1 : 0;
     params.exit_when_no_keys = a.exit_when_no_keys != 0 ? 1 : 0;
-    const long long units = static_cast<long long>(a.num_blocks) * a.shards;
+    const long long units = (a.num_blocks - split_blocks) + static_cast<long long>(split_blocks) * a.shards;
     return launch_fused<kModeTopK>(params, a.diag_logits != nullptr || a.trace != nullptr,
                                    fused_grid(device, units, a.max_ctas), stream);
 }

@@ -96,13 +96,16 @@ struct FusedParams {
     const float* weights;       // [rows, 64]
     const int32_t* k_start;     // [rows]
     const int32_t* k_end;       // [rows]
-    const float* thresholds;    // [shards, rows]      kModeTopK input
+    const float* thresholds;    // [rows]              kModeTopK input
     float* thresholds_out;      // [rows]              kModeSample output
     const int32_t* sample_ids;  // [keys]              kModeSample: key position of each sample
     int32_t* out_ids;           // [rows, 2048]        kModeTopK output (may be null when out_pairs is set)
-    uint64_t* out_pairs;        // [shards, rows, 2048] kModeTopK optional (ordered score << 32 | key)
-    int32_t* out_counts;        // [shards, rows]      number of pairs written (with out_pairs)
-    uint8_t* failure_flags;     // [shards, rows]      kModeTopK output / kModeRepair input
+    uint64_t* out_pairs;        // [rows, 2048]        kModeTopK optional (ordered score << 32 | key)
+    int32_t* out_counts;        // [rows]              number of pairs written (with out_pairs)
+    uint8_t* failure_flags;     // [rows]              kModeTopK output / kModeRepair input
+    uint64_t* shard_pairs;      // [shards, rows, 2048] pairs, counts and flags of the units that are one key
+    int32_t* shard_counts;      // [shards, rows]       shard of a split query block (the merge of a row's
+    uint8_t* shard_flags;       // [shards, rows]       shards decides about the row)
     uint64_t* spill;            // [4 * grid, 4, kSpillSegCap]: one region per CTA and query row of its current unit
     uint64_t* repair_pairs;     // [shards*rows, 16384] kModeRepair output, dense by key - chunk_lo
     float* diag_logits;         // [rows, diag_stride] dense scores, diagnostic builds only
@@ -118,14 +121,14 @@ struct FusedParams {
     int key_hi;                 // end of the last shard
     int shard_keys;             // keys per shard (multiple of 128)
     int shards;
+    int split_blocks;           // the key range of this many owned blocks (the ones with the fewest keys: the
+                                // lowest block numbers) is cut into `shards` units; the others are one unit each
     int block_begin;            // first owned query block
     int block_stride;           // stride between owned query blocks
     int num_blocks;             // owned query blocks
     int sample_rank;            // kModeSample
     int target_candidates;      // kModeSample
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
-    int row_thresholds;         // 1: thresholds are per row (shared by the row's shards); a shard that finds
-                                // fewer than 2048 candidates returns them all instead of failing
     int exit_when_no_keys;      // 1: return at once when every row's key range is empty (nothing is written then)
 };
 
@@ -195,6 +198,8 @@ __device__ __forceinline__ bool timed_wait(uint64_t* bar, uint32_t parity, const
 struct Unit {
     int block;       // query block index
     int shard;
+    bool split;      // one key shard of a split block: the result are pairs for the merge, and a shard that
+                     // finds fewer than 2048 candidates returns them all instead of failing
     int row0;
     int nrows;
     int key_lo;
@@ -211,15 +216,23 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
     const int grid = static_cast<int>(gridDim.x);
     const int cta = (iter & 1) ? grid - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
     const long long index = static_cast<long long>(iter) * grid + cta;
-    const long long total = static_cast<long long>(p.num_blocks) * p.shards;
+    // whole blocks first (the longest units), then the shards of the split blocks
+    const long long whole = p.num_blocks - p.split_blocks;
+    const long long total = whole + static_cast<long long>(p.split_blocks) * p.shards;
     if (index >= total) return false;
-    const int ordinal = static_cast<int>(index / p.shards);
-    u.shard = static_cast<int>(index - static_cast<long long>(ordinal) * p.shards);
+    int ordinal = static_cast<int>(index);
+    u.shard = 0;
+    u.split = index >= whole;
+    if (u.split) {
+        const long long inside = index - whole;
+        ordinal = static_cast<int>(whole + inside / p.shards);
+        u.shard = static_cast<int>(inside % p.shards);
+    }
     u.block = p.block_begin + (p.num_blocks - 1 - ordinal) * p.block_stride;
     u.row0 = u.block * kBlockQ;
     u.nrows = min(kBlockQ, p.rows - u.row0);
-    u.key_lo = p.key_lo + u.shard * p.shard_keys;
-    u.key_hi = min(p.key_hi, u.key_lo + p.shard_keys);
+    u.key_lo = u.split ? p.key_lo + u.shard * p.shard_keys : p.key_lo;
+    u.key_hi = u.split ? min(p.key_hi, u.key_lo + p.shard_keys) : p.key_hi;
     int lo = 0x7fffffff, hi = 0;
     for (int r = 0; r < u.nrows; ++r) {
         const int row = u.row0 + r;
@@ -235,9 +248,9 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
             s = max(start, u.key_lo);
             e = min(min(end, p.keys), u.key_hi);
             if (MODE == kModeTopK) {
-                needed = e - s > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
+                needed = e - s > ((u.split || p.out_pairs != nullptr) ? 0 : p.top_k_min_valid);
             } else {
-                needed = e > s && p.failure_flags[static_cast<long long>(u.shard) * p.rows + row] != 0;
+                needed = e > s && p.failure_flags[row] != 0;
             }
         }
         if (needed) {
@@ -721,17 +734,21 @@ __device__ __forceinline__ void emit_row(RowSelect& rs, const RowView& v, int la
 __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedParams& p, const Unit& u, int r,
                                                 bool has_tiles, RowBarrier& rb, int tid, int lane_entries) {
     const int row = u.row0 + r;
-    const long long row_slot = static_cast<long long>(u.shard) * p.rows + row;
+    // a shard of a split block writes pairs, count and flag of its own; a whole block the row's
+    const long long row_slot = u.split ? static_cast<long long>(u.shard) * p.rows + row : row;
     const int start = max(__ldg(p.k_start + row), u.key_lo);
     const int end = min(min(__ldg(p.k_end + row), p.keys), u.key_hi);
     const int valid = max(end - start, 0);
-    int32_t* out_ids = p.out_ids != nullptr ? p.out_ids + static_cast<long long>(row) * kTopK : nullptr;
-    uint64_t* out_pairs = p.out_pairs != nullptr ? p.out_pairs + row_slot * kTopK : nullptr;
+    int32_t* out_ids = !u.split && p.out_ids != nullptr ? p.out_ids + static_cast<long long>(row) * kTopK : nullptr;
+    uint64_t* const pair_base = u.split ? p.shard_pairs : p.out_pairs;
+    uint64_t* out_pairs = pair_base != nullptr ? pair_base + row_slot * kTopK : nullptr;
+    int32_t* const out_counts = u.split ? p.shard_counts : p.out_counts;
+    uint8_t* const failure_flags = u.split ? p.shard_flags : p.failure_flags;
 
     if (out_pairs == nullptr && valid <= p.top_k_min_valid) {
         // every valid key is selected; no scores are needed
         for (int i = tid; i < kTopK; i += kRowThreads) out_ids[i] = i < valid ? start + i : -1;
-        if (tid == 0) p.failure_flags[row_slot] = 0;
+        if (tid == 0) failure_flags[row_slot] = 0;
         return;
     }
     const auto fill_empty = [&](int from) {
@@ -744,8 +761,8 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
         // pairs requested but the row has no key in this shard
         fill_empty(0);
         if (tid == 0) {
-            p.failure_flags[row_slot] = 0;
-            if (p.out_counts != nullptr) p.out_counts[row_slot] = 0;
+            failure_flags[row_slot] = 0;
+            if (out_counts != nullptr) out_counts[row_slot] = 0;
         }
         return;
     }
@@ -754,7 +771,7 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     const int lane = tid & 31;
     const int segment = tid >> 5;
     const float threshold =
-        valid > kTopK ? __ldg(p.thresholds + (p.row_thresholds ? row : row_slot)) : __int_as_float(0xff800000);
+        valid > kTopK ? __ldg(p.thresholds + row) : __int_as_float(0xff800000);
     RowView view;
     view.segment = segment;
     view.scores = sh.cand_scores[r] + segment * kSegCap;
@@ -790,13 +807,13 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     view.in_spill = min(sh.spill_counts[r][segment], kSpillSegCap);
     const int wanted = min(valid, kTopK);
     uint32_t* row_hist = sh.row_hist[r];
-    if (overflow || (total < wanted && !p.row_thresholds)) {
+    if (overflow || (total < wanted && !u.split)) {
         // too many candidates for the buffers or too few for a full answer: the repair pass redoes the row
-        // (with per-row thresholds a shard may come up short: the merge of the shards checks the total)
+        // (a shard of a split block may come up short: the merge of the shards checks the total)
         fill_empty(0);
         if (tid == 0) {
-            p.failure_flags[row_slot] = 1;
-            if (p.out_counts != nullptr) p.out_counts[row_slot] = 0;
+            failure_flags[row_slot] = 1;
+            if (out_counts != nullptr) out_counts[row_slot] = 0;
         }
     } else {
         if (rb.lap != nullptr) rb.lap_start = clock64();
@@ -817,8 +834,8 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
             lap(rb, 5);
         }
         if (tid == 0) {
-            p.failure_flags[row_slot] = 0;
-            if (p.out_counts != nullptr) p.out_counts[row_slot] = min(total, kTopK);
+            failure_flags[row_slot] = 0;
+            if (out_counts != nullptr) out_counts[row_slot] = min(total, kTopK);
         }
     }
     row_sync(rb);   // every warp is done with the candidates, the histograms and the list
@@ -1215,16 +1232,16 @@ struct RowState {
     int lo, hi;          // key range of the row inside the unit's key slice
     float threshold;
     bool on;             // the row takes part in this launch
-    long long slot;      // row index in the per-shard arrays (thresholds, repair pairs)
+    long long slot;      // the row
 };
 
 template <int MODE>
-__device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row0, int nrows, int shard,
+__device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row0, int nrows, bool split,
                                                    int unit_key_lo, int unit_key_hi, int r) {
     RowState state{0, 0, __int_as_float(0xff800000), r < nrows, 0};
     if (state.on) {
         const int row = row0 + r;
-        state.slot = static_cast<long long>(shard) * p.rows + row;
+        state.slot = row;
         const int start = __ldg(p.k_start + row);
         const int end = __ldg(p.k_end + row);
         if (MODE == kModeSample) {
@@ -1236,8 +1253,8 @@ __device__ __forceinline__ RowState load_row_state(const FusedParams& p, int row
             state.hi = min(min(end, p.keys), unit_key_hi);
             if (MODE == kModeTopK) {
                 const int valid = state.hi - state.lo;
-                if (valid > kTopK) state.threshold = __ldg(p.thresholds + (p.row_thresholds ? row : state.slot));
-                state.on = valid > (p.out_pairs != nullptr ? 0 : p.top_k_min_valid);
+                if (valid > kTopK) state.threshold = __ldg(p.thresholds + row);
+                state.on = valid > ((split || p.out_pairs != nullptr) ? 0 : p.top_k_min_valid);
             } else {
                 state.on = p.failure_flags[state.slot] != 0;
             }
@@ -1328,7 +1345,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         // The usual case is that the fast path flagged no row: find that out with one parallel scan
         // of the flags before any barrier, TMEM or descriptor is set up.
         int any = 0;
-        const int flags = p.shards * p.rows;
+        const int flags = p.rows;
         for (int i = static_cast<int>(threadIdx.x); i < flags; i += kThreads) any |= p.failure_flags[i];
         if (__syncthreads_or(any) == 0) return;
     } else if (p.exit_when_no_keys) {
@@ -1557,7 +1574,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             // Filter state of the row, arranged so that the tile loop needs no branch: a key passes when
             // it lies in [row_lo, row_lo + row_span) and its score reaches the threshold (-inf for rows
             // that keep every key); a row that is switched off has an empty range.
-            const RowState row = load_row_state<MODE>(p, u.row0, u.nrows, u.shard, u.key_lo, u.key_hi, own_r);
+            const RowState row = load_row_state<MODE>(p, u.row0, u.nrows, u.split, u.key_lo, u.key_hi, own_r);
             int row_lo = row.lo;
             unsigned row_span = row.on && row.hi > row.lo ? static_cast<unsigned>(row.hi - row.lo) : 0u;
             float threshold = row.threshold;

@@ -121,6 +121,7 @@ class Workspace:
     graphs: dict = field(default_factory=dict)
     seen_inputs: set = field(default_factory=set)
     retry: Any = None        # RetryBuffers, or None when no row of this problem can be flagged
+    split_blocks: int = 0    # owned blocks (the lowest numbered ones) whose key range is cut into shards
 
     def __getattr__(self, name: str) -> Any:
         buffers = self.__dict__.get("buffers", {})
@@ -148,11 +149,13 @@ def make_workspace(
     with_pairs: bool = False,
     repair: bool = True,
     key_shards: int | None = None,
+    split_blocks_hint: int | None = None,
 ) -> Workspace:
     """Allocate every buffer once, outside any timed region.
 
-    ``key_shards`` > 1 cuts every query block's key range into that many work units (for calls with
-    too few query blocks to fill the GPU); ``None`` chooses it from Q, N and the SM count.
+    ``key_shards`` > 1 cuts the key range of ``split_blocks_hint`` query blocks (default: all of them)
+    into that many work units each; ``None`` lets ``plan_key_shards`` choose both from Q, N and the SM
+    count: the blocks of the last, partly filled wave of units are split so that they fill it.
     """
 
     import torch
@@ -190,8 +193,13 @@ def make_workspace(
             accumulator_counts=torch.zeros(rows, device=device, dtype=i32),
             repair_error_flags=torch.zeros(rows, device=device, dtype=u8),
         )
+    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
     if key_shards is None:
-        key_shards = auto_key_shards(owned, keys, torch.cuda.get_device_properties(device).multi_processor_count)
+        split_blocks, key_shards = plan_key_shards(owned, keys, sm_count)
+    else:
+        split_blocks = owned if key_shards > 1 else 0
+        if split_blocks_hint is not None and key_shards > 1:
+            split_blocks = max(1, min(owned, int(split_blocks_hint)))
     if key_shards > 1:
         shard_sizes = _lib.workspace_sizes(rows, keys, key_shards)
         buffers.update(
@@ -202,6 +210,7 @@ def make_workspace(
             merged_counts=torch.zeros(rows, device=device, dtype=i32),
         )
     workspace = Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
+    workspace.split_blocks = split_blocks if key_shards > 1 else 0
     if repair and plan.enabled:
         workspace.retry = _make_retry_buffers(rows, keys, device)
     return workspace
@@ -226,10 +235,11 @@ class RetryBuffers:
 
 
 def retry_key_shards(keys: int) -> int:
-    """Key shards of the retry problem: units of at least 32 tiles, at most 16 (8 blocks x 16 fill the SMs)."""
+    """Key shards of the retry problem: units of at least 32 tiles; at least 2 (a split block returns
+    pairs, which is what the merge into the operator output reads), at most 16 (8 blocks x 16 fill the SMs)."""
 
     tiles = (keys + 127) // 128
-    return max(1, min(_lib.MAX_PAIR_SOURCES, tiles // 32))
+    return max(2, min(_lib.MAX_PAIR_SOURCES, tiles // 32))
 
 
 def _make_retry_buffers(rows: int, keys: int, device: Any) -> RetryBuffers:
@@ -264,30 +274,39 @@ def _make_retry_buffers(rows: int, keys: int, device: Any) -> RetryBuffers:
 _TILE_US, _SELECT_US, _COPY_US, _UNIT_US, _MERGE_ROW_US, _MERGE_LAUNCH_US = 0.72, 16.0, 4.0, 3.0, 6.0, 6.0
 
 
-def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
-    """Key-range shards per query block for a call with ``query_blocks`` blocks of 4 rows.
+def plan_key_shards(query_blocks: int, keys: int, sm_count: int) -> tuple[int, int]:
+    """``(split_blocks, shards)`` for a call with ``query_blocks`` blocks of 4 rows.
 
-    The units of a launch run in waves of ``sm_count``; cutting every block's key range into S shards
-    makes S times as many units of 1/S the length, which pays when the last wave is poorly filled
-    (16 blocks of a 160 K context on 148 SMs; 128 blocks per rank of an 8-GPU run, where 8 shards
-    turn one wave of 128 long units into 7 waves of 148 short ones), and costs a selection per shard
-    and a merge launch.  The shard count with the smallest modelled time is returned, 1 on ties;
-    shards have at least 4096 keys.
+    The units of a launch run in waves of ``sm_count``.  The blocks of the last, partly filled wave (all
+    blocks when there are fewer than SMs) can be cut into S key shards each: S times as many units of 1/S
+    the length fill the wave better (128 blocks per rank of an 8-GPU run: 8 shards turn one wave of 128
+    long units into 7 waves of 148 short ones; 68 left-over blocks: 2 shards make 136 half units), at the
+    price of a selection per shard and of the merge launch.  The shard count with the smallest modelled
+    time of that last wave is returned, ``(0, 1)`` when not splitting is best; shards have at least 4096 keys.
     """
 
     if query_blocks <= 0:
-        return 1
+        return 0, 1
+    tail = query_blocks % sm_count if query_blocks > sm_count else query_blocks
+    if tail == 0:
+        return 0, 1
     tiles = (keys + 127) // 128
     best, best_time = 1, None
     for shards in range(1, min(8, keys // 4096) + 1):
-        waves = -(-query_blocks * shards // sm_count)
+        waves = -(-tail * shards // sm_count)
         select = _SELECT_US if shards == 1 else _COPY_US
         time = waves * (_UNIT_US + tiles / shards * _TILE_US + select)
         if shards > 1:
-            time += _MERGE_LAUNCH_US + -(-query_blocks * 4 // sm_count) * _MERGE_ROW_US
+            time += _MERGE_LAUNCH_US + -(-tail * 4 // (3 * sm_count)) * _MERGE_ROW_US
         if best_time is None or time < best_time * 0.97:   # a new count must win by 3 % to be taken
             best, best_time = shards, time
-    return best
+    return (tail, best) if best > 1 else (0, 1)
+
+
+def auto_key_shards(query_blocks: int, keys: int, sm_count: int) -> int:
+    """The shard count of ``plan_key_shards``."""
+
+    return plan_key_shards(query_blocks, keys, sm_count)[1]
 
 
 # --------------------------------------------------------------------------- stages
@@ -380,13 +399,12 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.physical_keys = int(kv.shape[0]) if tile_table is not None else 0
     sharded = "shard_pairs" in ws.buffers and diag_logits is None
     if sharded:
-        # every (query block, key shard) is a work unit; the shards share the row's threshold and
-        # return pairs, which the merge below turns into the row's ids
+        # the blocks of the last wave are cut into key shards: every (block, shard) is a work unit, the
+        # shards share the row's threshold and return pairs, which the merge below turns into the row's ids
         args.shards = int(ws.shard_pairs.shape[0])
-        args.thresholds_per_row = 1
-        args.out_ids = None
-        args.out_pairs, args.out_counts = ptr(ws.shard_pairs), ptr(ws.shard_counts)
-        args.failure_flags, args.spill = ptr(ws.shard_flags), ptr(ws.shard_spill)
+        args.split_blocks = ws.split_blocks
+        args.shard_pairs, args.shard_counts = ptr(ws.shard_pairs), ptr(ws.shard_counts)
+        args.shard_flags, args.spill = ptr(ws.shard_flags), ptr(ws.shard_spill)
     library = load_library()
     stream = current_stream(torch, ws.device)
     check(library.itk_fused_topk(ctypes.byref(args), stream))
@@ -395,12 +413,13 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         pair_table = _lib.pointer_table([ws.shard_pairs[s] for s in range(shards)])
         count_table = _lib.pointer_table([ws.shard_counts[s] for s in range(shards)])
         # the merge also decides which rows are complete: no shard overflowed and the union holds
-        # min(2048, valid keys) candidates; the others go to the repair graph
+        # min(2048, valid keys) candidates; the others go to the repair graph.  The split blocks are
+        # the first `split_blocks` owned ones.
         check(library.itk_merge_shard_lists(
             pair_table, count_table, shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
             ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows,
             ptr(ws.shard_flags), ptr(ws.failure_flags), ptr(k_start), ptr(k_end), key_lo, args.key_hi,
-            ws.block_begin, ws.block_stride, ws.num_blocks, None, stream))
+            ws.block_begin, ws.block_stride, ws.split_blocks, None, stream))
     return ws.output_ids
 
 
@@ -439,14 +458,14 @@ def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_l
     args.q, args.kv, args.kv_scales, args.weights = ptr(retry.q), ptr(kv), ptr(kv_scales), ptr(retry.weights)
     args.k_start, args.k_end = ptr(retry.k_start), ptr(retry.k_end)
     args.thresholds = ptr(retry.thresholds)
-    args.out_pairs, args.out_counts = ptr(retry.shard_pairs), ptr(retry.shard_counts)
-    args.failure_flags, args.spill = ptr(retry.shard_flags), ptr(retry.spill)
+    args.shard_pairs, args.shard_counts = ptr(retry.shard_pairs), ptr(retry.shard_counts)
+    args.shard_flags, args.spill = ptr(retry.shard_flags), ptr(retry.spill)
     args.status = ptr(ws.status)
     args.rows, args.keys = slots, ws.keys
     args.key_lo, args.key_hi = key_lo, key_hi
     args.shards = retry.shards
+    args.split_blocks = blocks
     args.block_begin, args.block_stride, args.num_blocks = 0, 1, blocks
-    args.thresholds_per_row = 1
     args.exit_when_no_keys = 1
     args.tile_table = ptr(tile_table)
     args.physical_keys = int(kv.shape[0]) if tile_table is not None else 0

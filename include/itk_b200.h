@@ -115,13 +115,16 @@ typedef struct itk_fused_args {
     const float* weights;
     const int32_t* k_start;
     const int32_t* k_end;
-    const float* thresholds;    /* [shards,Q] */
-    int32_t* out_ids;           /* [Q,2048]; may be null when out_pairs is given */
-    uint64_t* out_pairs;        /* optional [shards,Q,2048]: (ordered score << 32) | key */
-    int32_t* out_counts;        /* optional [shards,Q], with out_pairs */
-    uint8_t* failure_flags;     /* [shards,Q]: 1 = row must be repaired */
+    const float* thresholds;    /* [Q] */
+    int32_t* out_ids;           /* [Q,2048]; may be null when out_pairs is given or every block is split */
+    uint64_t* out_pairs;        /* optional [Q,2048]: (ordered score << 32) | key */
+    int32_t* out_counts;        /* optional [Q], with out_pairs */
+    uint8_t* failure_flags;     /* [Q]: 1 = row must be repaired */
     uint64_t* spill;            /* scratch of itk_workspace_sizes.spill_bytes: bounded overflow of the
                                  * shared-memory candidate lists, one region per CTA and unit row */
+    uint64_t* shard_pairs;      /* with shards > 1: [shards,Q,2048] pairs, [shards,Q] counts and [shards,Q] */
+    int32_t* shard_counts;      /* overflow flags of the key shards of the split blocks, for          */
+    uint8_t* shard_flags;       /* itk_merge_shard_lists; rows of whole blocks are not touched        */
     float* diag_logits;         /* optional fp32 [Q,diag_stride] dense scores (-inf outside the range) */
     long long diag_stride;
     long long* trace;           /* optional int64 [CTAs,32] phase trace; selects the diagnostic build.
@@ -137,16 +140,20 @@ typedef struct itk_fused_args {
     int keys;                   /* N */
     int key_lo;                 /* first key scored (multiple of 128) */
     int key_hi;                 /* one past the last key scored */
-    int shards;                 /* key range is cut into this many equal shards (>= 1) */
+    int shards;                 /* the key range of a split block is cut into this many equal shards (>= 1) */
+    int split_blocks;           /* with shards > 1: how many of the owned blocks are split, namely the ones with the
+                                 * lowest block numbers (the fewest keys under a causal mask); 0 = all of them.
+                                 * A launch runs its units in waves of one per SM; splitting the blocks of the
+                                 * last, partly filled wave fills it.  A shard uses the row's threshold and
+                                 * returns everything it found when that is fewer than 2048 candidates; the
+                                 * merge decides whether the row is complete.  Whole blocks write out_ids /
+                                 * out_pairs and failure_flags as with shards = 1. */
     int block_begin;            /* first owned block of 4 query rows */
     int block_stride;           /* stride between owned blocks (number of ranks) */
     int num_blocks;             /* owned blocks */
     int force_compute;          /* 1: score rows even when all their keys are selected anyway */
     int max_ctas;               /* 0 = one CTA per SM; otherwise the grid is capped (the reference plugin's
                                  * debug_ctas option, kernel/plugin.py:95-130) */
-    int thresholds_per_row;     /* with shards > 1: thresholds has [Q] entries (one per row, shared by its
-                                 * shards) and a shard that finds fewer than 2048 candidates returns them
-                                 * all instead of failing; the merge decides whether the row is complete */
     int exit_when_no_keys;      /* 1: return at once, writing nothing, when every row's key range is empty
                                  * (the compacted retry problem of a call without flagged rows) */
     const int32_t* tile_table;  /* paged keys (null = contiguous): physical 128-key tile of each logical
@@ -201,10 +208,10 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream);
 
-/* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1,
- * thresholds_per_row), which also decides per row whether the result is complete:
+/* itk_merge_candidate_lists for the key shards of ONE itk_fused_topk launch (shards > 1),
+ * which also decides per row whether the result is complete:
  * failure_flags[row] = 1 when any shard of the row reported an overflow
- * (shard_flags [sources, rows], the launch's failure_flags) or the union holds fewer than
+ * (shard_flags [sources, rows]) or the union holds fewer than
  * min(2048, number of keys of the row inside [key_lo, key_hi)) pairs, else 0.  Such rows
  * go to the repair graph.  Only the rows of the query blocks block_begin + i * block_stride,
  * i < num_blocks, are merged (num_blocks = 0: every row).  With out_rows (int32 [rows], optional)

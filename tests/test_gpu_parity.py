@@ -345,6 +345,39 @@ def test_key_shards_inside_one_gpu_give_the_unsharded_sets(device, rows, keys, s
     assert operator.auto_key_shards(2, 8192, 148) == 2
 
 
+@pytest.mark.parametrize("rows,keys,shards,split", [(48, 32768, 4, 5), (40, 16384, 2, 1), (30, 65536, 8, 7)])
+def test_only_the_blocks_of_the_last_wave_are_split(device, rows, keys, shards, split):
+    """`split` of the query blocks (the lowest numbered ones) are cut into key shards and merged, the others
+    run as whole units in the same launch; every row must be the exact Top-2048 of the kernel's own scores."""
+
+    host = make_workload_inputs("c2", query_tokens=rows, context_tokens=keys, seed=rows)
+    gpu = inputs_to(host, device)
+    tensors = _tensors(gpu)
+    case = PrefillCase("tail-split", rows, keys, 2048, 0)
+    plain = operator.make_workspace(rows, keys, device, key_shards=1)
+    want = operator.run_operator(plain, *tensors).clone()
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(plain, *tensors, diag_logits=logits)
+    cut = operator.make_workspace(rows, keys, device, key_shards=shards, split_blocks_hint=split)
+    assert cut.split_blocks == split
+    cut.output_ids.fill_(-9)
+    cut.failure_flags.fill_(1)
+    got = operator.run_operator(cut, *tensors)
+    torch.cuda.synchronize()
+    cut.check_status()
+    assert int(cut.failure_flags.sum()) == 0
+    # the whole blocks did not touch the shard buffers
+    assert int(cut.shard_counts[:, 4 * split:].abs().sum()) == 0
+    indices = got.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    verdict = score_threshold_check(indices, logits.cpu(), case)
+    if verdict["rows_with_cutoff_ties"] == 0:
+        assert torch.equal(got.sort(dim=-1).values, want.sort(dim=-1).values)
+    assert operator.plan_key_shards(512, 16384, 148) == (68, 2)
+    assert operator.plan_key_shards(1024, 16384, 148) == (0, 1)
+    assert operator.plan_key_shards(296, 16384, 148) == (0, 1)
+
+
 def test_public_callable_replays_a_graph_with_the_same_result(device):
     """From its second call with the same tensors on the callable replays one CUDA graph."""
 
