@@ -402,6 +402,7 @@ def score_threshold_check(indices: Any, scores: Any, case: PrefillCase, *, name:
     ends = _causal_ends(torch, case, scores.device)
     eligible = (ends > case.top_k).nonzero().flatten()
     tie_rows = 0
+    tie_row_ids: list[int] = []
     if eligible.numel():
         live = scores[eligible]
         cutoff = torch.topk(live, case.top_k, dim=-1, sorted=True).values[:, -1]
@@ -419,12 +420,17 @@ def score_threshold_check(indices: Any, scores: Any, case: PrefillCase, *, name:
             row = int(eligible[int(short[0])])
             raise CorrectnessError(f"{name} row {row} omitted an ID above the TopK cutoff")
         at_cutoff = (live == cutoff[:, None]).sum(dim=1)
-        tie_rows = int((at_cutoff > (case.top_k - above_total)).sum())
+        tied = at_cutoff > (case.top_k - above_total)
+        tie_rows = int(tied.sum())
+        tie_row_ids = eligible[tied].tolist()
     return {
         "status": "passed",
         "policy": "exact_score_threshold",
         "rows_checked": int(eligible.numel()),
         "rows_with_cutoff_ties": tie_rows,
+        # rows in which more keys share the cutoff score than fit: any of them completes an exact Top-K,
+        # so two exact results may differ there
+        "cutoff_tie_rows": tie_row_ids,
     }
 
 

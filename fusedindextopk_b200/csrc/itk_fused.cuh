@@ -69,7 +69,7 @@ constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueThreads = 512;
 constexpr int kEpilogueWarps = kEpilogueThreads / 32;
 constexpr int kScoreBins = 256;
-constexpr int kBinListCap = 64;     // scores of the histogram bin that holds the cutoff; more: radix fallback
+constexpr int kBinListCap = 128;    // scores of the histogram bin that holds the cutoff; more: radix fallback
 
 constexpr uint32_t kQBytes = kUmmaN * kHeadDim;       // 32768
 constexpr uint32_t kKvBytes = kTileKeys * kHeadDim;   // 16384
@@ -134,9 +134,13 @@ struct FusedParams {
 
 // Per-row scratch of the selection.
 struct RowSelect {
-    int hist[256];                      // second-level histogram / digit histogram of the radix fallback
-    uint32_t bin_scores[kBinListCap];   // the candidates of the histogram bin that holds the cutoff
-    int32_t bin_keys[kBinListCap];
+    union {
+        int hist[256];                          // digit histogram of the radix selection, which clears it itself
+        struct {                                // the binned selection, which never runs beside the radix one:
+            uint32_t bin_scores[kBinListCap];   // the candidates of the histogram bin that holds the cutoff
+            int32_t bin_keys[kBinListCap];
+        };
+    };
     int position;     // next free output position of the row
     int bin_count;
     int tickets;
@@ -565,28 +569,47 @@ __device__ __forceinline__ bool binned_select(RowSelect& rs, const RowView& v, u
         const bool found = find_rank(counts, lane, kTopK, cutoff_bin, above, in_list);
         share_rank(found, cutoff_bin, above, in_list);
     }
-    if (cutoff_bin < 0 || in_list > kBinListCap) return false;
-    // Smallest score of bin `b`: start from the arithmetic edge and move by single floats until
-    // bin_of puts the value into bin >= b and its predecessor below; bin_of is monotone in the score.
+    if (cutoff_bin < 0 || in_list > kBinListCap) {
+        if (rb.lap != nullptr) rb.lap[0] = cutoff_bin < 0 ? 1000000 : 2000000 + in_list * 256 + cutoff_bin;
+        return false;
+    }
+    // Smallest score of bin `b` (bin_of is monotone in the score).  Start from the arithmetic edge and
+    // move by single floats; that settles within a step or two unless the edge lies much closer to zero
+    // than the threshold does (a negative threshold, scores around zero): there one float of the edge
+    // is far smaller than the rounding of threshold + distance, and the edge is bisected over the
+    // ordered images of the floats between the threshold and the end of the bins instead.
     const auto lower_edge = [&](int b) -> float {
         if (b <= 0) return threshold;   // every candidate is at or above the threshold
         float edge = threshold + static_cast<float>(b) / bins_per_unit;
 #pragma unroll 1
-        for (int step = 0; step < 64 && bin_of(edge) < b; ++step) edge = neighbour_float(edge, 1);
+        for (int step = 0; step < 8 && bin_of(edge) < b; ++step) edge = neighbour_float(edge, 1);
 #pragma unroll 1
-        for (int step = 0; step < 64; ++step) {
+        for (int step = 0; step < 8; ++step) {
             const float lower = neighbour_float(edge, -1);
             if (bin_of(lower) < b) break;
             edge = lower;
         }
-        return edge;
+        if (bin_of(edge) >= b && bin_of(neighbour_float(edge, -1)) < b) return edge;
+        uint32_t below = ordered_bits(threshold);           // bin 0 < b
+        uint32_t reached = ordered_bits(threshold + width);  // the last bin
+#pragma unroll 1
+        while (reached - below > 1u) {
+            const uint32_t middle = below + ((reached - below) >> 1);
+            if (bin_of(ordered_to_float(middle)) >= b) reached = middle;
+            else below = middle;
+        }
+        return ordered_to_float(reached);
     };
     const float list_from = lower_edge(cutoff_bin);
     const float take_from = cutoff_bin >= kScoreBins - 1 ? __int_as_float(0x7f800000) : lower_edge(cutoff_bin + 1);
     // the edges must agree with the histogram, else the counts would not add up: check them
-    if (bin_of(list_from) != cutoff_bin || (cutoff_bin < kScoreBins - 1 && bin_of(take_from) != cutoff_bin + 1)) return false;
-    if (cutoff_bin > 0 && bin_of(neighbour_float(list_from, -1)) >= cutoff_bin) return false;
-    if (cutoff_bin < kScoreBins - 1 && bin_of(neighbour_float(take_from, -1)) > cutoff_bin) return false;
+    bool edges_ok = bin_of(list_from) == cutoff_bin && (cutoff_bin >= kScoreBins - 1 || bin_of(take_from) == cutoff_bin + 1);
+    edges_ok = edges_ok && !(cutoff_bin > 0 && bin_of(neighbour_float(list_from, -1)) >= cutoff_bin);
+    edges_ok = edges_ok && !(cutoff_bin < kScoreBins - 1 && bin_of(neighbour_float(take_from, -1)) > cutoff_bin);
+    if (!edges_ok) {
+        if (rb.lap != nullptr) rb.lap[0] = 3000000 + cutoff_bin;
+        return false;
+    }
     lap(rb, 2);
     emit_pass<true>(rs, v, lane, out_ids, out_pairs,
                     [&](uint32_t word) {
@@ -608,7 +631,7 @@ __device__ __forceinline__ bool binned_select(RowSelect& rs, const RowView& v, u
         const int need = kTopK - above;
         in_list = min(in_list, kBinListCap);
 #pragma unroll 1
-        for (int k = 0; k < kBinListCap / 32; ++k) {
+        for (int k = 0; k * 32 < in_list; ++k) {
             const int i = lane + 32 * k;
             const uint32_t mine = i < in_list ? rs.bin_scores[i] : 0u;
             int before = 0;
@@ -826,6 +849,10 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
             const float width = 4.0f * __uint_as_float(scale_bits);
             const bool usable = scale_bits != 0u && width < 3.0e38f;
             if (!usable || !binned_select(rs, view, row_hist, threshold, width, rb, tid, out_ids, out_pairs)) {
+                if (rb.lap != nullptr) {
+                    rb.lap[7] += 1;
+                    if (!usable) rb.lap[0] = 4000000;
+                }
                 uint32_t cutoff;
                 int equal_needed;
                 radix_select<true>(rs, view, rb, tid, kTopK, cutoff, equal_needed);
@@ -1747,6 +1774,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 cta_trace[30] = laps[4];   // list ranking
                 cta_trace[31] = laps[5];   // whole selection incl. fallback
                 cta_trace[20] = laps[6];   // clean-up
+                cta_trace[5] = laps[7];    // rows (of the unit's first row slot) that fell back to the radix selection
+                cta_trace[6] = laps[0];    // why the last of them did
                 cta_trace[kTraceNsEnd] = global_timer_ns();
             }
         }

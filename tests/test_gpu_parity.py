@@ -503,8 +503,11 @@ def test_full_size_parity(device, workload, rows, keys):
     again = ws.output_ids.unsqueeze(1).contiguous()
     validate_topk_indices(again, case)
     score_threshold_check(again, logits, case)
-    if workload != "c4":
-        assert torch.equal(first.sort(dim=-1).values, again.sort(dim=-1).values)
+    # the production build returns the same sets, except that a row whose cutoff score is shared by more
+    # keys than fit may complete its Top-K with any of them
+    same = torch.ones(rows, dtype=torch.bool, device=device)
+    same[torch.tensor(own["cutoff_tie_rows"], dtype=torch.long, device=device)] = False
+    assert torch.equal(first[same].sort(dim=-1).values, again[same].sort(dim=-1).values)
 
     sample = torch.linspace(0, rows - 1, min(rows, ORACLE_ROWS)).round().long().unique()
     want = oracle.dense_logits(host.q[sample], host.kv, host.kv_scales, host.weights[sample], host.k_start[sample],
