@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "itk_repair_produce", "itk_chunk_local_topk", "itk_merge_topk_pairs", "itk_finalize_repair",
     "itk_merge_candidate_lists", "itk_fused_topk_static", "itk_quantize_rows_e4m3",
     "itk_gather_sampled_kv_paged", "itk_repair_produce_paged", "itk_merge_shard_lists",
-    "itk_compact_flagged_rows", "itk_repair_merge_chunk",
+    "itk_compact_flagged_rows", "itk_repair_merge_chunk", "itk_flagged_scope_begin", "itk_flagged_scope_end",
 )
 
 
@@ -105,6 +105,8 @@ def load_library() -> ctypes.CDLL:
         [POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int]
         + [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]
     )
+    library.itk_flagged_scope_begin.argtypes = [c_void_p, c_int, c_void_p, POINTER(c_void_p)]
+    library.itk_flagged_scope_end.argtypes = [c_void_p, c_void_p]
     library.itk_compact_flagged_rows.argtypes = [c_void_p] * 5 + [c_int, c_int] + [c_void_p] * 6
     library.itk_repair_merge_chunk.argtypes = (
         [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 4

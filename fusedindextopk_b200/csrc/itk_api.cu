@@ -84,6 +84,7 @@ constexpr int kMaxDevices = 64;
 std::mutex g_init_mutex;
 bool g_initialised[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
+cudaStream_t g_body_stream[kMaxDevices] = {};   // captures the body of a conditional graph node
 
 constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairCapacity) * sizeof(uint64_t);
 constexpr int kShardMergeCapacity = 6144;   // pairs staged per row by the merge of one launch's key shards
@@ -113,6 +114,11 @@ int init_current_device(int* device_out) {
         ITK_CUDA(raise_smem(itk_fused_kernel<kModeRepair, false, true>, kFusedSmemBytes));
         ITK_CUDA(raise_smem(itk_pair_topk_kernel, kPairSmemBytes));
         g_sm_count[device] = properties.multiProcessorCount;
+        // (a stream cannot be created while this thread captures in the global mode; the scope then stays unconditional)
+        if (cudaStreamCreateWithFlags(&g_body_stream[device], cudaStreamNonBlocking) != cudaSuccess) {
+            g_body_stream[device] = nullptr;
+            (void)cudaGetLastError();
+        }
         g_initialised[device] = true;
     }
     if (device_out != nullptr) *device_out = device;
@@ -586,6 +592,50 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
     if (grid > items) grid = items;
     itk_pair_topk_kernel<<<grid, kPairThreads, smem, stream>>>(params);
     return launch_check("itk_pair_topk_kernel (lists)");
+}
+
+int itk_flagged_scope_begin(const uint8_t* failure_flags, int rows, itk_stream_t stream, itk_stream_t* body_stream) {
+    ITK_REQUIRE(failure_flags != nullptr && rows > 0 && body_stream != nullptr, "need failure_flags, rows > 0 and body_stream");
+    *body_stream = stream;   // outside a capture, or when a step below is refused: the launches run as they are
+    int device = 0;
+    const int rc = init_current_device(&device);
+    if (rc != ITK_OK) return rc;
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    cudaGraph_t graph = nullptr;
+    const cudaGraphNode_t* dependencies = nullptr;
+    size_t count = 0;
+    ITK_CUDA(cudaStreamGetCaptureInfo_v2(stream, &status, nullptr, &graph, &dependencies, &count));
+    if (status != cudaStreamCaptureStatusActive || g_body_stream[device] == nullptr) return ITK_OK;
+    cudaGraphConditionalHandle condition;
+    if (cudaGraphConditionalHandleCreate(&condition, graph, 0, cudaGraphCondAssignDefault) != cudaSuccess) {
+        (void)cudaGetLastError();   // no conditional nodes here: stay unconditional
+        return ITK_OK;
+    }
+    // from here on the capture is being changed: a failure is an error of the call
+    itk_any_flag_kernel<<<1, 256, 0, stream>>>(condition, failure_flags, rows);
+    const int launched = launch_check("itk_any_flag_kernel");
+    if (launched != ITK_OK) return launched;
+    ITK_CUDA(cudaStreamGetCaptureInfo_v2(stream, &status, nullptr, &graph, &dependencies, &count));
+    cudaGraphNodeParams node_params{};
+    node_params.type = cudaGraphNodeTypeConditional;
+    node_params.conditional.handle = condition;
+    node_params.conditional.type = cudaGraphCondTypeIf;
+    node_params.conditional.size = 1;
+    cudaGraphNode_t node = nullptr;
+    ITK_CUDA(cudaGraphAddNode(&node, graph, dependencies, count, &node_params));
+    // what the caller enqueues on `stream` after the scope comes after the conditional node
+    ITK_CUDA(cudaStreamUpdateCaptureDependencies(stream, &node, 1, cudaStreamSetCaptureDependencies));
+    cudaGraph_t body = node_params.conditional.phGraph_out[0];
+    ITK_CUDA(cudaStreamBeginCaptureToGraph(g_body_stream[device], body, nullptr, nullptr, 0, cudaStreamCaptureModeRelaxed));
+    *body_stream = g_body_stream[device];
+    return ITK_OK;
+}
+
+int itk_flagged_scope_end(itk_stream_t stream, itk_stream_t body_stream) {
+    if (body_stream == stream || body_stream == nullptr) return ITK_OK;
+    cudaGraph_t body = nullptr;
+    ITK_CUDA(cudaStreamEndCapture(body_stream, &body));
+    return ITK_OK;
 }
 
 int itk_compact_flagged_rows(const uint8_t* failure_flags, const void* q, const float* weights, const int32_t* k_start,

@@ -133,6 +133,17 @@ __global__ void __launch_bounds__(kCompactThreads) itk_compact_flagged_kernel(
     }
 }
 
+// ------------------------------------------------------------------ is any row flagged?
+
+// Sets the condition of a graph's IF node: 1 when any row is flagged, else 0.  One CTA.
+__global__ void __launch_bounds__(256) itk_any_flag_kernel(cudaGraphConditionalHandle condition,
+                                                            const uint8_t* __restrict__ flags, int rows) {
+    int any = 0;
+    for (int i = static_cast<int>(threadIdx.x); i < rows; i += static_cast<int>(blockDim.x)) any |= flags[i];
+    any = __syncthreads_or(any);
+    if (threadIdx.x == 0) cudaGraphSetConditional(condition, any != 0 ? 1u : 0u);
+}
+
 // ------------------------------------------------------------------ pair reducers
 
 struct PairSource {

@@ -75,6 +75,7 @@ class SamplePlan:
 # shards each that is one wave of CTAs); rows beyond it go straight to the dense repair.
 RETRY_SLOTS = 32
 RETRY_TARGET_FACTOR = 2      # the retry threshold aims at this many times the first pass's candidates
+CONDITIONAL_REPAIR_MIN_LAUNCHES = 9
 
 
 def make_sample_plan(context_tokens: int, *, seed: int, device: Any, guard_sigmas: float = 2.0) -> SamplePlan:
@@ -425,7 +426,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
 
 @_on_workspace_device
 def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
-              key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
+              key_hi: int | None = None, want_pairs: bool = False, tile_table=None, stream: int | None = None) -> Any:
     """Flagged rows once more, with a lower threshold and a candidate list per key shard.
 
     Four launches, all of them over the compact problem of ``RETRY_SLOTS`` rows and returning at once
@@ -441,7 +442,8 @@ def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_l
     if retry is None:
         return ws.output_ids
     library = load_library()
-    stream = current_stream(torch, ws.device)
+    if stream is None:
+        stream = current_stream(torch, ws.device)
     slots = int(retry.slot_rows.shape[0])
     key_hi = ws.keys if key_hi is None else key_hi
     check(library.itk_compact_flagged_rows(
@@ -492,28 +494,39 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
 
     import torch
 
-    if retry:
-        run_retry(ws, q, kv, kv_scales, weights, k_start, k_end, key_lo=key_lo, key_hi=key_hi,
-                  want_pairs=want_pairs, tile_table=tile_table)
     library = load_library()
-    stream = current_stream(torch, ws.device)
+    outer = current_stream(torch, ws.device)
     key_hi = ws.keys if key_hi is None else key_hi
     physical_keys = int(kv.shape[0]) if tile_table is not None else 0
     chunks = [(lo, min(ws.keys, lo + _lib.REPAIR_CHUNK)) for lo in range(0, ws.keys, _lib.REPAIR_CHUNK)]
     chunks = [(lo, hi) for lo, hi in chunks if hi > key_lo and lo < key_hi]
-    for index, (chunk_lo, chunk_hi) in enumerate(chunks):
-        check(library.itk_repair_produce_paged(
-            ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
-            ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
-            ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
-        ))
-        last = index == len(chunks) - 1
-        check(library.itk_repair_merge_chunk(
-            ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.repair_pairs), ptr(k_start), ptr(k_end),
-            chunk_lo, chunk_hi, ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows,
-            1 if index == 0 else 0, 1 if last else 0, ptr(ws.output_ids),
-            ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None, stream,
-        ))
+    # Inside a graph capture the whole stage can be the body of an IF node on "some row is flagged".  A replay
+    # without flagged rows then pays for the node (about 13 us) instead of about 1.5 us per launch that
+    # returns at once, which is the better deal from nine launches on (contexts beyond 32 K keys).
+    launches = (4 if retry and ws.retry is not None else 0) + 2 * len(chunks)
+    body = ctypes.c_void_p(outer)
+    if launches >= CONDITIONAL_REPAIR_MIN_LAUNCHES:
+        check(library.itk_flagged_scope_begin(ptr(ws.failure_flags), ws.rows, outer, ctypes.byref(body)))
+    stream = body.value
+    try:
+        if retry:
+            run_retry(ws, q, kv, kv_scales, weights, k_start, k_end, key_lo=key_lo, key_hi=key_hi,
+                      want_pairs=want_pairs, tile_table=tile_table, stream=stream)
+        for index, (chunk_lo, chunk_hi) in enumerate(chunks):
+            check(library.itk_repair_produce_paged(
+                ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
+                ptr(ws.repair_pairs), ws.rows, ws.keys, chunk_lo, chunk_hi, ws.block_begin, ws.block_stride,
+                ws.num_blocks, ptr(tile_table), physical_keys, ptr(ws.status), stream,
+            ))
+            last = index == len(chunks) - 1
+            check(library.itk_repair_merge_chunk(
+                ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.repair_pairs), ptr(k_start), ptr(k_end),
+                chunk_lo, chunk_hi, ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows,
+                1 if index == 0 else 0, 1 if last else 0, ptr(ws.output_ids),
+                ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None, stream,
+            ))
+    finally:
+        check(library.itk_flagged_scope_end(outer, stream))
     return ws.output_ids
 
 

@@ -224,6 +224,18 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
                           const int32_t* k_end, int key_lo, int key_hi, int block_begin, int block_stride,
                           int num_blocks, const int32_t* out_rows, itk_stream_t stream);
 
+/* A scope of launches that only matter when a row is flagged (the whole repair stage).  When `stream`
+ * is being captured into a CUDA graph, begin adds a one-CTA kernel that looks at failure_flags [rows]
+ * and an IF node after it, and returns in *body_stream a stream that captures the node's body: what
+ * the caller launches on it until itk_flagged_scope_end runs, in a replay, only if some row was
+ * flagged; a replay without flagged rows then pays for two graph nodes instead of for every launch of
+ * the stage.  Work enqueued on `stream` after the scope is ordered after the body.  Outside a capture
+ * (or where the driver offers no conditional nodes) *body_stream is `stream` itself and the launches
+ * run as they are; each of them returns at once on the device when it finds no flagged row.  The
+ * reference launches its repair graph unconditionally (src/fused_index_topk/kernel/plugin.py:333-377). */
+int itk_flagged_scope_begin(const uint8_t* failure_flags, int rows, itk_stream_t stream, itk_stream_t* body_stream);
+int itk_flagged_scope_end(itk_stream_t stream, itk_stream_t body_stream);
+
 /* First stage of the retry of flagged rows: the b-th flagged row (in row order) becomes row b of a
  * compact problem of `slots` rows: its query tile, head weights and key range are copied to
  * q_out [slots,64,128], weights_out [slots,64], k_start_out / k_end_out [slots], and slot_rows[b]

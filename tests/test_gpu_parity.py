@@ -378,6 +378,42 @@ def test_only_the_blocks_of_the_last_wave_are_split(device, rows, keys, shards, 
     assert operator.plan_key_shards(296, 16384, 148) == (0, 1)
 
 
+def test_repair_stage_is_a_conditional_part_of_a_captured_graph(device):
+    """Captured into a CUDA graph the repair stage is the body of an IF node on "some row is flagged".  One graph,
+    replayed with thresholds that flag no row, then every row (+inf: the retry repairs 32 of them, the dense
+    rescan the other 8), then none again, must give the exact result each time and leave no flag."""
+
+    rows, keys = 40, 50000   # four chunks: enough launches for the stage to be made conditional
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=9)
+    gpu = inputs_to(host, device)
+    tensors = _tensors(gpu)
+    case = PrefillCase("conditional", rows, keys, 2048, 0)
+    assert 4 + 2 * 4 >= operator.CONDITIONAL_REPAIR_MIN_LAUNCHES
+    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed)
+    sampled = operator.run_sample_thresholds(ws, *tensors).clone()
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(ws, *tensors, diag_logits=logits, force_compute=True)
+    thresholds = sampled.clone()
+    fast_flags = torch.zeros_like(ws.failure_flags)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        operator.run_fused_topk(ws, *tensors, thresholds=thresholds)
+        fast_flags.copy_(ws.failure_flags)
+        operator.run_repair(ws, *tensors)
+    for fill, flagged in ((None, 0), (math.inf, rows), (None, 0), (math.inf, rows)):
+        thresholds.copy_(sampled) if fill is None else thresholds.fill_(fill)
+        ws.output_ids.fill_(-3)
+        graph.replay()
+        torch.cuda.synchronize()
+        ws.check_status()
+        assert int(fast_flags.sum()) == flagged
+        assert int(ws.failure_flags.sum()) == 0 and int(ws.repair_error_flags.sum()) == 0
+        indices = ws.output_ids.unsqueeze(1).contiguous().cpu()
+        validate_topk_indices(indices, case)
+        score_threshold_check(indices, logits.cpu(), case)
+
+
 def test_public_callable_replays_a_graph_with_the_same_result(device):
     """From its second call with the same tensors on the callable replays one CUDA graph."""
 
