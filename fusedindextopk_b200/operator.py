@@ -272,7 +272,7 @@ def _make_retry_buffers(rows: int, keys: int, device: Any) -> RetryBuffers:
 # Cost model of one launch of the fused kernel, in microseconds (B200, measured): a 128-key tile of a unit,
 # a full selection per unit, a selection that only copies (a shard that found fewer than 2048 candidates),
 # the fixed cost of a unit, and the merge of a row's shard lists (one CTA per row).
-_TILE_US, _SELECT_US, _COPY_US, _UNIT_US, _MERGE_ROW_US, _MERGE_LAUNCH_US = 0.72, 16.0, 4.0, 3.0, 6.0, 6.0
+_TILE_US, _SELECT_US, _COPY_US, _UNIT_US, _MERGE_ROW_US, _MERGE_LAUNCH_US = 0.70, 16.0, 4.0, 3.0, 12.0, 5.0
 
 
 def plan_key_shards(query_blocks: int, keys: int, sm_count: int) -> tuple[int, int]:
@@ -299,7 +299,7 @@ def plan_key_shards(query_blocks: int, keys: int, sm_count: int) -> tuple[int, i
         time = waves * (_UNIT_US + tiles / shards * _TILE_US + select)
         if shards > 1:
             time += _MERGE_LAUNCH_US + -(-tail * 4 // (3 * sm_count)) * _MERGE_ROW_US
-        if best_time is None or time < best_time * 0.97:   # a new count must win by 3 % to be taken
+        if best_time is None or time < best_time * 0.95:   # a new count must win by 5 % to be taken
             best, best_time = shards, time
     return (tail, best) if best > 1 else (0, 1)
 
