@@ -64,6 +64,8 @@ class FusedArgs(ctypes.Structure):
         ("split_blocks", c_int), ("block_begin", c_int), ("block_stride", c_int), ("num_blocks", c_int),
         ("force_compute", c_int), ("max_ctas", c_int), ("exit_when_no_keys", c_int),
         ("tile_table", c_void_p), ("physical_keys", c_int),
+        ("sampled_kv", c_void_p), ("sampled_scales", c_void_p), ("sample_ids", c_void_p), ("thresholds_out", c_void_p),
+        ("samples", c_int), ("sample_rank", c_int), ("target_candidates", c_int),
     ]
 
 

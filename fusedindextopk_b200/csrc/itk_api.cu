@@ -394,6 +394,24 @@ int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream) {
     params.num_blocks = a.num_blocks;
     params.top_k_min_valid = a.force_compute ? 0 : kTopK;
     params.exit_when_no_keys = a.exit_when_no_keys != 0 ? 1 : 0;
+    if (a.sampled_kv != nullptr) {
+        ITK_REQUIRE(a.sampled_scales && a.sample_ids && a.thresholds_out, "in-kernel thresholds need sampled_scales, sample_ids, thresholds_out");
+        ITK_REQUIRE(a.samples > 0 && a.samples <= kRowCap - kSegments * 32 && a.samples <= kTopK,
+                    "at most %d samples fit the shared-memory candidate segments", kTopK);
+        ITK_REQUIRE(a.sample_rank >= 1 && a.sample_rank <= a.samples, "sample_rank must lie in [1, samples]");
+        ITK_REQUIRE(a.target_candidates > 0, "target_candidates must be positive");
+        ITK_REQUIRE(a.key_lo == 0 && a.key_hi == a.keys, "in-kernel thresholds need the whole key range");
+        ITK_REQUIRE(a.diag_logits == nullptr, "in-kernel thresholds are not offered with diag_logits");
+        ITK_REQUIRE(aligned16(a.sampled_kv), "sampled_kv must be 16-byte aligned");
+        if ((rc = make_row_map(&params.map_sample, a.sampled_kv, a.samples, kTileKeys)) != ITK_OK) return rc;
+        params.sample_scales = a.sampled_scales;
+        params.sample_ids = a.sample_ids;
+        params.thresholds_out = a.thresholds_out;
+        params.sample_count = a.samples;
+        params.sample_tiles = (a.samples + kTileKeys - 1) / kTileKeys;
+        params.sample_rank = a.sample_rank;
+        params.target_candidates = a.target_candidates;
+    }
     const long long units = (a.num_blocks - split_blocks) + static_cast<long long>(split_blocks) * a.shards;
     return launch_fused<kModeTopK>(params, a.diag_logits != nullptr || a.trace != nullptr,
                                    fused_grid(device, units, a.max_ctas), stream);

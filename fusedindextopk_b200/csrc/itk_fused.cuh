@@ -91,6 +91,8 @@ constexpr int kTraceSm = 24, kTraceNsBegin = 25, kTraceNsEnd = 26;
 struct FusedParams {
     CUtensorMap map_q;    // [rows*64, 128] bytes, box 256 x 128, 128-byte swizzle
     CUtensorMap map_kv;   // [keys, 128] bytes (PAGED: the physical pool), box 128 x 128, 128-byte swizzle
+    CUtensorMap map_sample;     // [samples, 128] gathered sample keys, kModeTopK with sample_tiles > 0
+    const float* sample_scales; // [samples]           their scales
     const float* kv_scales;     // [keys] (PAGED: [physical keys])
     const int32_t* tile_table;  // PAGED builds: physical 128-key tile of every logical tile, [ceil(keys/128)]
     const float* weights;       // [rows, 64]
@@ -126,8 +128,11 @@ struct FusedParams {
     int block_begin;            // first owned query block
     int block_stride;           // stride between owned query blocks
     int num_blocks;             // owned query blocks
-    int sample_rank;            // kModeSample
-    int target_candidates;      // kModeSample
+    int sample_rank;            // kModeSample, and kModeTopK with sample_tiles > 0
+    int target_candidates;      // the same
+    int sample_tiles;           // kModeTopK, > 0: a whole block scores the sample_count gathered sample keys (that many
+    int sample_count;           // 128-key tiles) in front of its own keys and takes its rows' thresholds from them
+                                // (written to thresholds_out as well), instead of reading `thresholds`
     int top_k_min_valid;        // rows with at most this many valid keys need no selection (= 2048)
     int exit_when_no_keys;      // 1: return at once when every row's key range is empty (nothing is written then)
 };
@@ -160,6 +165,7 @@ struct __align__(16) FusedShared {
     int counts[kBlockQ][kSegments];         // candidates of every (row, segment) in shared memory
     int spill_counts[kBlockQ][kSegments];   // candidates that went (or would have gone) to the segment's spill
     uint32_t scale_part[kBlockQ][kSegments];   // sampled median distance to the threshold, per segment
+    float unit_threshold[kBlockQ];             // thresholds the unit computed itself (sample_tiles > 0)
     RowSelect select[kBlockQ];
     uint32_t tmem_base;
     int abort;
@@ -210,6 +216,7 @@ struct Unit {
     int key_hi;
     int tile_begin;  // global tile indices (key >> 7)
     int tile_end;    // tile_begin == tile_end: nothing to compute
+    int sample_tiles;  // tiles of gathered sample keys in front of the unit's own (its rows' thresholds come from them)
 };
 
 // Unit `iter` of this CTA.  Units are ordered longest first (later query blocks
@@ -269,6 +276,7 @@ __device__ __forceinline__ bool load_unit(const FusedParams& p, int iter, Unit& 
         u.tile_begin = 0;
         u.tile_end = 0;
     }
+    u.sample_tiles = (MODE == kModeTopK && !u.split && hi > lo) ? p.sample_tiles : 0;
     return true;
 }
 
@@ -793,8 +801,8 @@ __device__ __forceinline__ void select_topk_row(FusedShared& sh, const FusedPara
     RowSelect& rs = sh.select[r];
     const int lane = tid & 31;
     const int segment = tid >> 5;
-    const float threshold =
-        valid > kTopK ? __ldg(p.thresholds + row) : __int_as_float(0xff800000);
+    const float threshold = valid > kTopK ? (u.sample_tiles > 0 ? sh.unit_threshold[r] : __ldg(p.thresholds + row))
+                                          : __int_as_float(0xff800000);
     RowView view;
     view.segment = segment;
     view.scores = sh.cand_scores[r] + segment * kSegCap;
@@ -988,7 +996,10 @@ __device__ __forceinline__ bool sample_threshold_row(FusedShared& sh, const Fuse
             result = ordered_to_float(cutoff);
         }
     }
-    if (solo ? tid == (r & 3) * 32 : tid == 0) p.thresholds_out[row] = result;
+    if (solo ? tid == (r & 3) * 32 : tid == 0) {
+        p.thresholds_out[row] = result;
+        sh.unit_threshold[r] = result;   // read by the row's warps after their next barrier
+    }
     return solo;
 }
 
@@ -1409,6 +1420,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
         fence_mbar_init();
         prefetch_tensormap(&p.map_q);
         prefetch_tensormap(&p.map_kv);
+        if (MODE == kModeTopK && p.sample_tiles > 0) prefetch_tensormap(&p.map_sample);
     }
     if (warp == 1) {
         tmem_alloc(&sh.tmem_base, kTmemColumns);
@@ -1442,13 +1454,19 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 mbar_arrive_expect_tx(&sh.w_full[ws], w_bytes);
                 bulk_load(sh.weights[ws], p.weights + static_cast<long long>(u.row0) * kHeads, w_bytes,
                           &sh.w_full[ws]);
-                for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
+                // the gathered sample keys first (when the unit takes its thresholds from them), then its own
+                for (int t = u.tile_begin - u.sample_tiles; t < u.tile_end; ++t, ++kv_iter) {
                     const int stage = kv_iter % kKvStages;
                     ok = timed_wait<DIAG>(&sh.tile_done[stage], ((kv_iter / kKvStages) & 1) ^ 1, ctl, wait_kv);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&sh.kv_full[stage], kKvBytes);
-                    tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0,
-                                (PAGED ? __ldg(p.tile_table + t) : t) * kTileKeys);
+                    if (t < u.tile_begin) {
+                        tma_load_2d(smem_kv + stage * kKvBytes, &p.map_sample, &sh.kv_full[stage], 0,
+                                    (t - u.tile_begin + u.sample_tiles) * kTileKeys);
+                    } else {
+                        tma_load_2d(smem_kv + stage * kKvBytes, &p.map_kv, &sh.kv_full[stage], 0,
+                                    (PAGED ? __ldg(p.tile_table + t) : t) * kTileKeys);
+                    }
                 }
                 ++q_iter;
             }
@@ -1486,7 +1504,7 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
                 // needs for them, so the barriers of tile t+1 are probed while the UMMAs of tile t
                 // execute; the blocking waits at the top are normally satisfied already.
                 bool acc_ready = false, kv_ready = false;
-                for (int t = u.tile_begin; t < u.tile_end; ++t, ++kv_iter) {
+                for (int t = u.tile_begin - u.sample_tiles; t < u.tile_end; ++t, ++kv_iter) {
                     const int buffer = kv_iter & 1;
                     const int stage = kv_iter % kKvStages;
                     if (!acc_ready) {
@@ -1700,6 +1718,55 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             // buffer; the other three epilogue warps of the scheduler cover the TMEM latency.  The
             // accumulator buffer goes back to the UMMA issuer as soon as the second fragment has landed.
             uint32_t frag[32];
+            if (MODE == kModeTopK && u.sample_tiles > 0) {
+                // The unit's first tiles are the gathered sample keys: score them like any tile, keep the
+                // scores of samples inside the row's key range as a dense segment, and let the row's warps
+                // pick the threshold from them (the arithmetic and the choice of the sample kernel).
+                const int start = own_r < u.nrows ? __ldg(p.k_start + u.row0 + own_r) : 0;
+                const int end = own_r < u.nrows ? __ldg(p.k_end + u.row0 + own_r) : 0;
+                const unsigned sample_span = end - start > p.target_candidates ? static_cast<unsigned>(end - start) : 0u;
+                int sampled = 0;
+                for (int st = 0; st < u.sample_tiles; ++st, ++acc_iter) {
+                    const int sample = st * kTileKeys + own_key;
+                    const bool sample_ok = sample < p.sample_count;
+                    const float sample_scale = sample_ok ? __ldg(p.sample_scales + sample) : 0.0f;
+                    const int position = sample_ok ? __ldg(p.sample_ids + sample) : 0x7fffffff;
+                    ok = warp_tile_wait<DIAG>(tile_done_bars + 8u * static_cast<uint32_t>(acc_iter % kKvStages),
+                                              (acc_iter / kKvStages) & 1, ctl, wait_acc);
+                    if (!ok) break;
+                    tcgen05_fence_after_sync();
+                    const uint32_t taddr = tmem_lane + static_cast<uint32_t>((acc_iter & 1) * kUmmaN);
+                    tmem_load_frag(taddr, frag);
+                    uint64_t acc_a, acc_b;
+                    tmem_load_wait(frag);
+                    fragment_fma(frag, w, acc_a, acc_b);
+                    tmem_load_frag(taddr + (16u << 16), frag);
+                    const float sum0 = pair_sum(acc_a), sum1 = pair_sum(acc_b);
+                    tmem_load_wait(frag);
+                    tcgen05_fence_before_sync();
+                    mbar_arrive_elected(acc_empty_bars + 8u * static_cast<uint32_t>(acc_iter & 1));
+                    fragment_fma(frag, w, acc_a, acc_b);
+                    const float score = __fmaf_rn(quad_reduce(sum0, sum1, pair_sum(acc_a), pair_sum(acc_b)), sample_scale, 0.0f);
+                    const uint32_t bits = __float_as_uint(score);
+                    const bool active = static_cast<unsigned>(position - start) < sample_span &&
+                                        fabsf(score) <= 3.4028234663852886e38f;   // finite
+                    const unsigned ballot = __ballot_sync(0xffffffffu, active);
+                    const int slot_at = sampled + __popc(ballot & lanemask_lt());
+                    sampled += __popc(ballot);
+                    if (active && slot_at < kSegCap)
+                        sh.cand_scores[own_r][quarter * kSegCap + slot_at] =
+                            bits ^ (static_cast<uint32_t>(static_cast<int32_t>(bits) >> 31) | 0x80000000u);
+                }
+                if (!ok) break;
+                if (lane == 0) sh.counts[own_r][quarter] = sampled;
+                row_sync(rb);   // the four segments of the row are complete and counted
+                bool solo = false;
+                if (own_r < u.nrows) solo = sample_threshold_row(sh, p, u, own_r, true, rb, quarter * 32 + lane);
+                if (solo && quarter != (own_r & 3)) row_sync_parked(rb);
+                else row_sync(rb);   // the threshold is in shared memory, the segments may be written again
+                if (row_span != 0u && row.hi - row.lo > kTopK) threshold = sh.unit_threshold[own_r];
+                keep_in_register(threshold);
+            }
             float scale, next_scale = 0.0f;
             int range_key = 0, next_range_key = 0;   // sample mode only
             per_key(u.tile_begin, scale, range_key);

@@ -335,8 +335,13 @@ def _on_workspace_device(function):
 
 @_on_workspace_device
 def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None,
-                          trace=None, tile_table=None) -> Any:
-    """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph."""
+                          trace=None, tile_table=None, only_blocks: int | None = None) -> Any:
+    """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph.
+
+    ``only_blocks`` limits the threshold launch to the first that many owned query blocks (0: the
+    sample keys are gathered and nothing else), for calls whose other blocks take their thresholds
+    inside the fused launch.
+    """
 
     import torch
 
@@ -350,13 +355,15 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
         ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(tile_table), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
         ws.keys, int(kv.shape[0]), plan.sample_elements, stream,
     ))
-    check(library.itk_sample_thresholds(
-        ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
-        ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
-        plan.target_candidates, ws.block_begin, ws.block_stride, ws.num_blocks, 0,
-        ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
-        ptr(trace), ptr(ws.status), stream,
-    ))
+    blocks = ws.num_blocks if only_blocks is None else min(only_blocks, ws.num_blocks)
+    if blocks > 0:
+        check(library.itk_sample_thresholds(
+            ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
+            ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
+            plan.target_candidates, ws.block_begin, ws.block_stride, blocks, 0,
+            ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
+            ptr(trace), ptr(ws.status), stream,
+        ))
     return ws.thresholds
 
 
@@ -364,11 +371,14 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
 def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, thresholds=None,
                    diag_logits=None, trace=None, force_compute: bool = False, max_ctas: int = 0,
                    wait_limit_ns: int = 0, withhold_loads: bool = False,
-                   key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False, tile_table=None) -> Any:
+                   key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False, tile_table=None,
+                   thresholds_in_kernel: bool = False) -> Any:
     """Stage ``fused_topk``: one launch of the persistent fused kernel.
 
     With ``tile_table`` (int32, one physical 128-key tile per logical tile) ``kv`` and ``kv_scales`` are
-    the physical pool of a paged key cache.
+    the physical pool of a paged key cache.  With ``thresholds_in_kernel`` the whole blocks score the
+    gathered sample keys themselves and write their thresholds to ``ws.thresholds``; only the rows of
+    split blocks need thresholds from ``run_sample_thresholds`` then.
     """
 
     import torch
@@ -398,6 +408,13 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.max_ctas = max_ctas
     args.tile_table = ptr(tile_table)
     args.physical_keys = int(kv.shape[0]) if tile_table is not None else 0
+    if thresholds_in_kernel:
+        _require(thresholds is None and diag_logits is None and ws.plan.enabled,
+                 "thresholds_in_kernel needs the workspace's own thresholds, a sample plan and no dense output")
+        plan = ws.plan
+        args.sampled_kv, args.sampled_scales = ptr(ws.sampled_kv), ptr(ws.sampled_scales)
+        args.sample_ids, args.thresholds_out = ptr(plan.sample_ids), ptr(ws.thresholds)
+        args.samples, args.sample_rank, args.target_candidates = plan.sample_elements, plan.sample_rank, plan.target_candidates
     sharded = "shard_pairs" in ws.buffers and diag_logits is None
     if sharded:
         # the blocks of the last wave are cut into key shards: every (block, shard) is a work unit, the
@@ -530,11 +547,19 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
     return ws.output_ids
 
 
+# Up to this many sample keys the threshold of a row is picked by one warp, which is cheap enough to do
+# inside the fused launch (four sample tiles in front of a block's own keys): contexts up to 32 K keys.
+IN_KERNEL_THRESHOLD_SAMPLES = 512
+
+
 def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, tile_table=None) -> Any:
     """Sampling + fused kernel + repair on the current stream; returns ``ws.output_ids``."""
 
-    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
-    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
+    in_kernel = ws.plan.enabled and ws.plan.sample_elements <= IN_KERNEL_THRESHOLD_SAMPLES
+    # the separate threshold launch serves the rows of split blocks (all rows when the fused launch does not sample)
+    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table,
+                          only_blocks=ws.split_blocks if in_kernel else None)
+    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table, thresholds_in_kernel=in_kernel)
     if "repair_pairs" in ws.buffers:
         run_repair(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
     return ws.output_ids
@@ -639,14 +664,16 @@ def _warn_once(message: str) -> None:
 class HostPipeline:
     """The operator for callers whose tensors live in pinned host memory.
 
-    Query rows are independent, so the call is cut into a few row chunks that flow through three
+    Query rows are independent, so the call is cut into a few row chunks that flow through four
     streams: host-to-device copies of chunk c+1, the operator on chunk c and the device-to-host
     copy of the ids of chunk c-1 overlap (the PCIe link is full duplex and the copy engines run
-    beside the SMs).  Keys and scales are copied once, ahead of the first chunk.  Chunks are whole
-    multiples of 148 work units (592 rows) where the row count allows, so that every chunk fills
-    the persistent kernel's CTAs evenly; the short chunk goes first, which also shortens the
-    time before the first kernel can start.  Everything is allocated here, nothing per call, and
-    repeated calls with the same host tensors replay one CUDA graph.
+    beside the SMs).  Keys, scales and the small per-row tensors are copied once, ahead of the first
+    chunk.  Chunks are whole multiples of 148 work units (592 rows) where the row count allows, so that
+    every chunk fills the persistent kernel's CTAs evenly; the short chunk goes first, which also
+    shortens the time before the first kernel can start.  Consecutive chunks run on two alternating
+    compute streams: the CTAs of chunk c+1 start on the SMs that the shorter units of chunk c have
+    left, instead of waiting for its longest unit.  Everything is allocated here, nothing per call,
+    and repeated calls with the same host tensors replay one CUDA graph.
     """
 
     UNIT_ROWS = 148 * _lib.BLOCK_Q
@@ -672,7 +699,7 @@ class HostPipeline:
         self.k_end = torch.empty((rows,), device=device, dtype=i32)
         self.workspaces = [make_workspace(hi - lo, keys, device, seed=seed) for lo, hi in self.bounds]
         self.copy_in = torch.cuda.Stream(device=device)
-        self.compute = torch.cuda.Stream(device=device)
+        self.compute = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
         self.copy_out = torch.cuda.Stream(device=device)
 
     @classmethod
@@ -761,25 +788,27 @@ class HostPipeline:
         caller = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(caller)
-        for stream in (self.copy_in, self.compute, self.copy_out):
+        for stream in (self.copy_in, *self.compute, self.copy_out):
             stream.wait_event(start)
         with torch.cuda.stream(self.copy_in):
             self.kv.copy_(kv_bytes, non_blocking=True)
             self.kv_scales.copy_(kv_scales, non_blocking=True)
+            # a megabyte of weights and ranges in three copies, not three small copies per chunk
+            self.weights.copy_(weights, non_blocking=True)
+            self.k_start.copy_(k_start, non_blocking=True)
+            self.k_end.copy_(k_end, non_blocking=True)
         last = None
-        for (lo, hi), ws in zip(self.bounds, self.workspaces):
+        for index, ((lo, hi), ws) in enumerate(zip(self.bounds, self.workspaces)):
             arrived, scored = torch.cuda.Event(), torch.cuda.Event()
+            compute = self.compute[index % 2]
             with torch.cuda.stream(self.copy_in):
                 self.q[lo:hi].copy_(q_bytes[lo:hi], non_blocking=True)
-                self.weights[lo:hi].copy_(weights[lo:hi], non_blocking=True)
-                self.k_start[lo:hi].copy_(k_start[lo:hi], non_blocking=True)
-                self.k_end[lo:hi].copy_(k_end[lo:hi], non_blocking=True)
                 arrived.record(self.copy_in)
-            with torch.cuda.stream(self.compute):
-                self.compute.wait_event(arrived)
+            with torch.cuda.stream(compute):
+                compute.wait_event(arrived)
                 ids = run_operator(ws, self.q[lo:hi], self.kv, self.kv_scales, self.weights[lo:hi],
                                    self.k_start[lo:hi], self.k_end[lo:hi])
-                scored.record(self.compute)
+                scored.record(compute)
             with torch.cuda.stream(self.copy_out):
                 self.copy_out.wait_event(scored)
                 out[lo:hi].copy_(ids, non_blocking=True)

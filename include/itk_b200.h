@@ -161,6 +161,21 @@ typedef struct itk_fused_args {
                                  * kv_scales then are the physical pool ([physical_keys,128], [physical_keys]);
                                  * ids, ranges and `keys` stay logical.  Not offered with diag_logits. */
     int physical_keys;          /* rows of the pool, a multiple of 128 (ignored without tile_table) */
+    /* Thresholds computed inside this launch (sampled_kv != null): every whole block scores the `samples`
+     * gathered sample keys (itk_gather_sampled_kv) in front of its own keys, with the query tile it has in
+     * shared memory anyway, and takes each row's threshold from them by the rule of itk_sample_thresholds
+     * (same arithmetic, same result); the threshold is also written to thresholds_out [Q].  This saves the
+     * separate prepass launch and its second read of q; it pays while the threshold is picked by one warp
+     * (samples <= 512, contexts up to 32 K keys).  Needs key_lo = 0 and key_hi = keys.  The shards of split
+     * blocks still read `thresholds`, which the caller fills for their rows with itk_sample_thresholds
+     * (`thresholds` and thresholds_out may be the same buffer). */
+    const void* sampled_kv;     /* [samples,128] e4m3, 16-byte aligned */
+    const float* sampled_scales;/* [samples] */
+    const int32_t* sample_ids;  /* [samples] key position of every sample */
+    float* thresholds_out;      /* [Q] */
+    int samples;
+    int sample_rank;
+    int target_candidates;
 } itk_fused_args;
 int itk_fused_topk(const itk_fused_args* args, itk_stream_t stream);
 

@@ -378,6 +378,41 @@ def test_only_the_blocks_of_the_last_wave_are_split(device, rows, keys, shards, 
     assert operator.plan_key_shards(296, 16384, 148) == (0, 1)
 
 
+@pytest.mark.parametrize("workload,rows,keys,shards,split", [
+    ("c1", 24, 16384, 1, 0), ("c2", 40, 32768, 1, 0), ("c0", 8, 8192, 1, 0), ("c2", 48, 32768, 4, 5), ("c4", 64, 32768, 1, 0),
+])
+def test_thresholds_taken_inside_the_fused_launch_match_the_prepass(device, workload, rows, keys, shards, split):
+    """Up to 512 sample keys the whole blocks score the samples themselves; the thresholds they write must be
+    bit-identical to the prepass kernel's and the ids the same exact sets."""
+
+    host = make_workload_inputs(workload, query_tokens=rows, context_tokens=keys, seed=rows + 1)
+    gpu = inputs_to(host, device)
+    tensors = _tensors(gpu)
+    case = PrefillCase("in-kernel", rows, keys, 2048, 0)
+    prepass = operator.make_workspace(rows, keys, device, seed=host.case.seed, key_shards=1)
+    assert prepass.plan.enabled and prepass.plan.sample_elements <= operator.IN_KERNEL_THRESHOLD_SAMPLES
+    want_thresholds = operator.run_sample_thresholds(prepass, *tensors).clone()
+    logits = torch.full((rows, keys), -math.inf, device=device)
+    operator.run_fused_topk(prepass, *tensors, diag_logits=logits)
+    operator.run_repair(prepass, *tensors)
+    want = prepass.output_ids.clone()
+    ws = operator.make_workspace(rows, keys, device, seed=host.case.seed, key_shards=shards,
+                                 split_blocks_hint=split if shards > 1 else None)
+    ws.thresholds.fill_(777.0)
+    got = operator.run_operator(ws, *tensors)
+    torch.cuda.synchronize()
+    ws.check_status()
+    prepass.check_status()
+    assert torch.equal(ws.thresholds.view(torch.int32), want_thresholds.view(torch.int32))
+    assert int(ws.failure_flags.sum()) == 0
+    indices = got.unsqueeze(1).contiguous().cpu()
+    validate_topk_indices(indices, case)
+    verdict = score_threshold_check(indices, logits.cpu(), case)
+    same = torch.ones(rows, dtype=torch.bool, device=device)
+    same[torch.tensor(verdict["cutoff_tie_rows"], dtype=torch.long, device=device)] = False
+    assert torch.equal(got[same].sort(dim=-1).values, want[same].sort(dim=-1).values)
+
+
 def test_repair_stage_is_a_conditional_part_of_a_captured_graph(device):
     """Captured into a CUDA graph the repair stage is the body of an IF node on "some row is flagged".  One graph,
     replayed with thresholds that flag no row, then every row (+inf: the retry repairs 32 of them, the dense
