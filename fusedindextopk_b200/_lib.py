@@ -105,13 +105,13 @@ def load_library() -> ctypes.CDLL:
     )
     library.itk_merge_shard_lists.argtypes = (
         [POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int]
-        + [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]
+        + [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p, c_void_p]
     )
     library.itk_flagged_scope_begin.argtypes = [c_void_p, c_int, c_void_p, POINTER(c_void_p)]
     library.itk_flagged_scope_end.argtypes = [c_void_p, c_void_p]
     library.itk_compact_flagged_rows.argtypes = [c_void_p] * 5 + [c_int, c_int] + [c_void_p] * 6
     library.itk_repair_merge_chunk.argtypes = (
-        [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 4
+        [c_void_p] * 5 + [c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 5
     )
     library.itk_gather_sampled_kv_paged.argtypes = [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p]
     library.itk_repair_produce_paged.argtypes = [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_int, c_void_p, c_void_p]

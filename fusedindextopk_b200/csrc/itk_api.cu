@@ -555,14 +555,14 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
                               int sources, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                               itk_stream_t stream) {
     return itk_merge_shard_lists(source_pairs, source_counts, sources, out_ids, out_pairs, out_counts, rows, nullptr,
-                                 nullptr, nullptr, nullptr, 0, 0, 0, 1, 0, nullptr, stream);
+                                 nullptr, nullptr, nullptr, 0, 0, 0, 1, 0, nullptr, nullptr, stream);
 }
 
 int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
                           int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                           const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
                           const int32_t* k_end, int key_lo, int key_hi, int block_begin, int block_stride,
-                          int num_blocks, const int32_t* out_rows, itk_stream_t stream) {
+                          int num_blocks, const int32_t* out_rows, int32_t* mirror_ids, itk_stream_t stream) {
     ITK_REQUIRE(source_pairs && source_counts, "source tables must not be null");
     ITK_REQUIRE(failure_flags == nullptr || (shard_flags && k_start && k_end && key_hi > key_lo && key_lo >= 0),
                 "a row verdict needs shard_flags, k_start, k_end and 0 <= key_lo < key_hi");
@@ -587,6 +587,7 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
     params.block_stride = block_stride;
     params.owned_blocks = num_blocks;
     params.out_rows = out_rows;
+    params.mirror_ids = out_ids != nullptr ? mirror_ids : nullptr;
     params.out_ids = out_ids;
     params.out_pairs = out_pairs;
     params.out_counts = out_counts;
@@ -675,7 +676,7 @@ int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_cou
                            const int32_t* k_start, const int32_t* k_end, int chunk_lo, int chunk_hi,
                            uint8_t* failure_flags, uint8_t* repair_error_flags, int rows, int first_chunk,
                            int last_chunk, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts,
-                           itk_stream_t stream) {
+                           int32_t* mirror_ids, itk_stream_t stream) {
     ITK_REQUIRE(accumulator_pairs && accumulator_counts && repair_pairs && k_start && k_end && failure_flags &&
                     repair_error_flags,
                 "repair merge pointers must not be null");
@@ -705,6 +706,7 @@ int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_cou
         // the result of the last chunk is the row's answer: it goes to the operator output and a full
         // result clears the row's failure flag
         params.out_ids = out_ids;
+        params.mirror_ids = out_ids != nullptr ? mirror_ids : nullptr;
         params.out_pairs = out_pairs;
         params.out_counts = out_counts;
         params.clear_flags = failure_flags;

@@ -177,6 +177,7 @@ struct PairTopKParams {
     int error_selection;            // code stored when the selection is inconsistent
     uint64_t* out_pairs;            // null or [rows, 2048]
     int32_t* out_ids;               // null or [rows, 2048]
+    int32_t* mirror_ids;            // null, or a second copy of the ids ([rows, 2048], e.g. in mapped host memory)
     int32_t* out_counts;            // null or [rows]
     uint8_t* clear_flags;           // null, or flag reset to 0 for rows that produced a full result
     // Merge of the key shards of one launch: verdict_flags[row] (null = off) becomes 1 when a shard of
@@ -304,11 +305,14 @@ __global__ void __launch_bounds__(kPairThreads, 3) itk_pair_topk_kernel(const Pa
 
         uint64_t* out_pairs = p.out_pairs != nullptr ? p.out_pairs + static_cast<long long>(out_row) * kTopK : nullptr;
         int32_t* out_ids = p.out_ids != nullptr ? p.out_ids + static_cast<long long>(out_row) * kTopK : nullptr;
+        int32_t* mirror_ids = p.mirror_ids != nullptr ? p.mirror_ids + static_cast<long long>(out_row) * kTopK : nullptr;
         if (count <= kTopK) {
             for (int i = tx; i < kTopK; i += kPairThreads) {
                 const uint64_t pair = i < count ? staged[i] : 0ull;
+                const int32_t id = i < count ? static_cast<int32_t>(static_cast<uint32_t>(pair)) : -1;
                 if (out_pairs != nullptr) out_pairs[i] = pair;
-                if (out_ids != nullptr) out_ids[i] = i < count ? static_cast<int32_t>(static_cast<uint32_t>(pair)) : -1;
+                if (out_ids != nullptr) out_ids[i] = id;
+                if (mirror_ids != nullptr) mirror_ids[i] = id;
             }
             if (tx == 0) {
                 if (p.out_counts != nullptr) p.out_counts[out_row] = count;
@@ -377,6 +381,7 @@ __global__ void __launch_bounds__(kPairThreads, 3) itk_pair_topk_kernel(const Pa
                 // the staged copy is complete, so the output may alias a source
                 if (out_pairs != nullptr) out_pairs[position] = pair;
                 if (out_ids != nullptr) out_ids[position] = static_cast<int32_t>(static_cast<uint32_t>(pair));
+                if (mirror_ids != nullptr) mirror_ids[position] = static_cast<int32_t>(static_cast<uint32_t>(pair));
             }
         }
         __syncthreads();

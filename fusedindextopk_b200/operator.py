@@ -151,12 +151,17 @@ def make_workspace(
     repair: bool = True,
     key_shards: int | None = None,
     split_blocks_hint: int | None = None,
+    shard_buffers: int = 0,
+    second_spill: bool = False,
 ) -> Workspace:
     """Allocate every buffer once, outside any timed region.
 
     ``key_shards`` > 1 cuts the key range of ``split_blocks_hint`` query blocks (default: all of them)
     into that many work units each; ``None`` lets ``plan_key_shards`` choose both from Q, N and the SM
     count: the blocks of the last, partly filled wave of units are split so that they fill it.
+    ``shard_buffers`` and ``second_spill`` serve a chunked call: shard buffers for chunks that are cut
+    into more shards than the whole problem would be, and a second spill area, because the spill is
+    addressed by CTA and two launches that run at the same time (on two streams) must not share it.
     """
 
     import torch
@@ -201,15 +206,20 @@ def make_workspace(
         split_blocks = owned if key_shards > 1 else 0
         if split_blocks_hint is not None and key_shards > 1:
             split_blocks = max(1, min(owned, int(split_blocks_hint)))
-    if key_shards > 1:
-        shard_sizes = _lib.workspace_sizes(rows, keys, key_shards)
+    planes = max(key_shards, shard_buffers)   # a chunked call may cut single chunks into more shards than the whole
+    if planes > 1:
+        shard_sizes = _lib.workspace_sizes(rows, keys, planes)
         buffers.update(
-            shard_pairs=empty((key_shards, rows, TOP_K), i64),
-            shard_counts=torch.zeros((key_shards, rows), device=device, dtype=i32),
-            shard_flags=torch.zeros((key_shards, rows), device=device, dtype=u8),
+            shard_pairs=empty((planes, rows, TOP_K), i64),
+            shard_counts=torch.zeros((planes, rows), device=device, dtype=i32),
+            shard_flags=torch.zeros((planes, rows), device=device, dtype=u8),
             shard_spill=empty((shard_sizes.spill_bytes // 8,), i64),
             merged_counts=torch.zeros(rows, device=device, dtype=i32),
         )
+        if second_spill:
+            buffers["shard_spill_second"] = empty((shard_sizes.spill_bytes // 8,), i64)
+    if second_spill:
+        buffers["spill_pairs_second"] = empty((sizes.spill_bytes // 8,), i64)
     workspace = Workspace(rows, keys, device, plan, block_begin, block_stride, owned, buffers)
     workspace.split_blocks = split_blocks if key_shards > 1 else 0
     if repair and plan.enabled:
@@ -267,6 +277,24 @@ def _make_retry_buffers(rows: int, keys: int, device: Any) -> RetryBuffers:
         spill=empty((spill_bytes // 8,), i64),
         counts=torch.zeros(rows, device=device, dtype=i32),
     )
+
+
+@dataclass(frozen=True)
+class Part:
+    """The query blocks one launch handles, when that is not the workspace's whole share: a row chunk of a
+    pipelined call.  ``split_blocks`` of them (the first ones) are cut into ``shards`` key shards."""
+
+    block_begin: int
+    num_blocks: int
+    split_blocks: int = 0
+    shards: int = 1
+
+
+def _launch_part(ws: "Workspace", part: Part | None) -> Part:
+    if part is not None:
+        return part
+    shards = int(ws.shard_pairs.shape[0]) if "shard_pairs" in ws.buffers else 1
+    return Part(ws.block_begin, ws.num_blocks, ws.split_blocks if shards > 1 else 0, shards)
 
 
 # Cost model of one launch of the fused kernel, in microseconds (B200, measured): a 128-key tile of a unit,
@@ -335,12 +363,14 @@ def _on_workspace_device(function):
 
 @_on_workspace_device
 def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, diag_logits=None,
-                          trace=None, tile_table=None, only_blocks: int | None = None) -> Any:
+                          trace=None, tile_table=None, only_blocks: int | None = None, part: Part | None = None,
+                          gather: bool = True) -> Any:
     """Stages ``sample_gather`` + ``sample_indexer`` + ``sample_threshold`` of the reference graph.
 
     ``only_blocks`` limits the threshold launch to the first that many owned query blocks (0: the
     sample keys are gathered and nothing else), for calls whose other blocks take their thresholds
-    inside the fused launch.
+    inside the fused launch.  ``part`` names the query blocks of a chunked call; ``gather`` = False
+    when the sample keys of this key cache are in the workspace already.
     """
 
     import torch
@@ -351,16 +381,18 @@ def run_sample_thresholds(ws: Workspace, q, kv, kv_scales, weights, k_start, k_e
     library = load_library()
     stream = current_stream(torch, ws.device)
     plan = ws.plan
-    check(library.itk_gather_sampled_kv_paged(
-        ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(tile_table), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
-        ws.keys, int(kv.shape[0]), plan.sample_elements, stream,
-    ))
-    blocks = ws.num_blocks if only_blocks is None else min(only_blocks, ws.num_blocks)
+    if gather:
+        check(library.itk_gather_sampled_kv_paged(
+            ptr(kv), ptr(kv_scales), ptr(plan.sample_ids), ptr(tile_table), ptr(ws.sampled_kv), ptr(ws.sampled_scales),
+            ws.keys, int(kv.shape[0]), plan.sample_elements, stream,
+        ))
+    owned = _launch_part(ws, part)
+    blocks = owned.num_blocks if only_blocks is None else min(only_blocks, owned.num_blocks)
     if blocks > 0:
         check(library.itk_sample_thresholds(
             ptr(q), ptr(ws.sampled_kv), ptr(ws.sampled_scales), ptr(weights), ptr(plan.sample_ids),
             ptr(k_start), ptr(k_end), ptr(ws.thresholds), ws.rows, plan.sample_elements, plan.sample_rank,
-            plan.target_candidates, ws.block_begin, ws.block_stride, blocks, 0,
+            plan.target_candidates, owned.block_begin, ws.block_stride, blocks, 0,
             ptr(diag_logits), 0 if diag_logits is None else int(diag_logits.stride(0)),
             ptr(trace), ptr(ws.status), stream,
         ))
@@ -372,7 +404,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
                    diag_logits=None, trace=None, force_compute: bool = False, max_ctas: int = 0,
                    wait_limit_ns: int = 0, withhold_loads: bool = False,
                    key_lo: int = 0, key_hi: int | None = None, want_pairs: bool = False, tile_table=None,
-                   thresholds_in_kernel: bool = False) -> Any:
+                   thresholds_in_kernel: bool = False, part: Part | None = None, second_spill: bool = False) -> Any:
     """Stage ``fused_topk``: one launch of the persistent fused kernel.
 
     With ``tile_table`` (int32, one physical 128-key tile per logical tile) ``kv`` and ``kv_scales`` are
@@ -392,7 +424,7 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         args.out_pairs = ptr(ws.output_pairs)
         args.out_counts = ptr(ws.output_counts)
     args.failure_flags = ptr(ws.failure_flags)
-    args.spill = ptr(ws.spill_pairs)
+    args.spill = ptr(ws.spill_pairs_second if second_spill else ws.spill_pairs)
     args.diag_logits = ptr(diag_logits)
     args.diag_stride = 0 if diag_logits is None else int(diag_logits.stride(0))
     args.trace = ptr(trace)
@@ -403,7 +435,8 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
     args.key_lo = key_lo
     args.key_hi = ws.keys if key_hi is None else key_hi
     args.shards = 1
-    args.block_begin, args.block_stride, args.num_blocks = ws.block_begin, ws.block_stride, ws.num_blocks
+    owned = _launch_part(ws, part)
+    args.block_begin, args.block_stride, args.num_blocks = owned.block_begin, ws.block_stride, owned.num_blocks
     args.force_compute = 1 if force_compute else 0
     args.max_ctas = max_ctas
     args.tile_table = ptr(tile_table)
@@ -415,14 +448,16 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
         args.sampled_kv, args.sampled_scales = ptr(ws.sampled_kv), ptr(ws.sampled_scales)
         args.sample_ids, args.thresholds_out = ptr(plan.sample_ids), ptr(ws.thresholds)
         args.samples, args.sample_rank, args.target_candidates = plan.sample_elements, plan.sample_rank, plan.target_candidates
-    sharded = "shard_pairs" in ws.buffers and diag_logits is None
+    sharded = owned.shards > 1 and owned.split_blocks > 0 and diag_logits is None
     if sharded:
         # the blocks of the last wave are cut into key shards: every (block, shard) is a work unit, the
         # shards share the row's threshold and return pairs, which the merge below turns into the row's ids
-        args.shards = int(ws.shard_pairs.shape[0])
-        args.split_blocks = ws.split_blocks
+        _require(owned.shards <= int(ws.shard_pairs.shape[0]), "the workspace has too few shard buffers for this part")
+        args.shards = owned.shards
+        args.split_blocks = owned.split_blocks
         args.shard_pairs, args.shard_counts = ptr(ws.shard_pairs), ptr(ws.shard_counts)
-        args.shard_flags, args.spill = ptr(ws.shard_flags), ptr(ws.shard_spill)
+        args.shard_flags = ptr(ws.shard_flags)
+        args.spill = ptr(ws.shard_spill_second if second_spill else ws.shard_spill)
     library = load_library()
     stream = current_stream(torch, ws.device)
     check(library.itk_fused_topk(ctypes.byref(args), stream))
@@ -437,13 +472,14 @@ def run_fused_topk(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, 
             pair_table, count_table, shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
             ptr(ws.output_counts) if want_pairs else ptr(ws.merged_counts), ws.rows,
             ptr(ws.shard_flags), ptr(ws.failure_flags), ptr(k_start), ptr(k_end), key_lo, args.key_hi,
-            ws.block_begin, ws.block_stride, ws.split_blocks, None, stream))
+            owned.block_begin, ws.block_stride, owned.split_blocks, None, None, stream))
     return ws.output_ids
 
 
 @_on_workspace_device
 def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
-              key_hi: int | None = None, want_pairs: bool = False, tile_table=None, stream: int | None = None) -> Any:
+              key_hi: int | None = None, want_pairs: bool = False, tile_table=None, stream: int | None = None,
+              mirror=None) -> Any:
     """Flagged rows once more, with a lower threshold and a candidate list per key shard.
 
     Four launches, all of them over the compact problem of ``RETRY_SLOTS`` rows and returning at once
@@ -495,18 +531,21 @@ def run_retry(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_l
         pair_table, count_table, retry.shards, ptr(ws.output_ids), ptr(ws.output_pairs) if want_pairs else None,
         ptr(ws.output_counts) if want_pairs else ptr(retry.counts), slots,
         ptr(retry.shard_flags), ptr(ws.failure_flags), ptr(retry.k_start), ptr(retry.k_end), key_lo, key_hi,
-        0, 1, 0, ptr(retry.slot_rows), stream))
+        0, 1, 0, ptr(retry.slot_rows), ptr(mirror), stream))
     return ws.output_ids
 
 
 @_on_workspace_device
 def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_lo: int = 0,
-               key_hi: int | None = None, want_pairs: bool = False, tile_table=None, retry: bool = True) -> Any:
+               key_hi: int | None = None, want_pairs: bool = False, tile_table=None, retry: bool = True,
+               mirror=None) -> Any:
     """Stage ``hierarchical_repair``: always launched, masked on the device by the failure flags.
 
     First the retry of the flagged rows (``run_retry``), then, for what is still flagged, the dense
     rescan: per 16384-key chunk one launch of the dense producer and one that selects the chunk's pairs
     into the running Top-2048 of each flagged row (the last one writes the ids and clears the flags).
+    ``mirror`` (int32 ``[Q, 2048]``, e.g. the pinned host buffer the fast path's ids were copied to
+    already) receives a second copy of the ids of every repaired row.
     """
 
     import torch
@@ -528,7 +567,7 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
     try:
         if retry:
             run_retry(ws, q, kv, kv_scales, weights, k_start, k_end, key_lo=key_lo, key_hi=key_hi,
-                      want_pairs=want_pairs, tile_table=tile_table, stream=stream)
+                      want_pairs=want_pairs, tile_table=tile_table, stream=stream, mirror=mirror)
         for index, (chunk_lo, chunk_hi) in enumerate(chunks):
             check(library.itk_repair_produce_paged(
                 ptr(q), ptr(kv), ptr(kv_scales), ptr(weights), ptr(k_start), ptr(k_end), ptr(ws.failure_flags),
@@ -540,7 +579,8 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
                 ptr(ws.accumulator_pairs), ptr(ws.accumulator_counts), ptr(ws.repair_pairs), ptr(k_start), ptr(k_end),
                 chunk_lo, chunk_hi, ptr(ws.failure_flags), ptr(ws.repair_error_flags), ws.rows,
                 1 if index == 0 else 0, 1 if last else 0, ptr(ws.output_ids),
-                ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None, stream,
+                ptr(ws.output_pairs) if want_pairs else None, ptr(ws.output_counts) if want_pairs else None,
+                ptr(mirror), stream,
             ))
     finally:
         check(library.itk_flagged_scope_end(outer, stream))
@@ -552,15 +592,22 @@ def run_repair(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, key_
 IN_KERNEL_THRESHOLD_SAMPLES = 512
 
 
-def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, tile_table=None) -> Any:
-    """Sampling + fused kernel + repair on the current stream; returns ``ws.output_ids``."""
+def run_operator(ws: Workspace, q, kv, kv_scales, weights, k_start, k_end, *, tile_table=None,
+                 part: Part | None = None, gather: bool = True, repair: bool = True, second_spill: bool = False) -> Any:
+    """Sampling + fused kernel + repair on the current stream; returns ``ws.output_ids``.
+
+    ``part``, ``gather`` and ``repair`` serve a chunked call (``HostPipeline``): the fast path of one
+    range of query blocks, with the sample keys gathered once and the repair stage run once at the end.
+    """
 
     in_kernel = ws.plan.enabled and ws.plan.sample_elements <= IN_KERNEL_THRESHOLD_SAMPLES
+    owned = _launch_part(ws, part)
     # the separate threshold launch serves the rows of split blocks (all rows when the fused launch does not sample)
-    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table,
-                          only_blocks=ws.split_blocks if in_kernel else None)
-    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table, thresholds_in_kernel=in_kernel)
-    if "repair_pairs" in ws.buffers:
+    run_sample_thresholds(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table, part=part, gather=gather,
+                          only_blocks=(owned.split_blocks if owned.shards > 1 else 0) if in_kernel else None)
+    run_fused_topk(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table, thresholds_in_kernel=in_kernel,
+                   part=part, second_spill=second_spill)
+    if repair and "repair_pairs" in ws.buffers:
         run_repair(ws, q, kv, kv_scales, weights, k_start, k_end, tile_table=tile_table)
     return ws.output_ids
 
@@ -664,32 +711,43 @@ def _warn_once(message: str) -> None:
 class HostPipeline:
     """The operator for callers whose tensors live in pinned host memory.
 
-    Query rows are independent, so the call is cut into a few row chunks that flow through four
-    streams: host-to-device copies of chunk c+1, the operator on chunk c and the device-to-host
-    copy of the ids of chunk c-1 overlap (the PCIe link is full duplex and the copy engines run
-    beside the SMs).  Keys, scales and the small per-row tensors are copied once, ahead of the first
-    chunk.  Chunks are whole multiples of 148 work units (592 rows) where the row count allows, so that
-    every chunk fills the persistent kernel's CTAs evenly; the short chunk goes first, which also
-    shortens the time before the first kernel can start.  Consecutive chunks run on two alternating
-    compute streams: the CTAs of chunk c+1 start on the SMs that the shorter units of chunk c have
-    left, instead of waiting for its longest unit.  Everything is allocated here, nothing per call,
-    and repeated calls with the same host tensors replay one CUDA graph.
+    Query rows are independent, so the call is cut into row chunks that flow through four streams:
+    the host-to-device copy of chunk c+1, the fast path (thresholds + fused kernel) of chunk c and
+    the device-to-host copy of the ids of chunk c-1 overlap (the PCIe link is full duplex and the
+    copy engines run beside the SMs).  Keys, scales and the small per-row tensors are copied once,
+    ahead of the first chunk, and the sample keys are gathered once.  All chunks share one workspace;
+    a chunk is a range of its query blocks.  Consecutive chunks alternate between two compute
+    streams, so that the CTAs of chunk c+1 start on the SMs that the shorter units of chunk c have
+    left.  The repair stage runs once, after the last chunk: it writes the ids of repaired rows
+    into the device output and, through the mapping of the pinned buffer, straight into ``out``
+    (their stale fast-path ids were copied there before), so no second copy of the output is needed.
+    Everything is allocated here, nothing per call, and repeated calls with the same host tensors
+    replay one CUDA graph.
     """
 
-    UNIT_ROWS = 148 * _lib.BLOCK_Q
+    UNIT_BLOCKS = 148                     # one wave of work units
+    EDGE_BLOCKS = 37                      # a quarter wave: the first and the last chunk of a long call
+    UNIT_ROWS = UNIT_BLOCKS * _lib.BLOCK_Q
+    EDGE_ROWS = EDGE_BLOCKS * _lib.BLOCK_Q
 
     def __init__(self, rows: int, keys: int, device: Any, *, chunk_units: int = 1, seed: int = 0,
                  use_graph: bool = True):
         import torch
 
-        # From the second call with the same host tensors on, the whole pipeline (some sixty copies
-        # and launches on three streams) is replayed as one CUDA graph.
+        # From the second call with the same host tensors on, the whole pipeline (some forty copies
+        # and launches on four streams) is replayed as one CUDA graph.
         self.use_graph = use_graph
         self._graphs: dict[tuple, Any] = {}
         self._seen: set[tuple] = set()
 
         self.rows, self.keys, self.device = rows, keys, device
         self.bounds = self.chunk_bounds(rows, chunk_units)
+        sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self.parts = []
+        for lo, hi in self.bounds:
+            blocks = (hi - lo + _lib.BLOCK_Q - 1) // _lib.BLOCK_Q
+            split, shards = plan_key_shards(blocks, keys, sm_count)
+            self.parts.append(Part(lo // _lib.BLOCK_Q, blocks, split, shards))
         f8, i32, f32 = torch.float8_e4m3fn, torch.int32, torch.float32
         self.q = torch.empty((rows, _lib.HEADS, _lib.HEAD_DIM), device=device, dtype=f8)
         self.kv = torch.empty((keys, _lib.HEAD_DIM), device=device, dtype=f8)
@@ -697,24 +755,37 @@ class HostPipeline:
         self.weights = torch.empty((rows, _lib.HEADS), device=device, dtype=f32)
         self.k_start = torch.empty((rows,), device=device, dtype=i32)
         self.k_end = torch.empty((rows,), device=device, dtype=i32)
-        self.workspaces = [make_workspace(hi - lo, keys, device, seed=seed) for lo, hi in self.bounds]
+        self.workspace = make_workspace(rows, keys, device, seed=seed, key_shards=1, second_spill=True,
+                                        shard_buffers=max(part.shards for part in self.parts))
         self.copy_in = torch.cuda.Stream(device=device)
         self.compute = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
         self.copy_out = torch.cuda.Stream(device=device)
 
     @classmethod
     def chunk_bounds(cls, rows: int, chunk_units: int = 1) -> list[tuple[int, int]]:
-        """Row ranges of the chunks: the remainder first, then whole multiples of 148 work units."""
+        """Row ranges of the chunks (every boundary a multiple of 4 rows, the block of a work unit).
+
+        The copies into the device are what bounds a long call, so what counts is how soon the first
+        kernel can start and how little is left to do after the last copy: a call of more than two
+        waves begins and ends with a chunk of 148 rows (a quarter wave of units; the planner cuts their
+        key ranges into shards, so that they still use every SM), with whole multiples of 148 work
+        units (592 rows) and one remainder chunk between them.  Shorter calls are one remainder chunk
+        followed by whole waves.
+        """
 
         if rows <= 0:
             raise ValueError("rows must be positive")
-        step = max(1, chunk_units) * cls.UNIT_ROWS
-        bounds = []
-        first = rows % step or min(rows, step)
-        begin = 0
-        while begin < rows:
-            size = first if begin == 0 else min(step, rows - begin)
-            bounds.append((begin, begin + size))
+        blocks = (rows + _lib.BLOCK_Q - 1) // _lib.BLOCK_Q
+        step = max(1, chunk_units) * cls.UNIT_BLOCKS
+        if blocks > 2 * step + 2 * cls.EDGE_BLOCKS:
+            middle = blocks - 2 * cls.EDGE_BLOCKS
+            sizes = [cls.EDGE_BLOCKS] + [step] * (middle // step) + ([middle % step] if middle % step else []) + [cls.EDGE_BLOCKS]
+        else:
+            first = blocks % step or min(blocks, step)
+            sizes = [first] + [step] * ((blocks - first) // step)
+        bounds, begin = [], 0
+        for size in sizes:
+            bounds.append((begin * _lib.BLOCK_Q, min(rows, (begin + size) * _lib.BLOCK_Q)))
             begin += size
         return bounds
 
@@ -722,7 +793,7 @@ class HostPipeline:
         """All arguments are pinned host tensors; ``out`` is int32 ``[Q, 2048]`` and is returned.
 
         The copies and kernels are ordered after the work already queued on the caller's current
-        stream, and that stream waits for the last copy into ``out``.
+        stream, and that stream waits for the last write into ``out``.
         """
 
         import torch
@@ -784,41 +855,58 @@ class HostPipeline:
         import torch
 
         q, kv, kv_scales, weights, k_start, k_end, out = tensors
-        q_bytes, kv_bytes = q, kv
+        ws = self.workspace
+        device_tensors = (self.q, self.kv, self.kv_scales, self.weights, self.k_start, self.k_end)
         caller = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(caller)
         for stream in (self.copy_in, *self.compute, self.copy_out):
             stream.wait_event(start)
         with torch.cuda.stream(self.copy_in):
-            self.kv.copy_(kv_bytes, non_blocking=True)
+            self.kv.copy_(kv, non_blocking=True)
             self.kv_scales.copy_(kv_scales, non_blocking=True)
             # a megabyte of weights and ranges in three copies, not three small copies per chunk
             self.weights.copy_(weights, non_blocking=True)
             self.k_start.copy_(k_start, non_blocking=True)
             self.k_end.copy_(k_end, non_blocking=True)
-        last = None
-        for index, ((lo, hi), ws) in enumerate(zip(self.bounds, self.workspaces)):
+        gathered = torch.cuda.Event()
+        scored = None
+        for index, ((lo, hi), part) in enumerate(zip(self.bounds, self.parts)):
             arrived, scored = torch.cuda.Event(), torch.cuda.Event()
             compute = self.compute[index % 2]
             with torch.cuda.stream(self.copy_in):
-                self.q[lo:hi].copy_(q_bytes[lo:hi], non_blocking=True)
+                self.q[lo:hi].copy_(q[lo:hi], non_blocking=True)
                 arrived.record(self.copy_in)
             with torch.cuda.stream(compute):
                 compute.wait_event(arrived)
-                ids = run_operator(ws, self.q[lo:hi], self.kv, self.kv_scales, self.weights[lo:hi],
-                                   self.k_start[lo:hi], self.k_end[lo:hi])
+                if index == 1:
+                    compute.wait_event(gathered)    # the other compute stream gathered the sample keys
+                run_operator(ws, *device_tensors, part=part, gather=index == 0, repair=False,
+                             second_spill=index % 2 == 1)
+                if index == 0:
+                    gathered.record(compute)
                 scored.record(compute)
             with torch.cuda.stream(self.copy_out):
                 self.copy_out.wait_event(scored)
-                out[lo:hi].copy_(ids, non_blocking=True)
-                last = torch.cuda.Event()
-                last.record(self.copy_out)
-        caller.wait_event(last)
+                out[lo:hi].copy_(ws.output_ids[lo:hi], non_blocking=True)
+        copied = torch.cuda.Event()
+        copied.record(self.copy_out)
+        # The repair stage, once for all rows, after every fast-path id has reached `out`: what it repairs
+        # it writes to the device output and, through the mapped pinned buffer, over the stale ids in `out`.
+        closing, other = self.compute[(len(self.bounds) - 1) % 2], self.compute[len(self.bounds) % 2]
+        joined = torch.cuda.Event()
+        joined.record(other)
+        with torch.cuda.stream(closing):
+            closing.wait_event(copied)
+            closing.wait_event(joined)
+            if "repair_pairs" in ws.buffers:
+                run_repair(ws, *device_tensors, mirror=out)
+            done = torch.cuda.Event()
+            done.record(closing)
+        caller.wait_event(done)
 
     def check_status(self) -> None:
-        for ws in self.workspaces:
-            ws.check_status()
+        self.workspace.check_status()
 
 
 _HOST_PIPELINES: dict[tuple, HostPipeline] = {}

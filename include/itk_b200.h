@@ -231,13 +231,16 @@ int itk_merge_candidate_lists(const uint64_t* const* source_pairs, const int32_t
  * go to the repair graph.  Only the rows of the query blocks block_begin + i * block_stride,
  * i < num_blocks, are merged (num_blocks = 0: every row).  With out_rows (int32 [rows], optional)
  * the lists, k_start and k_end are those of a compacted problem and row r's ids, pairs, count and
- * flag go to row out_rows[r] of the outputs; r is skipped when out_rows[r] < 0.
+ * flag go to row out_rows[r] of the outputs; r is skipped when out_rows[r] < 0.  mirror_ids
+ * (optional, [Q,2048]) receives a second copy of the ids of every row written: a caller that has
+ * already copied the fast path's ids to the host passes the mapped host buffer here, so that
+ * repaired rows reach it without another copy of the whole output.
  * No counterpart in the reference (one unit per query block there). */
 int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* const* source_counts, int sources,
                           int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts, int rows,
                           const uint8_t* shard_flags, uint8_t* failure_flags, const int32_t* k_start,
                           const int32_t* k_end, int key_lo, int key_hi, int block_begin, int block_stride,
-                          int num_blocks, const int32_t* out_rows, itk_stream_t stream);
+                          int num_blocks, const int32_t* out_rows, int32_t* mirror_ids, itk_stream_t stream);
 
 /* A scope of launches that only matter when a row is flagged (the whole repair stage).  When `stream`
  * is being captured into a CUDA graph, begin adds a one-CTA kernel that looks at failure_flags [rows]
@@ -267,14 +270,15 @@ int itk_compact_flagged_rows(const uint8_t* failure_flags, const void* q, const 
  * accumulator <- Top-2048(accumulator U the dense pairs of chunk [chunk_lo, chunk_hi)) for flagged rows;
  * the chunk-local key range of each row is derived from k_start / k_end here, so no
  * itk_update_chunk_ranges launch is needed.  With last_chunk the result goes to out_ids / out_pairs /
- * out_counts instead and a complete row's failure flag is cleared.  Error codes as in the separate
+ * out_counts (and a second copy of the ids to mirror_ids, optional, as in itk_merge_shard_lists)
+ * instead and a complete row's failure flag is cleared.  Error codes as in the separate
  * steps (count mismatch 1, selection 3).  Same kernels of the reference as those three
  * (long_context_repair.cu:237-426), launched there once each per chunk. */
 int itk_repair_merge_chunk(uint64_t* accumulator_pairs, int32_t* accumulator_counts, const uint64_t* repair_pairs,
                            const int32_t* k_start, const int32_t* k_end, int chunk_lo, int chunk_hi,
                            uint8_t* failure_flags, uint8_t* repair_error_flags, int rows, int first_chunk,
                            int last_chunk, int32_t* out_ids, uint64_t* out_pairs, int32_t* out_counts,
-                           itk_stream_t stream);
+                           int32_t* mirror_ids, itk_stream_t stream);
 
 /* Paged forms of itk_gather_sampled_kv and itk_repair_produce: the keys live in a pool of
  * 128-key physical tiles addressed through tile_table as in itk_fused_args.  The reference

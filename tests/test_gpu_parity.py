@@ -471,20 +471,62 @@ def test_public_callable_replays_a_graph_with_the_same_result(device):
     assert torch.equal(fused_index_topk(*args, workspace=workspace).sort(dim=-1).values, flipped)
 
 
+def test_repaired_rows_are_mirrored_into_a_mapped_host_buffer(device):
+    """The repair stage writes the ids of the rows it repairs a second time, into a pinned host buffer
+    (the host pipeline's output, which holds the stale fast-path ids of those rows by then)."""
+
+    rows, keys = 40, 20000
+    host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys, seed=4)
+    ws, _, fast_flags = _run_with_diagnostics(host, device, thresholds=math.inf, repair=False)
+    assert int(fast_flags.sum()) == rows
+    mirror = torch.full((rows, 2048), -11, dtype=torch.int32).pin_memory()
+    operator.run_repair(ws, *_tensors(inputs_to(host, device)), mirror=mirror)   # 32 rows by the retry, 8 by the rescan
+    torch.cuda.synchronize()
+    ws.check_status()
+    assert int(ws.failure_flags.sum()) == 0
+    assert torch.equal(mirror, ws.output_ids.cpu())
+
+
+def test_host_pipeline_repairs_a_flagged_row_of_a_long_context(device):
+    """c3 (4096 x 163840) from pinned host buffers: nine chunks, one of which holds the row the fast path
+    flags; the repair stage at the end of the pipeline must put its ids into the host output."""
+
+    from fusedindextopk_b200 import fused_index_topk
+    from fusedindextopk_b200.operator import HostPipeline
+
+    host = make_workload_inputs("c3")
+    rows, keys = host.case.query_tokens, host.case.context_tokens
+    gpu = inputs_to(host, device)
+    want = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end).clone()
+    pinned = [getattr(host, name).contiguous().pin_memory() for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")]
+    out = torch.empty((rows, 2048), dtype=torch.int32).pin_memory()
+    pipeline = HostPipeline(rows, keys, device)
+    for call in range(3):
+        out.fill_(-7)
+        pipeline(pinned[0], (pinned[1], pinned[2]), pinned[3], pinned[4], pinned[5], out)
+        torch.cuda.synchronize()
+        pipeline.check_status()
+        assert int(pipeline.workspace.failure_flags.sum()) == 0
+        assert int((out < 0).sum()) == 0 and int((out >= keys).sum()) == 0
+        differing = (out.sort(dim=-1).values != want.cpu().sort(dim=-1).values).any(dim=1)
+        assert int(differing.sum()) <= 4, f"call {call}: {int(differing.sum())} rows differ from the device call"   # cutoff ties only
+        assert torch.equal(out, pipeline.workspace.output_ids.cpu())
+
+
 def test_host_pipeline_matches_the_device_call(device):
     """Pinned host tensors through the chunked three-stream pipeline give the device call's sets."""
 
     from fusedindextopk_b200 import fused_index_topk
     from fusedindextopk_b200.operator import HostPipeline
 
-    rows, keys = 1500, 8192      # three row chunks (316 + 592 + 592), ragged tail block
+    rows, keys = 1500, 8192      # five row chunks (148 + 592 + 592 + 20 + 148), ragged blocks
     host = make_workload_inputs("c1", query_tokens=rows, context_tokens=keys)
     gpu = inputs_to(host, device)
     want = fused_index_topk(gpu.q, (gpu.kv, gpu.kv_scales), gpu.weights, gpu.k_start, gpu.k_end).clone()
     pinned = [getattr(host, name).contiguous().pin_memory() for name in ("q", "kv", "kv_scales", "weights", "k_start", "k_end")]
     out = torch.full((rows, 2048), -7, dtype=torch.int32).pin_memory()
     pipeline = HostPipeline(rows, keys, device)
-    assert len(pipeline.bounds) == 3 and pipeline.bounds[0] == (0, 316)
+    assert [hi - lo for lo, hi in pipeline.bounds] == [148, 592, 592, 20, 148]
     for _ in range(3):   # the first call runs on the streams, the second captures a CUDA graph, the third replays it
         out.fill_(-7)
         result = pipeline(pinned[0], (pinned[1], pinned[2]), pinned[3], pinned[4], pinned[5], out)

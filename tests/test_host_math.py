@@ -131,14 +131,23 @@ def test_host_pipeline_chunks_cover_the_rows_in_whole_waves():
 
     unit = HostPipeline.UNIT_ROWS
     assert unit == 148 * 4
-    assert HostPipeline.chunk_bounds(4096, 2) == [(0, 544), (544, 1728), (1728, 2912), (2912, 4096)]
+    edge = HostPipeline.EDGE_ROWS
+    assert edge == 148
+    # a long call: a quarter wave first and last, whole waves and one remainder between them
+    assert HostPipeline.chunk_bounds(4096, 1) == [(0, 148), (148, 740), (740, 1332), (1332, 1924), (1924, 2516),
+                                                  (2516, 3108), (3108, 3700), (3700, 3948), (3948, 4096)]
+    assert HostPipeline.chunk_bounds(4096, 2) == [(0, 148), (148, 1332), (1332, 2516), (2516, 3700), (3700, 3948),
+                                                  (3948, 4096)]
+    # short calls: the remainder, then whole waves
     assert HostPipeline.chunk_bounds(1184, 2) == [(0, 1184)]
+    assert HostPipeline.chunk_bounds(1400, 1) == [(0, 216), (216, 808), (808, 1400)]
     assert HostPipeline.chunk_bounds(5, 2) == [(0, 5)]
-    for rows in (1, 591, 592, 593, 4096, 10000):
+    for rows in (1, 591, 592, 593, 1480, 1481, 4095, 4096, 10000, 10001):
         for units in (1, 2, 3):
             bounds = HostPipeline.chunk_bounds(rows, units)
             assert bounds[0][0] == 0 and bounds[-1][1] == rows
-            assert all(a[1] == b[0] for a, b in zip(bounds, bounds[1:]))
-            assert all((hi - lo) % (units * unit) == 0 for lo, hi in bounds[1:])
+            assert all(a[1] == b[0] and a[1] > a[0] and a[1] % 4 == 0 for a, b in zip(bounds, bounds[1:]))
+            whole = [hi - lo for lo, hi in bounds[1:-1]] if len(bounds) > 2 else []
+            assert sum(1 for size in whole if size % (units * unit)) <= 1
     with pytest.raises(ValueError):
         HostPipeline.chunk_bounds(0)
