@@ -51,12 +51,12 @@ NOMINAL_FP8_TFLOPS = 4500.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused-kernel launch, from the ncu
 # capture summarised under profiles/ (bytes per launch at the named size), or None.
 NCU_TRAFFIC_BYTES = {
-    # captured at (c1, 512 rows, 16384 keys): 6,566,912 B read, 0 B written (the 4 MiB of ids were still
+    # captured at (c1, 512 rows, 16384 keys): 6,695,424 B read, 0 B written (the 4 MiB of ids were still
     # in L2 when the kernel ended)
-    ("c1", 512, 16384): 6566912,
+    ("c1", 512, 16384): 6695424,
     # scaled to the full launch by the rows processed: the row-proportional part of the reads (q,
-    # weights, ranges: everything but the 2.16 MB of keys and scales, which are read once) x 8
-    ("c1", 4096, 16384): int((6566912 - 2162688) * 8 + 2162688),
+    # weights, ranges: everything but the 2.2 MB of keys, scales and sample keys, which are read once) x 8
+    ("c1", 4096, 16384): int((6695424 - 2195456) * 8 + 2195456),
 }
 
 
