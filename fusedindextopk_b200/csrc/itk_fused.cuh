@@ -15,10 +15,13 @@
 // The dense score matrix is never written.  What happens to a score depends on
 // the kernel mode:
 //   kModeTopK    keep (score, key) when the key is inside the row's range and
-//                score >= threshold[row]; candidates go to per-row shared-memory
-//                segments (overflow to a bounded global spill) and are counted in a
-//                per-row histogram; when the unit's last tile is done the four
-//                epilogue warps of a row select its exact Top-2048 in place;
+//                score >= threshold[row]; every epilogue thread appends to its own
+//                candidate list in shared memory (overflow to a bounded global
+//                spill); when the unit's last tile is done the four epilogue warps
+//                of a row select its exact Top-2048 in place.  With sample_tiles > 0
+//                the unit first scores the gathered sample keys and takes its rows'
+//                thresholds from them; the blocks of the last wave may be cut into
+//                key shards whose lists a merge kernel combines;
 //   kModeSample  the "keys" are S gathered sample keys; one warp per row picks the
 //                rank-th largest valid sampled score = the row's threshold;
 //   kModeRepair  for rows flagged as failed, write every (score, key) of one
@@ -1835,8 +1838,8 @@ __global__ void __launch_bounds__(kThreads, 1) itk_fused_kernel(const __grid_con
             trace[kTraceEpiWaitW] = wait_w;
             if (own_r == 0) {
                 long long* cta_trace = p.trace + static_cast<long long>(blockIdx.x) * kTraceFields;
-                cta_trace[27] = laps[1];   // octave histogram pass
-                cta_trace[28] = laps[2];   // sub-bin histogram pass
+                cta_trace[27] = laps[1];   // histogram pass
+                cta_trace[28] = laps[2];   // bin of the cutoff and its exact edges
                 cta_trace[29] = laps[3];   // emission
                 cta_trace[30] = laps[4];   // list ranking
                 cta_trace[31] = laps[5];   // whole selection incl. fallback
