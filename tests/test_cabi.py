@@ -67,6 +67,16 @@ def test_argument_errors_are_reported_before_any_launch(library):
     assert library.itk_gather_sampled_kv(None, None, None, None, None, 8, 4, None) == -1
     assert library.itk_update_chunk_ranges(None, None, None, None, 4, 8192, None) == -1
     assert library.itk_merge_candidate_lists(None, None, 2, None, None, None, 4, None) == -1
+    # the entry points of the repair stage
+    assert library.itk_compact_flagged_rows(None, None, None, None, None, 8, 32, None, None, None, None, None, None) == -1
+    assert b"must not be null" in library.itk_last_error()
+    body = ctypes.c_void_p()
+    assert library.itk_flagged_scope_begin(None, 8, None, ctypes.byref(body)) == -1
+    assert library.itk_flagged_scope_end(None, None) == 0      # nothing was opened: nothing to close
+    assert library.itk_repair_merge_chunk(None, None, None, None, None, 0, 16384, None, None, 8, 1, 1,
+                                          None, None, None, None, None) == -1
+    assert library.itk_merge_shard_lists(None, None, 17, None, None, None, 4, None, None, None, None, 0, 0,
+                                         0, 1, 0, None, None, None) == -1
 
 
 def test_fused_args_layout_matches_header():
