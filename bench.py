@@ -541,7 +541,7 @@ def main() -> None:
         out_host = torch.empty((rows, 2048), dtype=torch.int32).pin_memory()
         h2d_bytes = sum(t.numel() * t.element_size() for t in pinned.values())
         d2h_bytes = out_host.numel() * out_host.element_size()
-        # the package's host-buffer entry: row chunks over three streams (copies in, kernels, ids out)
+        # the package's host-buffer entry: row chunks over four streams (copies in, two for the kernels, ids out)
         pipeline = HostPipeline(rows, keys, device, seed=host.case.seed, chunk_units=args.e2e_chunk_units)
 
         def e2e_step(step: int):

@@ -249,8 +249,10 @@ int itk_merge_shard_lists(const uint64_t* const* source_pairs, const int32_t* co
  * flagged; a replay without flagged rows then pays for two graph nodes instead of for every launch of
  * the stage.  Work enqueued on `stream` after the scope is ordered after the body.  Outside a capture
  * (or where the driver offers no conditional nodes) *body_stream is `stream` itself and the launches
- * run as they are; each of them returns at once on the device when it finds no flagged row.  The
- * reference launches its repair graph unconditionally (src/fused_index_topk/kernel/plugin.py:333-377). */
+ * run as they are; each of them returns at once on the device when it finds no flagged row.  One
+ * scope at a time per device (the library keeps one body stream per device); the first call on a
+ * device should come outside a capture, like every other entry point's.  The reference launches its
+ * repair graph unconditionally (src/fused_index_topk/kernel/plugin.py:333-377). */
 int itk_flagged_scope_begin(const uint8_t* failure_flags, int rows, itk_stream_t stream, itk_stream_t* body_stream);
 int itk_flagged_scope_end(itk_stream_t stream, itk_stream_t body_stream);
 

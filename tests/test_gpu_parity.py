@@ -514,7 +514,7 @@ def test_host_pipeline_repairs_a_flagged_row_of_a_long_context(device):
 
 
 def test_host_pipeline_matches_the_device_call(device):
-    """Pinned host tensors through the chunked three-stream pipeline give the device call's sets."""
+    """Pinned host tensors through the chunked pipeline give the device call's sets."""
 
     from fusedindextopk_b200 import fused_index_topk
     from fusedindextopk_b200.operator import HostPipeline
