@@ -633,3 +633,19 @@ def test_full_size_parity(device, workload, rows, keys):
           f"{own['rows_with_cutoff_ties']}/{own['rows_checked']}; vs oracle on {int(sample.numel())} rows: score error "
           f"{worst:.2e} of row max, rows_with_set_difference {report['rows_with_set_difference']}, "
           f"ids_swapped_within_tolerance {report['ids_swapped_within_tolerance']}")
+
+
+def test_phase_trace_report_of_the_diagnostic_build(device):
+    """`python -m fusedindextopk_b200.trace`: the counters of one traced launch add up."""
+
+    from fusedindextopk_b200.trace import phase_trace
+
+    report = phase_trace("c0", rows=16, keys=8192)
+    assert report["active_ctas"] == 4                       # four blocks of four rows, one unit each
+    fields = report["fields"]
+    assert fields["issuer: tiles"][0] == 64                 # 8192 keys in 128-key tiles
+    total = fields["epilogue (row 0): total"][0]
+    assert 0 < fields["epilogue: selection"][0] < total
+    assert fields["issuer: wait for a free accumulator"][0] < fields["issuer: total"][0]
+    assert fields["selection: rows that fell back to the radix rounds"][2] <= 7
+    assert 0 < report["cta_wall_us"][0] < 10_000 and 0.5 < report["sm_ghz"] < 3.0
